@@ -1,0 +1,72 @@
+// Shared helpers of the sm_100a kernels: element types, warp and block
+// reductions, launch checks.  Every exported function is plain C, takes raw
+// device pointers and the stream to launch on, and returns 0 or an error
+// code whose text sib_last_error() gives.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SIB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum SibDtype { SIB_F32 = 0, SIB_BF16 = 1 };
+
+void sib_set_error(const char* fmt, ...);
+int sib_check_launch(const char* what);
+
+#define SIB_REQUIRE(cond, ...)            \
+    do {                                  \
+        if (!(cond)) {                    \
+            sib_set_error(__VA_ARGS__);   \
+            return -1;                    \
+        }                                 \
+    } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats of shared memory and may be reused after return.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Dispatch on a SibDtype code: BODY sees the element type as T.
+#define SIB_DISPATCH_DTYPE(code, ...)                                         \
+    do {                                                                      \
+        if ((code) == SIB_F32) { typedef float T; __VA_ARGS__; }              \
+        else if ((code) == SIB_BF16) { typedef __nv_bfloat16 T; __VA_ARGS__; } \
+        else { sib_set_error("unknown element type code %d", (int)(code)); return -1; } \
+    } while (0)

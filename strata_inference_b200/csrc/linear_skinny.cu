@@ -1,0 +1,205 @@
+// y[R, N] = x[R, K] . W[N, K]^T for a few rows (R <= 64), bfloat16 operands,
+// 32-bit accumulation: the weight-streaming product of decoding, where every
+// weight is read once and the time is the time to read it.
+//
+// The weight tile is the A operand of mma.m16n8k16 (16 weight rows), the
+// activations are the B operand (8 activation rows per tile).  Fragments are
+// loaded straight from global memory with 16-byte loads: lane (g, t) reads 16
+// consecutive k of weight rows g and g + 8 and of activation row g.  Which k a
+// fragment register stands for is permuted the same way on both operands, so
+// the sums are those of the plain product.  The 8 warps of a block take
+// alternating 64-wide blocks of k of the same 16 (or 32) weight rows; their
+// partial sums are added in warp order through shared memory.
+//
+// Epilogues: none; soft cap (cap * tanh(y / cap)); gated tanh-GELU, for which
+// the weight rows come in groups of 16: 8 gate rows, then the 8 matching up
+// rows, and y gets N / 2 columns.
+// Plain counterpart: tests/plain_gemma2.py (x @ W.T), gelu_tanh(), lm_head().
+// Reference: src/model/layer.rs:22-43 (x . W^T, weights [out, in]).
+#include "common.cuh"
+
+enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2 };
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+// Weights are read once: keep them out of L1.
+__device__ __forceinline__ uint4 ld16_stream(const __nv_bfloat16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float g) {
+    const float c = 0.7978845608028654f;
+    return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+}
+
+// NT: activation tiles of 8 rows; MT: weight tiles of 16 rows per block.
+template <int NT, int MT, typename OutT, int EPI>
+__global__ void __launch_bounds__(256)
+skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                     OutT* __restrict__ y, int R, int N, int K, int x_stride, int y_stride,
+                     float cap) {
+    extern __shared__ float red[];  // [8 warps][MT][NT][32 lanes][4]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * (16 * MT);
+
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[m][j][c] = 0.f;
+
+    const __nv_bfloat16* wrow[MT][2];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        wrow[m][0] = W + (size_t)min(n0 + 16 * m + g, N - 1) * K;
+        wrow[m][1] = W + (size_t)min(n0 + 16 * m + g + 8, N - 1) * K;
+    }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    for (int kb = warp * 64; kb < K; kb += 8 * 64) {
+        const int k = kb + 16 * t;
+        const bool v0 = k + 8 <= K, v1 = k + 16 <= K;  // K is a multiple of 8
+        uint4 wa[MT][2], wb[MT][2];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            wa[m][0] = v0 ? ld16_stream(wrow[m][0] + k) : zero;
+            wa[m][1] = v1 ? ld16_stream(wrow[m][0] + k + 8) : zero;
+            wb[m][0] = v0 ? ld16_stream(wrow[m][1] + k) : zero;
+            wb[m][1] = v1 ? ld16_stream(wrow[m][1] + k + 8) : zero;
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int r = 8 * j + g;
+            uint4 x0 = zero, x1 = zero;
+            if (r < R) {
+                const __nv_bfloat16* xp = x + (size_t)r * x_stride + k;
+                if (v0) x0 = ld16(xp);
+                if (v1) x1 = ld16(xp + 8);
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                mma_bf16_16816(acc[m][j], wa[m][0].x, wb[m][0].x, wa[m][0].y, wb[m][0].y, x0.x, x0.y);
+                mma_bf16_16816(acc[m][j], wa[m][0].z, wb[m][0].z, wa[m][0].w, wb[m][0].w, x0.z, x0.w);
+                mma_bf16_16816(acc[m][j], wa[m][1].x, wb[m][1].x, wa[m][1].y, wb[m][1].y, x1.x, x1.y);
+                mma_bf16_16816(acc[m][j], wa[m][1].z, wb[m][1].z, wa[m][1].w, wb[m][1].w, x1.z, x1.w);
+            }
+        }
+    }
+
+    // partial sums of the 8 warps, added in warp order
+    float4* mine = reinterpret_cast<float4*>(red) + (size_t)warp * (MT * NT * 32);
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+            mine[(m * NT + j) * 32 + lane] =
+                make_float4(acc[m][j][0], acc[m][j][1], acc[m][j][2], acc[m][j][3]);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < MT * NT * 32; idx += blockDim.x) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float4 v = reinterpret_cast<const float4*>(red)[(size_t)w * (MT * NT * 32) + idx];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const int l2 = idx & 31, j = (idx >> 5) % NT, m = idx / (32 * NT);
+        const int gg = l2 >> 2, tt = l2 & 3;
+        const int n_lo = n0 + 16 * m + gg;          // s.x, s.y; n_lo + 8: s.z, s.w
+        const int r0 = 8 * j + 2 * tt;              // s.x, s.z; r0 + 1: s.y, s.w
+        if (EPI == EPI_GEGLU) {
+            // rows gg (gate) and gg + 8 (up) of the 16-row group make column n_out
+            const int n_out = (n0 + 16 * m) / 2 + gg;
+            if (n_lo + 8 < N) {
+                if (r0 < R) y[(size_t)r0 * y_stride + n_out] = from_f32<OutT>(gelu_tanh_f(s.x) * s.z);
+                if (r0 + 1 < R)
+                    y[(size_t)(r0 + 1) * y_stride + n_out] = from_f32<OutT>(gelu_tanh_f(s.y) * s.w);
+            }
+        } else {
+            float o[4] = {s.x, s.y, s.z, s.w};
+            if (EPI == EPI_SOFTCAP) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[c] = cap * tanhf(o[c] / cap);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int n = n_lo + (c >= 2 ? 8 : 0), r = r0 + (c & 1);
+                if (n < N && r < R) y[(size_t)r * y_stride + n] = from_f32<OutT>(o[c]);
+            }
+        }
+    }
+}
+
+template <int NT, int MT, typename OutT, int EPI>
+static int launch_skinny(const void* W, const void* x, void* y, int R, int N, int K, int x_stride,
+                         int y_stride, float cap, cudaStream_t s) {
+    const size_t smem = (size_t)8 * MT * NT * 32 * 4 * sizeof(float);
+    auto kernel = skinny_linear_kernel<NT, MT, OutT, EPI>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) {
+            sib_set_error("skinny_linear: shared memory: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
+    const int blocks = (N + 16 * MT - 1) / (16 * MT);
+    kernel<<<blocks, 256, smem, s>>>((const __nv_bfloat16*)W, (const __nv_bfloat16*)x, (OutT*)y, R,
+                                     N, K, x_stride, y_stride, cap);
+    return sib_check_launch("skinny_linear");
+}
+
+template <typename OutT, int EPI>
+static int dispatch_skinny(const void* W, const void* x, void* y, int R, int N, int K,
+                           int x_stride, int y_stride, float cap, cudaStream_t s) {
+    if (R <= 8) return launch_skinny<1, 1, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
+    if (R <= 16) return launch_skinny<2, 1, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
+    if (R <= 32) return launch_skinny<4, 2, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
+    return launch_skinny<8, 2, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
+}
+
+// The largest R this kernel takes.
+SIB_EXPORT int sib_skinny_linear_max_rows() { return 64; }
+
+SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_dtype, int R, int N,
+                                 int K, int x_stride, int y_stride, int epilogue, float cap,
+                                 void* stream) {
+    if (R == 0) return 0;
+    SIB_REQUIRE(R > 0 && R <= 64, "skinny_linear: %d rows; this kernel takes 1 to 64", R);
+    SIB_REQUIRE(N > 0 && K > 0 && K % 8 == 0,
+                "skinny_linear: N=%d K=%d; K must be a multiple of 8", N, K);
+    SIB_REQUIRE(x_stride % 8 == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)x % 16) == 0,
+                "skinny_linear: operands must be 16-byte aligned (x_stride=%d)", x_stride);
+    SIB_REQUIRE(epilogue != EPI_GEGLU || N % 16 == 0,
+                "skinny_linear: the gated epilogue needs N (%d) in whole groups of 16", N);
+    SIB_REQUIRE(epilogue != EPI_SOFTCAP || cap > 0.f, "skinny_linear: soft cap must be positive");
+    cudaStream_t s = (cudaStream_t)stream;
+#define GO(OUT, EPI) return dispatch_skinny<OUT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s)
+    if (out_dtype == SIB_BF16) {
+        if (epilogue == EPI_NONE) GO(__nv_bfloat16, EPI_NONE);
+        if (epilogue == EPI_GEGLU) GO(__nv_bfloat16, EPI_GEGLU);
+        if (epilogue == EPI_SOFTCAP) GO(__nv_bfloat16, EPI_SOFTCAP);
+    } else if (out_dtype == SIB_F32) {
+        if (epilogue == EPI_NONE) GO(float, EPI_NONE);
+        if (epilogue == EPI_SOFTCAP) GO(float, EPI_SOFTCAP);
+        if (epilogue == EPI_GEGLU) GO(float, EPI_GEGLU);
+    }
+#undef GO
+    SIB_REQUIRE(false, "skinny_linear: unknown output type %d or epilogue %d", out_dtype, epilogue);
+}

@@ -1,0 +1,159 @@
+"""The generation loop: batches of unequal prompts, stop tokens, sequences
+that end earlier, one batch after another until every request is served.
+
+Per sequence the decisions are the reference's, in its order
+(src/engine/generate.rs:655-778):
+
+* an empty prompt and a prompt of ``max_seq_len`` tokens or more are errors;
+* the whole prompt is one step; its last row's logits give the first token;
+* then, up to ``max_tokens`` times: a stop token ends the sequence and is
+  not emitted ("eos"); otherwise the token is emitted and streamed; a
+  callback that returns False ends it ("cancelled", the token is kept); a
+  full context ends it ("context_length", the token is kept but never fed);
+  otherwise the token is fed as a one-token step and the next one sampled;
+* running out of ``max_tokens`` ends it ("max_tokens").
+
+A batch's requests start together; a finished sequence leaves the batch and
+gives its slot back at once; the next batch starts when the current one is
+done.  The loop talks to the model through a small *stepper* (prefill,
+decode, slots), so its decisions can be tested without a device.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling.sampler import SamplingConfig
+
+STOP_TOKEN = "eos"
+MAX_TOKENS = "max_tokens"
+CONTEXT_LENGTH = "context_length"
+CANCELLED = "cancelled"
+
+
+class GenerationError(ValueError):
+    pass
+
+
+@dataclass
+class GenerationConfig:
+    """src/engine/generate.rs:86-104.  ``max_tokens`` < 0: until a stop token or the context's end."""
+
+    max_tokens: int = 256
+    stop_tokens: Sequence[int] = ()
+    sampling: SamplingConfig = field(default_factory=SamplingConfig)
+
+
+@dataclass
+class GenerationOutput:
+    """src/engine/generate.rs:73-83, plus the time spent decoding."""
+
+    token_ids: List[int]
+    stop_reason: str
+    prompt_tokens: int
+    prefill_duration: float
+    decode_duration: float = 0.0
+
+
+def _round_up(n: int, unit: int) -> int:
+    return -(-n // unit) * unit
+
+
+def plan_batch(lengths: Sequence[int], max_tokens: int, max_seq_len: int, page_tokens: int,
+               capacity_tokens: int, free_slots: int) -> int:
+    """How many of the waiting requests (in order) start together: as many as
+    the cache can hold to their ends.  At least one, or an error."""
+    used, n = 0, 0
+    for length in lengths:
+        end = max_seq_len if max_tokens < 0 else min(length + max_tokens, max_seq_len)
+        need = _round_up(max(end, length), page_tokens)
+        if n >= free_slots or used + need > capacity_tokens:
+            break
+        used += need
+        n += 1
+    if n == 0:
+        raise GenerationError(
+            f"a request of {lengths[0]} prompt tokens and up to "
+            f"{'the context end' if max_tokens < 0 else max_tokens} new tokens does not fit "
+            f"the cache ({capacity_tokens} positions, {free_slots} free slots)")
+    return n
+
+
+def generate(stepper, prompts: Sequence[Sequence[int]], config: GenerationConfig,
+             callback: Optional[Callable[[int, int], bool]] = None,
+             seeds: Optional[Sequence[int]] = None) -> List[GenerationOutput]:
+    """Generate for every prompt.  ``callback(request_index, token)`` is called
+    for every emitted token; returning False cancels that request.  Every
+    request draws from its own generator, seeded with ``seeds[i]`` if given,
+    else with the configured seed: a request samples the same tokens alone or
+    in any batch."""
+    if not prompts:
+        return []
+    max_seq_len = stepper.max_seq_len
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise GenerationError(f"request {i}: empty prompt")
+        if len(p) >= max_seq_len:
+            raise GenerationError(f"request {i}: prompt length ({len(p)}) exceeds "
+                                  f"max_seq_len ({max_seq_len})")
+    if seeds is not None and len(seeds) != len(prompts):
+        raise GenerationError("'seeds' needs one seed per prompt")
+    stops = set(int(t) for t in config.stop_tokens) | set(stepper.default_stop_tokens)
+    limit = config.max_tokens
+    results: List[Optional[GenerationOutput]] = [None] * len(prompts)
+    waiting = list(range(len(prompts)))
+
+    while waiting:
+        n = plan_batch([len(prompts[i]) for i in waiting], limit, max_seq_len,
+                       stepper.page_tokens, stepper.capacity_tokens, stepper.free_slots)
+        batch, waiting = waiting[:n], waiting[n:]
+        held = set()
+        live = []
+        try:
+            slots = []
+            for _ in batch:
+                slots.append(stepper.new_sequence())
+                held.add(slots[-1])
+            for i, s in zip(batch, slots):
+                stepper.seed(s, seeds[i] if seeds is not None else config.sampling.seed_value())
+            t0 = time.perf_counter()
+            nxt = stepper.prefill(slots, [prompts[i] for i in batch], config.sampling)
+            prefill_s = time.perf_counter() - t0
+            for i, s, t in zip(batch, slots, nxt):
+                results[i] = GenerationOutput([], MAX_TOKENS, len(prompts[i]), prefill_s)
+                live.append((i, s, int(t)))
+            t_decode = time.perf_counter()
+            while live:
+                going = []
+                for i, s, tok in live:
+                    out = results[i]
+                    reason = None
+                    if limit >= 0 and len(out.token_ids) >= limit:
+                        reason = MAX_TOKENS
+                    elif tok in stops:
+                        reason = STOP_TOKEN
+                    else:
+                        out.token_ids.append(tok)
+                        if callback is not None and not callback(i, tok):
+                            reason = CANCELLED
+                        elif stepper.length(s) >= max_seq_len:
+                            reason = CONTEXT_LENGTH
+                    if reason is None:
+                        going.append((i, s, tok))
+                    else:
+                        out.stop_reason = reason
+                        out.decode_duration = time.perf_counter() - t_decode
+                        held.discard(s)
+                        stepper.end_sequence(s)
+                live = []
+                if going:
+                    nxt = stepper.decode([s for _, s, _ in going], [t for _, _, t in going],
+                                         config.sampling)
+                    live = [(i, s, int(t)) for (i, s, _), t in zip(going, nxt)]
+        except BaseException:
+            for s in held:      # give back what the failed batch still holds
+                stepper.end_sequence(s)
+            raise
+    return results  # type: ignore[return-value]

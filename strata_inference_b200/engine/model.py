@@ -1,0 +1,122 @@
+"""The decoder, assembled from a ModelSpec: embedding, blocks run in the
+order the schedule gives, final norm and head on the wanted rows.
+
+Nothing here names an architecture.  The reference's counterpart is one
+function with per-architecture branches (src/model/layer.rs:1255-1392).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional
+
+import torch
+
+from ..cache.paged import CacheNeed
+from ..config.spec import ModelSpec, PartSpec
+from ..parts import registry as parts
+from ..weights.loader import TensorDecl
+
+
+def _sub(weights: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
+    return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
+
+
+def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
+    """Every tensor the model needs, by full name, from the parts' declarations."""
+    H, V = spec.hidden_size, spec.vocab_size
+    out: Dict[str, TensorDecl] = {}
+
+    def add(prefix: str, decls: Mapping[str, TensorDecl]) -> None:
+        for name, d in decls.items():
+            out[prefix + name] = d
+
+    add(spec.names["embedding"],
+        parts.part_class("embedding", spec.embedding.kind).tensors(spec.embedding.params, H, V))
+    for layer in spec.layers:
+        add(layer.prefix + layer.names["mixer"],
+            parts.part_class("mixer", layer.mixer.kind).tensors(layer.mixer.params, H))
+        add(layer.prefix + layer.names["feed_forward"],
+            parts.part_class("feed_forward", layer.feed_forward.kind).tensors(
+                layer.feed_forward.params, H))
+        for site, norm in layer.norms.items():
+            add(layer.prefix + layer.names[site],
+                parts.part_class("norm", norm.kind).tensors(norm.params, H))
+    add(spec.names["final_norm"],
+        parts.part_class("norm", spec.final_norm.kind).tensors(spec.final_norm.params, H))
+    add(spec.names["head"],
+        parts.part_class("head", spec.head.kind).tensors(spec.head.params, H, V))
+    return out
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, weights: Mapping[str, torch.Tensor], rt):
+        spec.validate()
+        self.spec = spec
+        self.rt = rt
+        H, V = spec.hidden_size, spec.vocab_size
+        self.embedding = parts.part_class("embedding", spec.embedding.kind)(
+            spec.embedding.params, H, V, _sub(weights, spec.names["embedding"]), rt)
+        self.blocks = []
+        for layer in spec.layers:
+            mixer = parts.part_class("mixer", layer.mixer.kind)(
+                layer.mixer.params, H, _sub(weights, layer.prefix + layer.names["mixer"]), rt)
+            ff = parts.part_class("feed_forward", layer.feed_forward.kind)(
+                layer.feed_forward.params, H,
+                _sub(weights, layer.prefix + layer.names["feed_forward"]), rt)
+            norms = {site: parts.part_class("norm", n.kind)(
+                n.params, H, _sub(weights, layer.prefix + layer.names[site]), rt)
+                for site, n in layer.norms.items()}
+            self.blocks.append(parts.part_class("block", layer.block)(mixer, ff, norms, rt))
+        self.final_norm = parts.part_class("norm", spec.final_norm.kind)(
+            spec.final_norm.params, H, _sub(weights, spec.names["final_norm"]), rt)
+        self.head = parts.part_class("head", spec.head.kind)(
+            spec.head.params, H, V, _sub(weights, spec.names["head"]), rt, self.embedding)
+
+    def cache_needs(self) -> List[Optional[CacheNeed]]:
+        """One entry per schedule position; None where the run borrows a cache."""
+        needs: List[Optional[CacheNeed]] = []
+        for e in self.spec.schedule:
+            needs.append(None if e.cache_of is not None
+                         else self.blocks[e.layer].mixer.cache_need())
+        return needs
+
+    def hidden_states(self, ctx) -> torch.Tensor:
+        """Run every schedule entry over the step's rows; returns the 32-bit
+        residual stream [rows, hidden]."""
+        h = self.embedding.forward(ctx.tokens)
+        schedule = self.spec.schedule
+        normed = None
+        for pos, e in enumerate(schedule):
+            block = self.blocks[e.layer]
+            nxt = self.blocks[schedule[pos + 1].layer].first_norm if pos + 1 < len(schedule) else None
+            cache_entry = pos if e.cache_of is None else e.cache_of
+            normed = block.forward(h, normed, ctx, pos, cache_entry, e.cache_of is None, nxt)
+        return h
+
+    def logits(self, h: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """32-bit logits [len(rows), vocab] of the chosen rows of h."""
+        y = self.final_norm.forward(h, out_dtype=self.rt.dtype, rows=rows)
+        return self.head.forward(y)
+
+    def weight_bytes(self) -> int:
+        """Bytes of every distinct weight tensor a step reads."""
+        seen, total = set(), 0
+
+        def visit(obj):
+            nonlocal total
+            for v in vars(obj).values():
+                if isinstance(v, torch.Tensor) and v.is_cuda:
+                    key = v.untyped_storage().data_ptr()
+                    if key not in seen:
+                        seen.add(key)
+                        total += v.untyped_storage().nbytes()
+                elif hasattr(v, "__dict__") and not isinstance(v, (type, torch.device)) \
+                        and v is not self.rt and id(v) not in seen:
+                    seen.add(id(v))
+                    visit(v)
+        visit(self.embedding)
+        for b in self.blocks:
+            visit(b)
+        visit(self.final_norm)
+        visit(self.head)
+        return total

@@ -1,0 +1,282 @@
+"""The compiled sm_100a kernels, called with torch tensors.
+
+The library is plain C (``csrc/*.cu``), loaded with ctypes; each wrapper
+checks types and layouts, passes raw device pointers and the current
+stream, and raises :class:`KernelError` with the library's message when a
+launcher refuses its arguments.  There is no other implementation behind
+these functions: without the compiled library, or on a device that is not
+sm_100, they raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+F32, BF16 = 0, 1
+EPI_NONE, EPI_SOFTCAP, EPI_GEGLU = 0, 1, 2
+ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library():
+    """Load (compiling first if needed) the kernel library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    from ..csrc.build import ensure_built
+    path = ensure_built()
+    lib = ctypes.CDLL(path)
+    lib.sib_last_error.restype = ctypes.c_char_p
+    lib.sib_attention_rows_scratch_bytes.restype = c_longlong
+    if lib.sib_compiled_arch() != 100:
+        raise KernelError(f"{path} was not compiled for sm_100a")
+    _lib = lib
+    return lib
+
+
+def require_device(device: torch.device) -> None:
+    """Fail loudly unless ``device`` is a CUDA device of compute capability 10.x."""
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise KernelError("strata_inference_b200 runs on an sm_100 CUDA device only; "
+                          f"got device '{device}' (there is no CPU path)")
+    major, minor = torch.cuda.get_device_capability(device)
+    if major != 10:
+        raise KernelError(f"strata_inference_b200 is compiled for sm_100a; device '{device}' "
+                          f"has compute capability {major}.{minor}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {dtype} is not supported (float32 and bfloat16 are)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many launcher calls of this library succeeded so far in this process
+    (a launcher that merges split partial results launches two kernels and counts once)."""
+    return _launches
+
+
+def _check(rc: int) -> None:
+    global _launches
+    if rc != 0:
+        raise KernelError(library().sib_last_error().decode())
+    _launches += 1
+
+
+def _want(t: torch.Tensor, dtype: torch.dtype, name: str, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor")
+    if t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name}: expected a contiguous tensor")
+
+
+# --------------------------------------------------------------------------
+
+def embed_rows(tokens: torch.Tensor, table: torch.Tensor, scale: float,
+               out: torch.Tensor) -> torch.Tensor:
+    """out[r] = scale * table[tokens[r]] in 32-bit."""
+    _want(tokens, torch.int32, "tokens")
+    _want(out, torch.float32, "out")
+    rows, hidden = out.shape
+    if tokens.numel() != rows or table.shape[1] != hidden or not table.is_contiguous():
+        raise KernelError("embed_rows: shapes do not fit")
+    _check(library().sib_embed_rows(_ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out),
+                                    c_int(rows), c_int(hidden), c_float(scale), _stream()))
+    return out
+
+
+def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.Tensor:
+    """out[r, i] = gelu_tanh(gate(r, i)) * up(r, i); gate_up rows are [gates | ups]
+    (group 0) or groups of ``group`` gates followed by their ups."""
+    rows, inter = out.shape
+    _want(gate_up, out.dtype, "gate_up")
+    _want(out, out.dtype, "out")
+    if tuple(gate_up.shape) != (rows, 2 * inter):
+        raise KernelError("gelu_mul: gate_up must be [rows, 2 * intermediate]")
+    _check(library().sib_gelu_mul(_ptr(gate_up), _ptr(out), _code(out.dtype), c_int(rows),
+                                  c_int(inter), c_int(group), _stream()))
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place (32-bit)."""
+    _want(x, torch.float32, "x")
+    _check(library().sib_softcap(_ptr(x), c_longlong(x.numel()), c_float(cap), _stream()))
+    return x
+
+
+def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = rms(x[rows[i] if rows else i]) * gain; statistics in 32-bit."""
+    _want(gain, torch.float32, "gain")
+    _want(x, x.dtype, "x")
+    _want(out, out.dtype, "out")
+    n, hidden = out.shape
+    if x.shape[1] != hidden or gain.numel() != hidden:
+        raise KernelError("rms_norm: shapes do not fit")
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+        if rows.numel() != n:
+            raise KernelError("rms_norm: one row index per output row")
+    elif x.shape[0] != n:
+        raise KernelError("rms_norm: x and out differ in rows")
+    _check(library().sib_rms_norm(_ptr(x), _code(x.dtype), _ptr(rows), _ptr(gain), c_float(eps),
+                                  _ptr(out), _code(out.dtype), c_int(n), c_int(hidden), _stream()))
+    return out
+
+
+def add_rms_norm(a: torch.Tensor, post_gain: Optional[torch.Tensor], post_eps: float,
+                 h: torch.Tensor, pre_gain: Optional[torch.Tensor], pre_eps: float,
+                 out: Optional[torch.Tensor]) -> None:
+    """h += rms(a) * post_gain (or a when post_gain is None); out = rms(h) * pre_gain."""
+    _want(h, torch.float32, "h")
+    _want(a, a.dtype, "a")
+    rows, hidden = h.shape
+    if tuple(a.shape) != (rows, hidden):
+        raise KernelError("add_rms_norm: a and h differ in shape")
+    for g, nm in ((post_gain, "post_gain"), (pre_gain, "pre_gain")):
+        if g is not None:
+            _want(g, torch.float32, nm)
+            if g.numel() != hidden:
+                raise KernelError(f"add_rms_norm: {nm} has the wrong length")
+    if pre_gain is not None:
+        if out is None:
+            raise KernelError("add_rms_norm: pre_gain needs out")
+        _want(out, a.dtype, "out")
+    _check(library().sib_add_rms_norm(_ptr(a), _code(a.dtype), _ptr(post_gain), c_float(post_eps),
+                                      _ptr(h), _ptr(pre_gain), c_float(pre_eps), _ptr(out),
+                                      c_int(rows), c_int(hidden), _stream()))
+
+
+def rope_store(qkv: torch.Tensor, row_pos, row_seq, seq_slot, seq_end,
+               inv_freq: Optional[torch.Tensor], rotary_dim: int, style: int,
+               k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+               page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int,
+               n_heads: int, n_kv: int, head_dim: int) -> None:
+    """Rotate q and k of the packed rows in place and write k, v into the paged cache."""
+    _want(qkv, qkv.dtype, "qkv")
+    rows = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("rope_store: qkv width does not fit the head counts")
+    if inv_freq is not None:
+        _want(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError("rope_store: one frequency per rotated pair")
+    max_pages = 0
+    if k_pool is not None:
+        _want(k_pool, qkv.dtype, "k_pool")
+        _want(v_pool, qkv.dtype, "v_pool")
+        _want(page_table, torch.int32, "page_table")
+        max_pages = page_table.shape[1]
+        if tuple(k_pool.shape[1:]) != (n_kv, page_tokens, head_dim):
+            raise KernelError("rope_store: pool layout must be [pages, kv_heads, page_tokens, head_dim]")
+    _check(library().sib_rope_store(
+        _ptr(qkv), _code(qkv.dtype), _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(seq_end),
+        _ptr(inv_freq), c_int(rotary_dim), c_int(style), _ptr(k_pool), _ptr(v_pool),
+        _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens), c_int(rows),
+        c_int(n_heads), c_int(n_kv), c_int(head_dim), _stream()))
+
+
+def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits: int) -> int:
+    return int(library().sib_attention_rows_scratch_bytes(c_int(rows), c_int(n_heads),
+                                                          c_int(head_dim), c_int(splits)))
+
+
+def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor],
+                   v_new: Optional[torch.Tensor], kv_stride: int,
+                   k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                   page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int,
+                   row_pos, row_seq, seq_slot, seq_start, seq_row0, out: torch.Tensor,
+                   scratch: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
+                   scale: float, softcap: float, window: int, splits: int) -> torch.Tensor:
+    """General attention of independent rows (see csrc/attention_rows.cu).
+
+    ``q``, ``k_new``, ``v_new`` may be views into one packed buffer; only
+    their first elements' addresses and the strides are used."""
+    rows = out.shape[0]
+    _want(out, out.dtype, "out")
+    if q.dtype != out.dtype:
+        raise KernelError("attention_rows: q and out differ in type")
+    max_pages = page_table.shape[1] if page_table is not None else 0
+    if k_pool is not None and tuple(k_pool.shape[1:]) != (n_kv, page_tokens, head_dim):
+        raise KernelError("attention_rows: pool layout must be [pages, kv_heads, page_tokens, head_dim]")
+    if splits > 1:
+        need = attention_rows_scratch_bytes(rows, n_heads, head_dim, splits)
+        if scratch is None or scratch.numel() * scratch.element_size() < need:
+            raise KernelError(f"attention_rows: {need} bytes of scratch memory are needed")
+    _check(library().sib_attention_rows(
+        _ptr(q), c_int(q_stride), _ptr(k_new), _ptr(v_new), c_int(kv_stride), _ptr(k_pool),
+        _ptr(v_pool), _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens),
+        _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_row0), _ptr(out),
+        _ptr(scratch), _code(out.dtype), c_int(rows), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+        c_float(scale), c_float(softcap), c_int(window), c_int(splits), _stream()))
+    return out
+
+
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+                  cap: float = 0.0) -> torch.Tensor:
+    """out = x . w^T for at most 64 rows of bfloat16 x (see csrc/linear_skinny.cu)."""
+    _want(x, torch.bfloat16, "x", contiguous=False)
+    _want(w, torch.bfloat16, "w")
+    _want(out, out.dtype, "out", contiguous=False)
+    R, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("skinny_linear: shapes do not fit")
+    _check(library().sib_skinny_linear(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
+                                       c_int(N), c_int(K), c_int(x.stride(0)),
+                                       c_int(out.stride(0)), c_int(epilogue), c_float(cap),
+                                       _stream()))
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
+                rng_state: Optional[torch.Tensor], out: torch.Tensor,
+                rng_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of 32-bit logits; advances each row's generator by one draw.
+    ``rng_index[row]`` (int32) says which element of ``rng_state`` a row uses."""
+    _want(logits, torch.float32, "logits", contiguous=False)
+    _want(out, torch.int32, "out")
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1 or out.numel() != rows:
+        raise KernelError("sample_rows: shapes do not fit")
+    if rng_state is not None:
+        _want(rng_state, torch.int64, "rng_state")
+        if rng_index is None and rng_state.numel() != rows:
+            raise KernelError("sample_rows: one generator state per row")
+        if rng_index is not None:
+            _want(rng_index, torch.int32, "rng_index")
+    _check(library().sib_sample_rows(_ptr(logits), c_longlong(logits.stride(0)), c_int(rows),
+                                     c_int(vocab), c_float(temperature), c_int(top_k),
+                                     c_float(top_p), _ptr(rng_state), _ptr(rng_index), _ptr(out),
+                                     _stream()))
+    return out

@@ -1,0 +1,135 @@
+"""The attention mixer: grouped-query attention over the paged cache.
+
+Parameters (all from the PartSpec): ``num_heads``, ``num_kv_heads``,
+``head_dim`` (heads x head_dim need not equal the hidden size),
+``score_scale`` (the factor on q.k), ``logit_softcap`` (0: off), ``window``
+(0: every earlier key is visible; W: the last W keys, the query's own
+included) and ``position`` (a PartSpec of a position encoding).
+
+Order of operations, as in the reference (src/model/layer.rs:1113-1161,
+872-984): q, k, v projections (no bias); rotation of q and k; k and v
+appended to the cache at the rows' positions; scores scaled, soft-capped,
+masked; softmax; weighted sum of v; output projection.
+
+A step whose sequences all begin at position 0 (prompts) attends over the
+step's own k and v rows; any other step attends over the cache.  A run that
+borrows another schedule entry's cache projects q only and reads that cache.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache.paged import CacheNeed, KVNeed
+from ..config.spec import ConfigError, PartSpec
+from ..kernels import native
+from ..weights.loader import TensorDecl
+from .registry import part_class, register_mixer
+
+_TARGET_WARPS = 148 * 16
+
+
+class Attention:
+    @staticmethod
+    def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        nh, nkv, hd = params["num_heads"], params["num_kv_heads"], params["head_dim"]
+        out = {
+            "q_proj.weight": TensorDecl((nh * hd, hidden)),
+            "k_proj.weight": TensorDecl((nkv * hd, hidden)),
+            "v_proj.weight": TensorDecl((nkv * hd, hidden)),
+            "o_proj.weight": TensorDecl((hidden, nh * hd)),
+        }
+        pos: PartSpec = params["position"]
+        for name, decl in part_class("position", pos.kind).tensors(pos.params, hd).items():
+            out["position." + name] = decl
+        return out
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.hidden = hidden
+        self.nh = int(params["num_heads"])
+        self.nkv = int(params["num_kv_heads"])
+        self.hd = int(params["head_dim"])
+        self.scale = float(params["score_scale"])
+        self.softcap = float(params.get("logit_softcap") or 0.0)
+        self.window = int(params.get("window") or 0)
+        if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
+            raise ConfigError(f"attention: {self.nh} heads cannot share {self.nkv} kv heads")
+        if self.hd % 16 or not 16 <= self.hd <= 512:
+            raise ConfigError(f"attention: head_dim {self.hd} must be a multiple of 16 "
+                              f"between 16 and 512")
+        pos: PartSpec = params["position"]
+        pos_w = {k[len("position."):]: v for k, v in weights.items() if k.startswith("position.")}
+        self.position = part_class("position", pos.kind)(pos.params, self.hd, pos_w, rt)
+        self.w_qkv = rt.cast_matrix(torch.cat(
+            [weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0))
+        self.w_q = self.w_qkv[: self.nh * self.hd]
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
+
+    # ------------------------------------------------------------------
+    def _splits(self, ctx, capacity: int) -> int:
+        """How many runs of keys each (row, head) is cut into when it reads the cache."""
+        longest = capacity if ctx.graph_capture else ctx.max_end
+        if self.window > 0:
+            longest = min(longest, self.window)
+        units = max(1, ctx.n_rows * self.nh)
+        want = -(-_TARGET_WARPS // units)
+        return max(1, min(want, -(-longest // 32), 128))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        rt, nh, hd = self.rt, self.nh, self.hd
+        R = x.shape[0]
+        nkv = self.nkv if owns_cache else 0
+        qkv = rt.linear(x, self.w_qkv if owns_cache else self.w_q)
+        view = ctx.kv(cache_entry)
+        fresh = ctx.all_from_start and owns_cache
+        if not fresh and not ctx.all_from_start and view.ring_tokens > 0 and \
+                ctx.max_count > view.ring_tokens - self.window + 1:
+            raise ValueError(f"a step that continues sequences may add at most "
+                             f"{view.ring_tokens - self.window + 1} positions to a sequence "
+                             f"whose layers keep a window of {self.window}; got {ctx.max_count}")
+        if not fresh and ctx.all_from_start and view.ring_tokens > 0 and \
+                ctx.max_end > view.ring_tokens:
+            raise ValueError("a run that borrows a windowed cache cannot take prompts longer "
+                             "than what that cache keeps")
+
+        if hasattr(self.position, "rotary"):
+            inv_freq, rot, style = self.position.rotary()
+        else:
+            q_view = qkv[:, : nh * hd].view(R, nh, hd)
+            k_view = qkv[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd) if nkv else None
+            self.position.apply(q_view, k_view, ctx)
+            inv_freq, rot, style = None, 0, native.ROPE_HALF_SPLIT
+        native.rope_store(qkv, ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end, inv_freq, rot,
+                          style, view.k if owns_cache else None, view.v if owns_cache else None,
+                          view.page_table if owns_cache else None, view.page_tokens,
+                          view.ring_tokens, nh, nkv, hd)
+
+        out = torch.empty((R, nh * hd), dtype=qkv.dtype, device=qkv.device)
+        width = qkv.shape[1]
+        if fresh:
+            k_new = qkv[:, nh * hd:]
+            v_new = qkv[:, (nh + nkv) * hd:]
+            native.attention_rows(qkv, width, k_new, v_new, width, None, None, None,
+                                  view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
+                                  ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, None, nh,
+                                  self.nkv, hd, self.scale, self.softcap, self.window, 1)
+        else:
+            splits = self._splits(ctx, ctx.cache.max_seq_len)
+            scratch = None
+            if splits > 1:
+                scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, hd, splits))
+            native.attention_rows(qkv, width, None, None, width, view.k, view.v, view.page_table,
+                                  view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
+                                  ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, scratch, nh,
+                                  self.nkv, hd, self.scale, self.softcap, self.window, splits)
+        return rt.linear(out, self.w_o)
+
+
+register_mixer("attention", Attention)

@@ -1,0 +1,69 @@
+"""The dense gated feed-forward: down(act(gate(x)) * up(x)), no biases.
+
+Reference: src/model/layer.rs:696-710 (two products, the gated activation,
+the down product), src/backend/cpu.rs:1190-1199 (tanh-GELU).  The gate and up
+matrices are kept as ONE matrix so that one product makes both halves; when
+the intermediate size allows it their rows are interleaved in groups of 8
+(8 gate rows, then the 8 matching up rows), which puts a gate value and its
+up value into the same thread of the weight-streaming kernel, whose epilogue
+then writes act(gate) * up directly.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from ..config.spec import ConfigError
+from ..kernels import native
+from ..weights.loader import TensorDecl
+from .registry import register_feed_forward
+
+_ACTIVATIONS = ("gelu_pytorch_tanh",)
+_GROUP = 8
+
+
+class GatedMLP:
+    @staticmethod
+    def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        inter = params["intermediate_size"]
+        return {
+            "gate_proj.weight": TensorDecl((inter, hidden)),
+            "up_proj.weight": TensorDecl((inter, hidden)),
+            "down_proj.weight": TensorDecl((hidden, inter)),
+        }
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.inter = int(params["intermediate_size"])
+        act = params.get("activation", _ACTIVATIONS[0])
+        if act not in _ACTIVATIONS:
+            raise ConfigError(f"gated_mlp: activation {act!r} is not supported; "
+                              f"known: {', '.join(_ACTIVATIONS)}")
+        gate, up = weights["gate_proj.weight"], weights["up_proj.weight"]
+        if self.inter % _GROUP == 0:
+            self.group = _GROUP
+            g = gate.view(self.inter // _GROUP, _GROUP, hidden)
+            u = up.view(self.inter // _GROUP, _GROUP, hidden)
+            fused = torch.cat([g, u], dim=1).reshape(2 * self.inter, hidden)
+        else:
+            self.group = 0
+            fused = torch.cat([gate, up], dim=0)
+        self.w_gate_up = rt.cast_matrix(fused)
+        self.w_down = rt.cast_matrix(weights["down_proj.weight"])
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        rt = self.rt
+        R = x.shape[0]
+        if (self.group == _GROUP and x.dtype == torch.bfloat16 and R <= rt.skinny_max_rows
+                and x.shape[1] % 8 == 0):
+            t = rt.linear(x, self.w_gate_up, epilogue=native.EPI_GEGLU)
+        else:
+            gate_up = rt.linear(x, self.w_gate_up)
+            t = torch.empty((R, self.inter), dtype=x.dtype, device=x.device)
+            native.gelu_mul(gate_up, t, self.group)
+        return rt.linear(t, self.w_down)
+
+
+register_feed_forward("gated_mlp", GatedMLP)

@@ -1,0 +1,206 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16:
+each request alone and whole; with its last 32 tokens one by one; in batches
+of unequal lengths whose shorter requests end earlier, one batch after
+another so that slots are used again; long decoding; the first tokens."""
+
+import pytest
+import torch
+
+from helpers import (CONFIGS, assert_logits_close, make_model_dir, plain_logits, random_prompts)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+# (config, page size): the small page sizes make the window's ring wrap
+CASES = [("A", 64), ("A", 4), ("B", 64), ("B", 8), ("C", 16)]
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    out = {}
+    for i, (name, cfg) in enumerate(CONFIGS.items()):
+        out[name] = make_model_dir(str(tmp_path_factory.mktemp(f"tiny_{name}")), cfg, seed=10 + i)
+    return out
+
+
+def _engine(model_dirs, name, dtype, page_tokens, max_tokens=1024):
+    from strata_inference_b200 import Engine
+    return Engine.from_dir(model_dirs[name], dtype=dtype, max_tokens=max_tokens,
+                           page_tokens=page_tokens)
+
+
+def _lengths(cfg):
+    top = cfg["max_position_embeddings"]
+    return [top - 3, 40, top // 2 + 5]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page", CASES)
+def test_whole_prompt_each_request_alone(model_dirs, name, page, dtype):
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, page)
+    for r, toks in enumerate(random_prompts(cfg, _lengths(cfg), seed=1)):
+        ref = plain_logits(toks, model_dirs[name], cfg)
+        slot = eng.new_sequence()
+        got = eng.step([(slot, toks)], want=[list(range(len(toks)))])
+        eng.end_sequence(slot)
+        assert_logits_close(got, ref, dtype, f"{name} request {r} whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page", CASES)
+def test_last_32_tokens_one_by_one(model_dirs, name, page, dtype):
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, page)
+    for r, toks in enumerate(random_prompts(cfg, _lengths(cfg), seed=2)):
+        ref = plain_logits(toks, model_dirs[name], cfg)
+        cut = len(toks) - 32
+        slot = eng.new_sequence()
+        got = [eng.step([(slot, toks[:cut])], want=[[cut - 1]])]
+        for t in toks[cut:]:
+            got.append(eng.step([(slot, [t])]))
+        eng.end_sequence(slot)
+        got = torch.cat(got, dim=0)
+        assert_logits_close(got, ref[cut - 1:], dtype, f"{name} request {r} last 32 one by one")
+
+
+def _run_batch(eng, requests, prompt_lens, refs, dtype, tag):
+    """Prompts of unequal lengths in one step, then one given token each per
+    step; a request leaves (and frees its slot) when its tokens are used up."""
+    slots = [eng.new_sequence() for _ in requests]
+    entries = [(s, toks[:p]) for s, toks, p in zip(slots, requests, prompt_lens)]
+    want = [[0, p - 1] if p > 1 else [0] for p in prompt_lens]
+    got = eng.step(entries, want)
+    ref = torch.cat([refs[i][w] for i, w in enumerate(want)], dim=0)
+    assert_logits_close(got, ref, dtype, f"{tag} prompts")
+    pos = list(prompt_lens)
+    live = list(range(len(requests)))
+    step = 0
+    while live:
+        still = [i for i in live if pos[i] < len(requests[i])]
+        for i in live:
+            if i not in still:
+                eng.end_sequence(slots[i])
+        live = still
+        if not live:
+            break
+        got = eng.step([(slots[i], [requests[i][pos[i]]]) for i in live])
+        ref = torch.stack([refs[i][pos[i]] for i in live], dim=0)
+        assert_logits_close(got, ref, dtype, f"{tag} decode step {step} (requests {live})")
+        for i in live:
+            pos[i] += 1
+        step += 1
+    return slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page", CASES)
+def test_unequal_batches_one_after_another(model_dirs, name, page, dtype):
+    cfg = CONFIGS[name]
+    top = cfg["max_position_embeddings"]
+    eng = _engine(model_dirs, name, dtype, page, max_tokens=4 * ((top + 63) // 64) * 64)
+    total = [top - 1, 30, 45, 37, top - 10, 12, 50]
+    prompt = [20, 3, 33, 1, top - 30, 11, 9]
+    reqs = random_prompts(cfg, total, seed=3)
+    refs = [plain_logits(t, model_dirs[name], cfg) for t in reqs]
+    first = _run_batch(eng, reqs[:4], prompt[:4], refs[:4], dtype, f"{name} batch 1")
+    assert eng.cache.pages_in_use() == 0
+    second = _run_batch(eng, reqs[4:], prompt[4:], refs[4:], dtype, f"{name} batch 2")
+    assert set(second) & set(first), "the second batch should reuse slots of the first"
+    assert eng.cache.pages_in_use() == 0 and eng.cache.n_free_slots == eng.cache.max_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_dirs, dtype):
+    """A 2-token prompt, then every further token one by one up to the context's end."""
+    name, cfg = "C", CONFIGS["C"]
+    eng = _engine(model_dirs, name, dtype, 16)
+    toks = random_prompts(cfg, [cfg["max_position_embeddings"]], seed=4)[0]
+    ref = plain_logits(toks, model_dirs[name], cfg)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, toks[:2])], want=[[0, 1]])]
+    for t in toks[2:]:
+        got.append(eng.step([(slot, [t])]))
+    assert_logits_close(torch.cat(got, dim=0), ref, dtype, "C long decoding")
+    with pytest.raises(Exception):
+        eng.step([(slot, [1])])   # the context is full
+    eng.end_sequence(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens(model_dirs, name, dtype):
+    """Position 0 alone, then positions 1, 2, 3 one by one, and a one-token
+    prompt beside longer ones."""
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, 64)
+    toks = random_prompts(cfg, [4], seed=5)[0]
+    ref = plain_logits(toks, model_dirs[name], cfg)
+    slot = eng.new_sequence()
+    got = torch.cat([eng.step([(slot, [t])]) for t in toks], dim=0)
+    eng.end_sequence(slot)
+    assert_logits_close(got, ref, dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_far_key_and_window_edge(tmp_path, dtype):
+    """One early key made to stand out: a global layer must find it among all
+    keys, a sliding layer must lose it exactly when it leaves the window."""
+    from strata_inference_b200 import Engine
+    cfg = dict(CONFIGS["A"])
+    cfg["max_position_embeddings"] = 256
+    cfg["sliding_window"] = 24
+    d = make_model_dir(str(tmp_path / "m"), cfg, seed=21, sharpen=10.0)
+    toks = random_prompts(cfg, [200], seed=6)[0]
+    toks[5] = 77                      # a token that appears once, early
+    toks = [t if (t != 77 or i == 5) else 78 for i, t in enumerate(toks)]
+    ref = plain_logits(toks, d, cfg)
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=512, page_tokens=8)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, toks[:20])], want=[list(range(20))])]
+    for t in toks[20:]:
+        got.append(eng.step([(slot, [t])]))
+    eng.end_sequence(slot)
+    assert_logits_close(torch.cat(got, dim=0), ref, dtype, "far key / window edge")
+
+
+def test_padding_free_batch_is_independent_of_neighbours(model_dirs):
+    """The same request gives the same logits alone and beside others (32-bit)."""
+    name, cfg = "B", CONFIGS["B"]
+    eng = _engine(model_dirs, name, "float32", 8)
+    reqs = random_prompts(cfg, [17, 5, 29], seed=7)
+    alone = []
+    for t in reqs:
+        s = eng.new_sequence()
+        alone.append(eng.step([(s, t)]))
+        eng.end_sequence(s)
+    slots = [eng.new_sequence() for _ in reqs]
+    together = eng.step(list(zip(slots, reqs)))
+    for s in slots:
+        eng.end_sequence(s)
+    scale = torch.cat(alone).abs().max().item()
+    assert (together - torch.cat(alone)).abs().max().item() <= 1e-5 * scale
+
+
+def test_step_errors(model_dirs):
+    from strata_inference_b200.cache.paged import CacheError, CacheFull
+    name, cfg = "A", CONFIGS["A"]
+    eng = _engine(model_dirs, name, "float32", 64, max_tokens=128)
+    s = eng.new_sequence()
+    with pytest.raises(ValueError, match="exceeds vocab_size"):
+        eng.step([(s, [cfg["vocab_size"]])])
+    with pytest.raises(ValueError):
+        eng.step([(s, [])])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([(s, [1]), (s, [2])])
+    eng.step([(s, [1, 2, 3])])
+    s2 = eng.new_sequence()
+    with pytest.raises(CacheFull):
+        eng.step([(s2, list(range(100)))])      # 2 pages wanted, 1 free
+    assert eng.length(s2) == 0
+    eng.end_sequence(s)
+    eng.end_sequence(s2)
+    with pytest.raises(CacheError):
+        eng.end_sequence(s2)
+    with pytest.raises(CacheError):
+        eng.step([(s2, [1])])

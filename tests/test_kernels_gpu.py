@@ -1,0 +1,334 @@
+"""Each kernel alone against a plain PyTorch restatement of the same
+operation in 32-bit/64-bit, at sizes other than the engine tests use."""
+
+import math
+
+import pytest
+import torch
+
+import plain_gemma2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _native():
+    from strata_inference_b200.kernels import native
+    native.require_device(torch.device(DEV))
+    return native
+
+
+def _tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 1e-2
+
+
+def _close(got, ref, dtype, what, factor=1.0):
+    got = got.detach().double().cpu()
+    ref = ref.double().cpu()
+    scale = max(ref.abs().max().item(), 1e-30)
+    err = (got - ref).abs().max().item()
+    assert err <= factor * _tol(dtype) * scale, f"{what}: {err:.3e} vs scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,vocab", [(72, 50), (2304, 1000)])
+def test_embed_rows(dtype, hidden, vocab):
+    n = _native()
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, hidden, generator=g).to(dtype)
+    toks = torch.randint(0, vocab, (37,), generator=g, dtype=torch.int32)
+    out = torch.empty(37, hidden, dtype=torch.float32, device=DEV)
+    n.embed_rows(toks.to(DEV), table.to(DEV), math.sqrt(hidden), out)
+    ref = plain.embed(toks.tolist(), table.double(), hidden, torch.float64)
+    _close(out, ref, torch.float32, "embed_rows")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [48, 1000, 2304, 20000])
+def test_rms_norm_and_fused_add(dtype, hidden):
+    n = _native()
+    g = torch.Generator().manual_seed(1)
+    rows = 9
+    h = torch.randn(rows, hidden, generator=g) * 3
+    a = torch.randn(rows, hidden, generator=g).to(dtype)
+    w1 = torch.randn(hidden, generator=g) * 0.3
+    w2 = torch.randn(hidden, generator=g) * 0.3
+    eps1, eps2 = 1e-5, 3e-3
+    # norm of selected rows of a 32-bit stream
+    idx = torch.tensor([8, 0, 3], dtype=torch.int32)
+    out = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    n.rms_norm(h.to(DEV), (1 + w1).to(DEV), eps1, out, idx.to(DEV))
+    _close(out, plain.rms_norm(h.double()[idx.long()], w1.double(), eps1), dtype, "rms_norm rows")
+    # norm of an activation-typed input into 32-bit
+    out32 = torch.empty(rows, hidden, dtype=torch.float32, device=DEV)
+    n.rms_norm(a.to(DEV), (1 + w2).to(DEV), eps2, out32)
+    _close(out32, plain.rms_norm(a.double(), w2.double(), eps2), torch.float32, "rms_norm act")
+    # h += rms(a) g1 ; out = rms(h) g2
+    hd = h.clone().to(DEV)
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    n.add_rms_norm(a.to(DEV), (1 + w1).to(DEV), eps1, hd, (1 + w2).to(DEV), eps2, out)
+    h_ref = h.double() + plain.rms_norm(a.double(), w1.double(), eps1)
+    _close(hd, h_ref, torch.float32, "add_rms_norm residual")
+    _close(out, plain.rms_norm(h_ref, w2.double(), eps2), dtype, "add_rms_norm out")
+    # without a post norm and without a following norm
+    hd = h.clone().to(DEV)
+    n.add_rms_norm(a.to(DEV), None, 0.0, hd, None, 0.0, None)
+    _close(hd, h.double() + a.double(), torch.float32, "plain residual add")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter,group", [(24, 0), (24, 8), (1000, 8), (9, 0)])
+def test_gelu_mul(dtype, inter, group):
+    n = _native()
+    g = torch.Generator().manual_seed(2)
+    gate = (torch.randn(5, inter, generator=g) * 2).to(dtype)
+    up = torch.randn(5, inter, generator=g).to(dtype)
+    if group:
+        gu = torch.cat([gate.view(5, -1, group), up.view(5, -1, group)], dim=2).reshape(5, -1)
+    else:
+        gu = torch.cat([gate, up], dim=1)
+    out = torch.empty(5, inter, dtype=dtype, device=DEV)
+    n.gelu_mul(gu.contiguous().to(DEV), out, group)
+    _close(out, plain.gelu_tanh(gate.double()) * up.double(), dtype, "gelu_mul")
+
+
+def test_softcap():
+    n = _native()
+    x = torch.linspace(-200, 200, 10001)
+    y = n.softcap_(x.clone().to(DEV), 30.0)
+    _close(y, 30.0 * torch.tanh(x.double() / 30.0), torch.float32, "softcap")
+
+
+def _paged(k, v, page_tokens, ring_tokens, n_kv, hd, dtype, positions):
+    """Lay keys/values [T, n_kv, hd] of ONE sequence out as pages in shuffled
+    order; returns pools and the page table for slot 1 of 3."""
+    T = k.shape[0]
+    cells = ring_tokens if ring_tokens else -(-T // page_tokens) * page_tokens
+    n_seq_pages = cells // page_tokens
+    n_pages = n_seq_pages + 5
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(9))[:n_seq_pages]
+    kp = torch.full((n_pages, n_kv, page_tokens, hd), float("nan"), dtype=dtype)
+    vp = torch.full((n_pages, n_kv, page_tokens, hd), float("nan"), dtype=dtype)
+    for p in positions:
+        cell = p % ring_tokens if ring_tokens else p
+        kp[perm[cell // page_tokens], :, cell % page_tokens] = k[p].to(dtype)
+        vp[perm[cell // page_tokens], :, cell % page_tokens] = v[p].to(dtype)
+    table = torch.zeros(3, n_seq_pages, dtype=torch.int32)
+    table[1] = perm.to(torch.int32)
+    return kp, vp, table
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window,cap,splits", [
+    (4, 2, 16, 0, 0.0, 1), (3, 1, 48, 7, 20.0, 3), (8, 4, 256, 40, 50.0, 5),
+    (2, 2, 128, 0, 0.0, 16), (6, 3, 512, 33, 0.0, 2)])
+def test_attention_rows_over_cache_and_fresh(dtype, nh, nkv, hd, window, cap, splits):
+    """Single rows deep in a sequence read the paged cache (with a ring when
+    there is a window); whole prompts read the step's own rows."""
+    n = _native()
+    g = torch.Generator().manual_seed(3)
+    T = 150
+    q = torch.randn(T, nh, hd, generator=g).to(dtype)
+    k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+    v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+    scale = 3.0 / math.sqrt(hd)
+    ref = plain.attention(q.double(), k.double(), v.double(), scale, cap, window)
+    page = 8
+    ring = (-(-window // page) + 1) * page if window else 0
+    # (a) the last rows, one per launch-row, from the cache
+    rows = [T - 1, T - 2, 60, 5, 0]
+    for r in rows:
+        keep = range(max(0, r + 1 - ring), r + 1) if ring else range(r + 1)
+        kp, vp, table = _paged(k, v, page, ring, nkv, hd, dtype, keep)
+        out = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+        scratch = torch.empty(max(1, n.attention_rows_scratch_bytes(1, nh, hd, splits)),
+                              dtype=torch.uint8, device=DEV)
+        qr = q[r].reshape(1, nh * hd).contiguous().to(DEV)
+        n.attention_rows(qr, nh * hd, None, None, nh * hd, kp.to(DEV), vp.to(DEV), table.to(DEV),
+                         page, ring, i32([r]), i32([0]), i32([1]), i32([r]), i32([0]), out,
+                         scratch, nh, nkv, hd, scale, cap, window, splits)
+        _close(out.view(nh, hd), ref[r], dtype, f"cache row {r}", factor=4)
+    # (b) two packed prompts (the sequence and its first 21 tokens) from fresh rows
+    T2 = 21
+    packed = torch.cat([torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1),
+                        torch.cat([q[:T2].reshape(T2, -1), k[:T2].reshape(T2, -1),
+                                   v[:T2].reshape(T2, -1)], dim=1)], dim=0).contiguous().to(DEV)
+    width = (nh + 2 * nkv) * hd
+    out = torch.empty(T + T2, nh * hd, dtype=dtype, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n.attention_rows(packed, width, packed[:, nh * hd:], packed[:, (nh + nkv) * hd:], width,
+                     None, None, None, page, ring,
+                     i32(list(range(T)) + list(range(T2))), i32([0] * T + [1] * T2), i32([0, 2]),
+                     i32([0, 0]), i32([0, T]), out, None, nh, nkv, hd, scale, cap, window, 1)
+    _close(out[:T].view(T, nh, hd), ref, dtype, "fresh rows, sequence 0", factor=4)
+    _close(out[T:].view(T2, nh, hd), ref[:T2], dtype, "fresh rows, sequence 1", factor=4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("style", [0, 1])
+def test_rope_store(dtype, style):
+    n = _native()
+    g = torch.Generator().manual_seed(4)
+    nh, nkv, hd, rot = 3, 2, 48, 32
+    theta = 777.0
+    positions = [0, 1, 2, 3, 4, 17, 18, 19, 20]        # two sequences: 5 rows from 0, 4 rows from 17
+    R = len(positions)
+    qkv = torch.randn(R, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    page, ring = 4, 8
+    kp = torch.zeros(9, nkv, page, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros(9, nkv, page, hd, dtype=dtype, device=DEV)
+    table = torch.tensor([[3, 5], [0, 0], [7, 2]], dtype=torch.int32, device=DEV)
+    inv_freq = torch.pow(torch.tensor(theta), (-1.0 / rot) * torch.arange(rot // 2).float() * 2)
+    buf = qkv.clone().to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n.rope_store(buf, i32(positions), i32([0] * 5 + [1] * 4), i32([2, 0]), i32([5, 21]),
+                 inv_freq.to(DEV), rot, style, kp, vp, table, page, ring, nh, nkv, hd)
+
+    def rot_ref(x):  # x [R, heads, hd]
+        x = x.double()
+        ang = torch.tensor(positions).double()[:, None] * inv_freq.double()[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = x.clone()
+        if style == 0:
+            a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+            out[..., :rot // 2], out[..., rot // 2:rot] = a * c - b * s, a * s + b * c
+        else:
+            a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+            out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, a * s + b * c
+        return out
+    qd = qkv.double()
+    q_ref = rot_ref(qd[:, :nh * hd].view(R, nh, hd))
+    k_ref = rot_ref(qd[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd))
+    v_ref = qd[:, (nh + nkv) * hd:].view(R, nkv, hd)
+    got = buf.double().cpu()
+    _close(got[:, :nh * hd].view(R, nh, hd), q_ref, dtype, "q rotated in place")
+    _close(got[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd), k_ref, dtype, "k rotated in place")
+    # cache cells: sequence 0 -> slot 2 (pages 7, 2), sequence 1 -> slot 0 (pages 3, 5)
+    tab = table.cpu()
+    for r, p in enumerate(positions):
+        slot = 2 if r < 5 else 0
+        cell = p % ring
+        pg = int(tab[slot, cell // page])
+        _close(kp[pg, :, cell % page].cpu(), k_ref[r], dtype, f"k cell of row {r}")
+        _close(vp[pg, :, cell % page].cpu(), v_ref[r], dtype, f"v cell of row {r}")
+
+
+def test_rope_store_ring_keeps_only_the_last_positions():
+    """A prompt longer than the ring: only its last ring_tokens positions are written."""
+    n = _native()
+    nh, nkv, hd = 1, 1, 16
+    T, page, ring = 20, 4, 8
+    qkv = torch.arange(T, dtype=torch.float32).repeat_interleave(3 * hd).view(T, 3 * hd).to(DEV)
+    kp = torch.full((2, nkv, page, hd), -1.0, device=DEV)
+    vp = torch.full((2, nkv, page, hd), -1.0, device=DEV)
+    table = torch.tensor([[1, 0]], dtype=torch.int32, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n.rope_store(qkv, i32(list(range(T))), i32([0] * T), i32([0]), i32([T]), None, 0, 0,
+                 kp, vp, table, page, ring, nh, nkv, hd)
+    for p in range(T - ring, T):
+        cell = p % ring
+        pg = [1, 0][cell // page]
+        assert float(vp[pg, 0, cell % page, 0]) == float(p)
+
+
+@pytest.mark.parametrize("R", [1, 3, 8, 13, 32, 64])
+@pytest.mark.parametrize("N,K", [(48, 64), (300, 96), (2304, 2048), (1000, 200)])
+def test_skinny_linear(R, N, K):
+    n = _native()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    out = torch.empty(R, N, dtype=torch.float32, device=DEV)
+    n.skinny_linear(x.to(DEV), w.to(DEV), out)
+    _close(out, ref, torch.float32, "skinny f32 out", factor=20)
+    out16 = torch.empty(R, N, dtype=torch.bfloat16, device=DEV)
+    n.skinny_linear(x.to(DEV), w.to(DEV), out16)
+    _close(out16, ref, torch.bfloat16, "skinny bf16 out")
+    capped = torch.empty(R, N, dtype=torch.float32, device=DEV)
+    n.skinny_linear(x.to(DEV), w.to(DEV), capped, n.EPI_SOFTCAP, 0.7)
+    _close(capped, 0.7 * torch.tanh(ref / 0.7), torch.float32, "skinny soft cap", factor=20)
+    if N % 16 == 0:
+        gated = torch.empty(R, N // 2, dtype=torch.bfloat16, device=DEV)
+        n.skinny_linear(x.to(DEV), w.to(DEV), gated, n.EPI_GEGLU)
+        y = ref.view(R, N // 16, 2, 8)
+        _close(gated, (plain.gelu_tanh(y[:, :, 0]) * y[:, :, 1]).reshape(R, N // 2),
+               torch.bfloat16, "skinny gated")
+
+
+def test_skinny_linear_refuses_what_it_cannot_do():
+    n = _native()
+    x = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(16, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(n.KernelError, match="1 to 64"):
+        n.skinny_linear(x, w, torch.empty(65, 16, dtype=torch.float32, device=DEV))
+    x = torch.zeros(2, 60, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(16, 60, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(n.KernelError, match="multiple of 8"):
+        n.skinny_linear(x, w, torch.empty(2, 16, dtype=torch.float32, device=DEV))
+    with pytest.raises(n.KernelError, match="head_dim"):
+        i32 = torch.zeros(1, dtype=torch.int32, device=DEV)
+        q = torch.zeros(1, 24, dtype=torch.float32, device=DEV)
+        n.attention_rows(q, 24, q, q, 24, None, None, None, 8, 0, i32, i32, i32, i32, i32,
+                         torch.empty(1, 24, device=DEV), None, 1, 1, 24, 1.0, 0.0, 0, 1)
+
+
+# ---------------------------------------------------------------- sampling
+
+def _xorshift_uniforms(seed, count):
+    rng = plain.XorShift64(seed)
+    return [rng.next_f32() for _ in range(count)]
+
+
+@pytest.mark.parametrize("vocab", [17, 300, 5000])
+def test_greedy_takes_the_first_maximum(vocab):
+    n = _native()
+    g = torch.Generator().manual_seed(6)
+    logits = torch.randn(6, vocab, generator=g)
+    logits[2, 3] = logits[2, vocab - 2] = 50.0      # a tie: the lower index wins
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    n.sample_rows(logits.to(DEV), 0.0, 0, 1.0, None, out)
+    assert out.tolist() == [plain.argmax(r.tolist()) for r in logits]
+    assert out[2] == 3
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [
+    (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.9), (1.0, 40, 0.95), (2.0, 1, 1.0), (0.5, 3, 0.3)])
+def test_sampling_matches_the_plain_sampler_draw_by_draw(temperature, top_k, top_p):
+    """Same generator, same draws: the kernel picks the token the plain sampler
+    picks, except where a draw falls within rounding of a boundary."""
+    n = _native()
+    g = torch.Generator().manual_seed(7)
+    vocab, rows, draws = 1000, 4, 40
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    logits[1, 10] = logits[1, 20] = logits[1, 30] = logits[1].max() + 1   # ties at the top
+    seeds = [42, 0, 7, 123456789]
+    state = torch.tensor([s or 1 for s in seeds], dtype=torch.int64, device=DEV)
+    dev_logits = logits.to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    got = []
+    for _ in range(draws):
+        n.sample_rows(dev_logits, temperature, top_k, top_p, state, out)
+        got.append(out.tolist())
+    differ = 0
+    for r in range(rows):
+        rng = plain.XorShift64(seeds[r])
+        for d in range(draws):
+            want = plain.sample_token(logits[r], temperature, top_k, top_p, rng)
+            differ += want != got[d][r]
+    assert differ <= 2, f"{differ} of {rows * draws} draws differ from the plain sampler"
+
+
+def test_sampling_uses_the_indexed_generator_and_advances_it():
+    n = _native()
+    logits = torch.randn(2, 50, generator=torch.Generator().manual_seed(8)).to(DEV)
+    state = torch.tensor([5, 6, 7, 8], dtype=torch.int64, device=DEV)
+    out = torch.empty(2, dtype=torch.int32, device=DEV)
+    n.sample_rows(logits, 1.0, 0, 1.0, state, out, torch.tensor([3, 1], dtype=torch.int32, device=DEV))
+    after = state.tolist()
+    r8, r6 = plain.XorShift64(8), plain.XorShift64(6)
+    r8.next_u64(), r6.next_u64()
+    assert after[0] == 5 and after[2] == 7
+    assert after[3] & 0xFFFFFFFFFFFFFFFF == r8.state and after[1] & 0xFFFFFFFFFFFFFFFF == r6.state

@@ -1,0 +1,306 @@
+"""Each part alone against the plain implementation's function for it, and a
+toy mixer with state of its own, defined here, registered, built and stepped
+without touching the library's files."""
+
+import math
+
+import pytest
+import torch
+
+import plain_gemma2 as plain
+from helpers import CONFIGS, REL_TOL
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _rt(dtype):
+    from strata_inference_b200.parts.base import Runtime
+    return Runtime(DEV, dtype)
+
+
+def _close(got, ref, dtype, what):
+    tol = REL_TOL["float32" if dtype == torch.float32 else "bfloat16"]
+    got, ref = got.detach().double().cpu(), ref.double().cpu()
+    scale = ref.abs().max().item()
+    err = (got - ref).abs().max().item()
+    assert err <= tol * scale, f"{what}: {err:.3e} vs {tol:.0e} x {scale:.3e}"
+
+
+def _ctx(rt, cache, seqs):
+    """A StepContext for sequences [(slot, start, count)]."""
+    from strata_inference_b200.parts.base import StepContext
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    row_pos, row_seq, row0, acc = [], [], [], 0
+    for b, (_, start, n) in enumerate(seqs):
+        row_pos += list(range(start, start + n))
+        row_seq += [b] * n
+        row0.append(acc)
+        acc += n
+    return StepContext(
+        n_rows=acc, n_seqs=len(seqs), tokens=i32([0] * acc), row_pos=i32(row_pos),
+        row_seq=i32(row_seq), seq_slot=i32([s for s, _, _ in seqs]),
+        seq_start=i32([st for _, st, _ in seqs]), seq_end=i32([st + n for _, st, n in seqs]),
+        seq_row0=i32(row0), starts=[st for _, st, _ in seqs], counts=[n for _, _, n in seqs],
+        slots=[s for s, _, _ in seqs], all_from_start=all(st == 0 for _, st, _ in seqs),
+        max_count=max(n for _, _, n in seqs), max_end=max(st + n for _, st, n in seqs),
+        cache=cache, runtime=rt)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    from strata_inference_b200.parts.norm import RMSNorm
+    rt = _rt(dtype)
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(200, generator=g) * 0.2).to(torch.bfloat16)
+    x = torch.randn(7, 200, generator=g)
+    for offset in (True, False):
+        part = RMSNorm({"eps": 1e-4, "unit_offset": offset}, 200, {"weight": w}, rt)
+        got = part.forward(x.to(DEV))
+        ref = plain.rms_norm(x.double(), w.double() if offset else w.double() - 1.0, 1e-4)
+        _close(got, ref, dtype, f"rms_norm part, unit_offset={offset}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gated_mlp_part(dtype):
+    from strata_inference_b200.parts.feed_forward import GatedMLP
+    rt = _rt(dtype)
+    g = torch.Generator().manual_seed(1)
+    for hidden, inter, rows in ((96, 320, 5), (96, 320, 100), (80, 36, 3)):
+        ws = {n: (torch.randn(s, generator=g) * 0.2).to(torch.bfloat16) for n, s in (
+            ("gate_proj.weight", (inter, hidden)), ("up_proj.weight", (inter, hidden)),
+            ("down_proj.weight", (hidden, inter)))}
+        part = GatedMLP({"intermediate_size": inter, "activation": "gelu_pytorch_tanh"},
+                        hidden, ws, rt)
+        x = torch.randn(rows, hidden, generator=g).to(dtype)
+        got = part.forward(x.to(DEV), None)
+        ref = plain.geglu_ffn(x.double(), ws["gate_proj.weight"].double(),
+                              ws["up_proj.weight"].double(), ws["down_proj.weight"].double())
+        _close(got, ref, dtype, f"gated_mlp {hidden}x{inter}, {rows} rows")
+
+
+def _attention_setup(dtype, window, cfg_name="B"):
+    from strata_inference_b200.cache.paged import SequenceCache
+    from strata_inference_b200.config.spec import PartSpec
+    from strata_inference_b200.parts.attention import Attention
+    cfg = dict(CONFIGS[cfg_name])
+    rt = _rt(dtype)
+    g = torch.Generator().manual_seed(2)
+    nh, nkv, hd, H = (cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                      cfg["hidden_size"])
+    ws = {"q_proj.weight": torch.randn(nh * hd, H, generator=g) * 0.3,
+          "k_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.3,
+          "v_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.1,
+          "o_proj.weight": torch.randn(H, nh * hd, generator=g) * 0.1}
+    ws = {k: v.to(torch.bfloat16) for k, v in ws.items()}
+    params = {"num_heads": nh, "num_kv_heads": nkv, "head_dim": hd,
+              "score_scale": cfg["query_pre_attn_scalar"] ** -0.5,
+              "logit_softcap": cfg["attn_logit_softcapping"] or 0.0, "window": window,
+              "position": PartSpec("rope_neox", {"theta": cfg["rope_theta"], "rotary_dim": hd})}
+    part = Attention(params, H, ws, rt)
+    cache = SequenceCache([part.cache_need()], 512, 128, dtype, DEV, page_tokens=8)
+    pw = {"self_attn." + k: v for k, v in ws.items()}
+    return cfg, rt, part, cache, pw, g
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 16])
+def test_attention_part_prompt_then_tokens(dtype, window):
+    """The mixer alone: a prompt in one step, then single tokens, against the
+    plain attention block over the whole sequence."""
+    cfg, rt, part, cache, pw, g = _attention_setup(dtype, window)
+    T, cut = 70, 30
+    x = torch.randn(T, cfg["hidden_size"], generator=g).to(dtype)
+    pcfg = dict(cfg, sliding_window=window or None)
+    ref = plain.attention_block(x.double(), {k: v.double() for k, v in pw.items()}, "self_attn.",
+                                pcfg, sliding=window > 0)
+    slot = cache.acquire()
+    other = cache.acquire()      # a neighbour, so that slot 0's pages are not the first ones
+    cache.reserve([(other, 9)])
+    cache.reserve([(slot, cut)])
+    cache.sync_tables()
+    got = [part.forward(x[:cut].to(DEV), _ctx(rt, cache, [(slot, 0, cut)]), 0, 0, True)]
+    cache.advance(slot, cut)
+    for t in range(cut, T):
+        cache.reserve([(slot, 1)])
+        cache.sync_tables()
+        got.append(part.forward(x[t:t + 1].to(DEV), _ctx(rt, cache, [(slot, t, 1)]), 0, 0, True))
+        cache.advance(slot, 1)
+    _close(torch.cat(got), ref, dtype, f"attention part, window {window}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_part_reads_a_lent_cache(dtype):
+    """A run that borrows another entry's cache projects q only and attends
+    over the lender's keys and values."""
+    cfg, rt, part, cache, pw, g = _attention_setup(dtype, 0)
+    T = 20
+    x = torch.randn(T, cfg["hidden_size"], generator=g).to(dtype)
+    y = torch.randn(T, cfg["hidden_size"], generator=g).to(dtype)
+    slot = cache.acquire()
+    cache.reserve([(slot, T)])
+    cache.sync_tables()
+    ctx = _ctx(rt, cache, [(slot, 0, T)])
+    part.forward(x.to(DEV), ctx, 0, 0, True)                 # the lender writes k(x), v(x)
+    got = part.forward(y.to(DEV), ctx, 1, 0, False)          # the borrower: q(y) over them
+    W = {k: v.double() for k, v in pw.items()}
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    pos = torch.arange(T)
+    q = plain.rope_neox((y.double() @ W["self_attn.q_proj.weight"].T).view(T, nh, hd), pos,
+                        cfg["rope_theta"])
+    k = plain.rope_neox((x.double() @ W["self_attn.k_proj.weight"].T).view(T, nkv, hd), pos,
+                        cfg["rope_theta"])
+    v = (x.double() @ W["self_attn.v_proj.weight"].T).view(T, nkv, hd)
+    o = plain.attention(q, k, v, cfg["query_pre_attn_scalar"] ** -0.5,
+                        cfg["attn_logit_softcapping"] or 0.0, 0)
+    ref = o.reshape(T, nh * hd) @ W["self_attn.o_proj.weight"].T
+    _close(got, ref, dtype, "attention over a lent cache")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    from strata_inference_b200.parts.embedding import LMHead, TokenEmbedding
+    rt = _rt(dtype)
+    g = torch.Generator().manual_seed(3)
+    V, H = 300, 80
+    table = (torch.randn(V, H, generator=g) * 0.1).to(torch.bfloat16)
+    emb = TokenEmbedding({"scale": math.sqrt(H)}, H, V, {"weight": table}, rt)
+    toks = torch.randint(0, V, (11,), generator=g, dtype=torch.int32)
+    h = emb.forward(toks.to(DEV))
+    _close(h, plain.embed(toks.tolist(), table.double(), H, torch.float64), torch.float32,
+           "embedding")
+    for rows in (3, 100):
+        y = torch.randn(rows, H, generator=g).to(dtype)
+        for cap in (0.0, 2.0):
+            head = LMHead({"tied": True, "logit_softcap": cap}, H, V, {}, rt, emb)
+            got = head.forward(y.to(DEV))
+            ref = y.double() @ table.double().T
+            if cap:
+                ref = cap * torch.tanh(ref / cap)
+            assert got.dtype == torch.float32
+            _close(got, ref, dtype, f"head, {rows} rows, cap {cap}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part(dtype):
+    """One sandwich block built from a LayerSpec against the plain decoder layer."""
+    from strata_inference_b200.cache.paged import SequenceCache
+    from strata_inference_b200.config.registry import spec_from_config
+    from strata_inference_b200.engine.model import DecoderModel, expected_tensors
+    from strata_inference_b200.weights.random_init import random_tensors
+    cfg = dict(CONFIGS["C"], num_hidden_layers=1, layer_types=["sliding_attention"])
+    _, spec = spec_from_config(cfg)
+    ws = random_tensors(expected_tensors(spec), 5, torch.bfloat16, "cpu", 0.1, 0.3)
+    rt = _rt(dtype)
+    model = DecoderModel(spec, ws, rt)
+    cache = SequenceCache(model.cache_needs(), 512, 256, dtype, DEV, page_tokens=16)
+    T = 50
+    h0 = torch.randn(T, cfg["hidden_size"], generator=torch.Generator().manual_seed(6))
+    slot = cache.acquire()
+    cache.reserve([(slot, T)])
+    cache.sync_tables()
+    h = h0.clone().to(DEV)
+    model.blocks[0].forward(h, None, _ctx(rt, cache, [(slot, 0, T)]), 0, 0, True, None)
+    ref = plain.decoder_layer(h0.double(), {k: v.double() for k, v in ws.items()}, 0, cfg)
+    _close(h, ref, dtype, "sandwich block")
+
+
+# ---------------------------------------------------------------- a toy mixer
+
+class RunningMeanMixer:
+    """y_t = W . mean(x_1 .. x_t): needs no keys, only a fixed-size state per
+    sequence (the running sum and the count)."""
+
+    @staticmethod
+    def tensors(params, hidden):
+        from strata_inference_b200.weights.loader import TensorDecl
+        return {"mix.weight": TensorDecl((hidden, hidden))}
+
+    def __init__(self, params, hidden, weights, rt):
+        self.hidden = hidden
+        self.w = weights["mix.weight"].to(device=rt.device, dtype=torch.float32)
+
+    def cache_need(self):
+        from strata_inference_b200.cache.paged import CacheNeed, StateNeed
+        return CacheNeed(state=StateNeed((self.hidden + 1,), torch.float32))
+
+    def forward(self, x, ctx, entry, cache_entry, owns_cache):
+        state = ctx.state(cache_entry)
+        out = torch.empty_like(x)
+        row = 0
+        for slot, n in zip(ctx.slots, ctx.counts):
+            xs = x[row:row + n].float()
+            sums = torch.cumsum(xs, 0) + state[slot, :-1]
+            counts = state[slot, -1] + torch.arange(1, n + 1, device=x.device)
+            out[row:row + n] = ((sums / counts[:, None]) @ self.w.t()).to(x.dtype)
+            if owns_cache:
+                state[slot, :-1] = sums[-1]
+                state[slot, -1] = counts[-1]
+            row += n
+        return out
+
+
+def _toy_spec(config):
+    from strata_inference_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = config["hidden_size"]
+    norm = PartSpec("rms_norm", {"eps": config["eps"], "unit_offset": False})
+    ffn = PartSpec("gated_mlp", {"intermediate_size": config["inter"],
+                                 "activation": "gelu_pytorch_tanh"})
+    layers = tuple(LayerSpec(prefix=f"layers.{i}.", block="pre_norm",
+                             mixer=PartSpec("running_mean", {}), feed_forward=ffn,
+                             norms={"pre_mixer": norm, "pre_feed_forward": norm},
+                             names={"mixer": "mixer.", "feed_forward": "ffn.",
+                                    "pre_mixer": "norm1.", "pre_feed_forward": "norm2."})
+                   for i in range(config["layers"]))
+    return ModelSpec(architecture="ToyRunningMean", hidden_size=H, vocab_size=config["vocab"],
+                     max_positions=config["max_pos"], embedding=PartSpec("token_embedding", {}),
+                     layers=layers, schedule=tuple(ScheduleEntry(i) for i in range(len(layers))),
+                     final_norm=norm, head=PartSpec("lm_head", {"tied": True}),
+                     names={"embedding": "embed.", "final_norm": "norm.", "head": "head."})
+
+
+def _toy_plain(tokens, W, config):
+    """The toy model, whole sequence, in 64-bit."""
+    eps = config["eps"]
+    norm = lambda x, w: x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w  # noqa: E731
+    h = W["embed.weight"][torch.tensor(tokens)]
+    for i in range(config["layers"]):
+        p = f"layers.{i}."
+        n = norm(h, W[p + "norm1.weight"])
+        means = torch.cumsum(n, 0) / torch.arange(1, len(tokens) + 1)[:, None]
+        h = h + means @ W[p + "mixer.mix.weight"].T
+        n = norm(h, W[p + "norm2.weight"])
+        h = h + plain.geglu_ffn(n, W[p + "ffn.gate_proj.weight"], W[p + "ffn.up_proj.weight"],
+                                W[p + "ffn.down_proj.weight"])
+    return norm(h, W["norm.weight"]) @ W["embed.weight"].T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    from strata_inference_b200 import Engine, register_architecture, write_random_model
+    from strata_inference_b200.parts import register_mixer
+    from safetensors.torch import load_file
+    register_mixer("running_mean", RunningMeanMixer)
+    register_architecture("ToyRunningMean", dict, _toy_spec)
+    config = {"architectures": ["ToyRunningMean"], "hidden_size": 40, "inter": 56, "vocab": 90,
+              "layers": 2, "eps": 1e-5, "max_pos": 64}
+    d = write_random_model(str(tmp_path / "toy"), config, seed=3, dtype=torch.float32,
+                           matrix_std=0.2, norm_std=0.5)
+    W = {k: v.double() for k, v in load_file(d + "/model.safetensors").items()}
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=256)
+    assert not eng.cache.groups and len(eng.cache.state) == 2
+    g = torch.Generator().manual_seed(1)
+    a = torch.randint(0, 90, (23,), generator=g).tolist()
+    b = torch.randint(0, 90, (9,), generator=g).tolist()
+    ref_a, ref_b = _toy_plain(a, W, config), _toy_plain(b, W, config)
+    for round_ in range(2):                      # the second round reuses the slots: state is reset
+        sa, sb = eng.new_sequence(), eng.new_sequence()
+        got = eng.step([(sa, a[:10]), (sb, b[:4])], want=[list(range(10)), list(range(4))])
+        _close(got, torch.cat([ref_a[:10], ref_b[:4]]), torch.float32, f"toy prompts {round_}")
+        for t in range(4, 9):
+            got = eng.step([(sa, [a[6 + t]]), (sb, [b[t]])])
+            _close(got, torch.stack([ref_a[6 + t], ref_b[t]]), torch.float32, f"toy step {t}")
+        eng.end_sequence(sb)
+        got = eng.step([(sa, a[15:])], want=[list(range(8))])
+        _close(got, ref_a[15:], torch.float32, f"toy tail {round_}")
+        eng.end_sequence(sa)
