@@ -1,0 +1,305 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of strata_inference_b200 on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  The run: Gemma2-2B's layer sizes with random bfloat16
+weights, a batch of 8 sequences that each hold close to the 8,192-token
+context; a "step" is one decode step (one new token per sequence).
+
+* ``value``: decoded tokens per second, K steps timed on the device with CUDA
+  events around the replayed step graphs (tokens are fed from the host each
+  step; the result is not read back).
+* ``e2e``: the same through the Python entry point ``GenerationEngine.generate``:
+  host token lists in, host token lists out, wall clock over the decode steps.
+* ``prefill``: one 2,048-token prompt through ``Engine.step``.
+* ``roofline``: bytes a decode step has to read (every weight once, the keys and
+  values each live sequence's layers attend to) / its time / the measured copy
+  bandwidth.
+* ``points``: decoded tokens per second at batch 1 and 64.
+
+Between timed steps nothing flushes L2: each step reads 5 GB of weights and more
+of cache, against 126 MB of L2.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s at batch 8 (BF16, one B200, Gemma2-2B shape, context 8192)"
+
+
+def baseline_config():
+    """Layer sizes of BASELINE.json's configs[2] (Gemma2-2B shape)."""
+    return {
+        "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+        "num_hidden_layers": 26, "hidden_size": 2304, "num_attention_heads": 8,
+        "num_key_value_heads": 4, "head_dim": 256, "intermediate_size": 9216,
+        "vocab_size": 256000, "rope_theta": 10000.0, "sliding_window": 4096,
+        "query_pre_attn_scalar": 256, "attn_logit_softcapping": 50.0,
+        "final_logit_softcapping": 30.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 8192,
+        "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True,
+    }
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def fill_context(engine, slots, n_tokens):
+    """Give each slot ``n_tokens`` positions of random keys and values (what a
+    prompt of that length would leave, without running it)."""
+    import torch
+    engine.cache.reserve([(s, n_tokens) for s in slots])
+    for s in slots:
+        engine.cache.advance(s, n_tokens)
+    engine.cache.sync_tables()
+
+
+def randomize_pools(engine):
+    import torch
+    g = torch.Generator(device=engine.device).manual_seed(11)
+    for grp in engine.cache.groups:
+        for pool in (grp.k, grp.v):
+            for layer in range(pool.shape[0]):
+                pool[layer].normal_(0.0, 0.5, generator=g)
+
+
+def kv_bytes_per_step(engine, lengths):
+    """Bytes of keys and values one decode step reads for sequences of these lengths."""
+    total = 0
+    for grp in engine.cache.groups:
+        per_token = 2 * grp.need.n_kv_heads * grp.need.head_dim * grp.k.element_size()
+        for n in lengths:
+            seen = min(n, grp.need.window) if grp.need.window else n
+            total += len(grp.entries) * seen * per_token
+    return total
+
+
+def time_decode(engine, batch, context, steps, warmup):
+    """ms per decode step (device time) for ``batch`` sequences near ``context`` positions."""
+    import torch
+    start_len = context - (steps + warmup + 2)
+    slots = [engine.new_sequence() for _ in range(batch)]
+    fill_context(engine, slots, start_len)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, engine.vocab_size, (steps + warmup + 2, batch), generator=g).tolist()
+    for i in range(warmup + 2):            # eager, capture, then replays
+        engine.decode_step(slots, toks[i])
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for i in range(steps):
+        engine.decode_step(slots, toks[warmup + 2 + i])
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    lengths = [engine.length(s) for s in slots]
+    graph = engine._graphs[(batch, 0.0, 0, 1.0)]
+    launches = graph.launches_per_step
+    for s in slots:
+        engine.end_sequence(s)
+    return ms, lengths, launches
+
+
+def time_prefill(engine, n_tokens, reps=5):
+    import torch
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, engine.vocab_size, (n_tokens,), generator=g).tolist()
+    times = []
+    for i in range(reps + 2):
+        slot = engine.new_sequence()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        engine.step([(slot, toks)])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(begin.elapsed_time(end))
+        engine.end_sequence(slot)
+    return statistics.median(times)
+
+
+def prefill_flops(cfg, T):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd, L = (cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                      cfg["num_hidden_layers"])
+    per_layer = 2 * T * H * (nh + 2 * nkv) * hd + 2 * T * nh * hd * H + 3 * 2 * T * H * I
+    attn = 0
+    for i in range(L):
+        w = cfg["sliding_window"] if i % 2 == 0 else 0
+        pairs = sum(min(p + 1, w) if w else p + 1 for p in range(T))
+        attn += 4 * pairs * nh * hd
+    return L * per_layer + attn + 2 * H * V          # logits of the last row only
+
+
+def run_ours(args):
+    import torch
+    from strata_inference_b200 import GenerationConfig, GenerationEngine
+
+    cfg = baseline_config()
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    context, batch = args.context, args.batch
+    peaks = measured_peaks()
+    biggest = max(batch, 64 if not args.no_points else batch)
+    gen = GenerationEngine.from_random(cfg, seed=5, dtype="bfloat16", ctx=context,
+                                       max_tokens=biggest * context, max_slots=biggest)
+    engine = gen.engine
+    randomize_pools(engine)
+    weight_bytes = engine.model.weight_bytes()
+
+    with ClockSampler() as clocks:
+        ms, lengths, launches = time_decode(engine, batch, context, args.steps, args.warmup)
+    value = batch * 1e3 / ms
+    step_bytes = weight_bytes + kv_bytes_per_step(engine, lengths)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _ = time_decode(engine, b, context, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
+
+    T = 2048
+    pre_ms = time_prefill(engine, T)
+    flops = prefill_flops(cfg, T)
+    prefill = {"value": round(T * 1e3 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # end to end: the public generate() call, host tokens in and out every step
+    n_new = args.steps + args.warmup
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, engine.vocab_size, (context - n_new - 2,), generator=g).tolist()
+               for _ in range(batch)]
+    stamps = []
+
+    def on_token(index, token):
+        if index == 0:
+            stamps.append(time.perf_counter())
+        return True
+    outs = gen.generate(prompts, GenerationConfig(max_tokens=n_new), on_token)
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    timed_tokens = sum(len(o.token_ids) for o in outs) - batch * args.warmup
+    e2e_value = timed_tokens / (t_end - stamps[args.warmup - 1])
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Gemma2-2B shape", "global_batch": batch, "seq_len": context,
+            "parallelism": "none", "layers": cfg["num_hidden_layers"],
+            "layers_of_named_config": full_layers, "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+            "vocab": cfg["vocab_size"], "sliding_window": cfg["sliding_window"],
+            "context": context, "kv_len_at_decode": int(statistics.mean(lengths)),
+            "l2": "no flush: each step reads more than 5 GB, L2 is 126 MB",
+            "peaks": peaks["source"],
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 8 * batch * 4, "d2h_bytes_per_step": batch * 4},
+        "gpu_launches": launches * args.steps,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="fewer layers than the named configuration (both numbers are reported)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "strata-inference is a Rust crate (Cargo.toml, no setup.py or "
+                          "pyproject.toml): pip cannot install it and no Rust toolchain is in "
+                          "the image"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this library runs on one GPU; --gpus %d is not supported" % args.gpus)
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

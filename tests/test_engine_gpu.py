@@ -6,7 +6,8 @@ another so that slots are used again; long decoding; the first tokens."""
 import pytest
 import torch
 
-from helpers import (CONFIGS, assert_logits_close, make_model_dir, plain_logits, random_prompts)
+from helpers import (CONFIGS, SHARPEN, assert_logits_close, make_model_dir, plain_logits,
+                     random_prompts)
 
 pytestmark = pytest.mark.gpu
 
@@ -19,13 +20,15 @@ CASES = [("A", 64), ("A", 4), ("B", 64), ("B", 8), ("C", 16)]
 def model_dirs(tmp_path_factory):
     out = {}
     for i, (name, cfg) in enumerate(CONFIGS.items()):
-        out[name] = make_model_dir(str(tmp_path_factory.mktemp(f"tiny_{name}")), cfg, seed=10 + i)
+        for dtype, sharpen in SHARPEN.items():
+            out[name, dtype] = make_model_dir(str(tmp_path_factory.mktemp(f"tiny_{name}_{dtype}")),
+                                              cfg, seed=10 + i, sharpen=sharpen)
     return out
 
 
 def _engine(model_dirs, name, dtype, page_tokens, max_tokens=1024):
     from strata_inference_b200 import Engine
-    return Engine.from_dir(model_dirs[name], dtype=dtype, max_tokens=max_tokens,
+    return Engine.from_dir(model_dirs[name, dtype], dtype=dtype, max_tokens=max_tokens,
                            page_tokens=page_tokens)
 
 
@@ -40,7 +43,7 @@ def test_whole_prompt_each_request_alone(model_dirs, name, page, dtype):
     cfg = CONFIGS[name]
     eng = _engine(model_dirs, name, dtype, page)
     for r, toks in enumerate(random_prompts(cfg, _lengths(cfg), seed=1)):
-        ref = plain_logits(toks, model_dirs[name], cfg)
+        ref = plain_logits(toks, model_dirs[name, dtype], cfg)
         slot = eng.new_sequence()
         got = eng.step([(slot, toks)], want=[list(range(len(toks)))])
         eng.end_sequence(slot)
@@ -53,7 +56,7 @@ def test_last_32_tokens_one_by_one(model_dirs, name, page, dtype):
     cfg = CONFIGS[name]
     eng = _engine(model_dirs, name, dtype, page)
     for r, toks in enumerate(random_prompts(cfg, _lengths(cfg), seed=2)):
-        ref = plain_logits(toks, model_dirs[name], cfg)
+        ref = plain_logits(toks, model_dirs[name, dtype], cfg)
         cut = len(toks) - 32
         slot = eng.new_sequence()
         got = [eng.step([(slot, toks[:cut])], want=[[cut - 1]])]
@@ -102,7 +105,7 @@ def test_unequal_batches_one_after_another(model_dirs, name, page, dtype):
     total = [top - 1, 30, 45, 37, top - 10, 12, 50]
     prompt = [20, 3, 33, 1, top - 30, 11, 9]
     reqs = random_prompts(cfg, total, seed=3)
-    refs = [plain_logits(t, model_dirs[name], cfg) for t in reqs]
+    refs = [plain_logits(t, model_dirs[name, dtype], cfg) for t in reqs]
     first = _run_batch(eng, reqs[:4], prompt[:4], refs[:4], dtype, f"{name} batch 1")
     assert eng.cache.pages_in_use() == 0
     second = _run_batch(eng, reqs[4:], prompt[4:], refs[4:], dtype, f"{name} batch 2")
@@ -116,7 +119,7 @@ def test_long_decoding(model_dirs, dtype):
     name, cfg = "C", CONFIGS["C"]
     eng = _engine(model_dirs, name, dtype, 16)
     toks = random_prompts(cfg, [cfg["max_position_embeddings"]], seed=4)[0]
-    ref = plain_logits(toks, model_dirs[name], cfg)
+    ref = plain_logits(toks, model_dirs[name, dtype], cfg)
     slot = eng.new_sequence()
     got = [eng.step([(slot, toks[:2])], want=[[0, 1]])]
     for t in toks[2:]:
@@ -135,7 +138,7 @@ def test_first_tokens(model_dirs, name, dtype):
     cfg = CONFIGS[name]
     eng = _engine(model_dirs, name, dtype, 64)
     toks = random_prompts(cfg, [4], seed=5)[0]
-    ref = plain_logits(toks, model_dirs[name], cfg)
+    ref = plain_logits(toks, model_dirs[name, dtype], cfg)
     slot = eng.new_sequence()
     got = torch.cat([eng.step([(slot, [t])]) for t in toks], dim=0)
     eng.end_sequence(slot)
@@ -150,7 +153,7 @@ def test_far_key_and_window_edge(tmp_path, dtype):
     cfg = dict(CONFIGS["A"])
     cfg["max_position_embeddings"] = 256
     cfg["sliding_window"] = 24
-    d = make_model_dir(str(tmp_path / "m"), cfg, seed=21, sharpen=10.0)
+    d = make_model_dir(str(tmp_path / "m"), cfg, seed=21, sharpen=1.5 * SHARPEN[dtype])
     toks = random_prompts(cfg, [200], seed=6)[0]
     toks[5] = 77                      # a token that appears once, early
     toks = [t if (t != 77 or i == 5) else 78 for i, t in enumerate(toks)]

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_gemma2 as plain
-from helpers import (CONFIGS, assert_logits_close, make_model_dir, plain_logits, plain_weights,
+from helpers import (CONFIGS, SHARPEN, assert_logits_close, eos_list, make_model_dir, plain_logits, plain_weights,
                      random_prompts)
 
 pytestmark = pytest.mark.gpu
@@ -39,7 +39,7 @@ def test_greedy_generation_matches_plain(model_dirs, name, use_graph):
     outs = eng.generate(prompts, GenerationConfig(max_tokens=steps))
     W = plain_weights(model_dirs[name])
     for p, o in zip(prompts, outs):
-        want, reason = plain.generate(p, W, cfg, steps)
+        want, reason = plain.generate(p, W, cfg, steps, stop_tokens=eos_list(cfg))
         assert o.token_ids == want and o.stop_reason == reason and o.prompt_tokens == len(p)
     assert eng.engine.cache.pages_in_use() == 0
 
@@ -57,7 +57,7 @@ def test_sampled_generation_alone_and_in_batch(model_dirs):
     W = plain_weights(model_dirs[name])
     for p, t, a in zip(prompts, together, alone):
         assert t.token_ids == a.token_ids
-        want, _ = plain.generate(p, W, cfg, 12, temperature=0.8, seed=4)
+        want, _ = plain.generate(p, W, cfg, 12, stop_tokens=eos_list(cfg), temperature=0.8, seed=4)
         assert t.token_ids == want
     seeded = eng.generate(prompts, conf, seeds=[4, 5, 6])
     assert seeded[0].token_ids == together[0].token_ids
@@ -76,7 +76,7 @@ def test_stop_tokens_context_end_and_batches_one_after_another(model_dirs):
     conf = GenerationConfig(max_tokens=-1, stop_tokens=[stop])
     outs = eng.generate(prompts, conf)
     for p, o in zip(prompts, outs):
-        want, reason = plain.generate(p, W, cfg, 10 ** 6, stop_tokens=[stop] + cfg["eos_token_id"])
+        want, reason = plain.generate(p, W, cfg, 10 ** 6, stop_tokens=[stop] + eos_list(cfg))
         assert o.token_ids == want and o.stop_reason == reason
         assert stop not in o.token_ids
     assert {o.stop_reason for o in outs} <= {"eos", "context_length"}
@@ -104,7 +104,8 @@ def test_command_line_json(model_dirs):
     r = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert r.returncode == 0, r.stderr
     out = json.loads(r.stdout)
-    want, reason = plain.generate(prompt, plain_weights(model_dirs["A"]), cfg, 5)
+    want, reason = plain.generate(prompt, plain_weights(model_dirs["A"]), cfg, 5,
+                                  stop_tokens=eos_list(cfg))
     assert out["output_token_ids"] == want and out["stop_reason"] == reason
     assert out["generated_tokens"] == len(want)
     assert set(out["timings"]) >= {"load_ms", "prefill_ms", "decode_ms", "total_ms",
@@ -139,8 +140,9 @@ def test_trace_replay(model_dirs, tmp_path, dtype):
     shorter request ends earlier, then a second batch on the freed cache."""
     name, cfg = "A", CONFIGS["A"]
     V = cfg["vocab_size"]
+    model_dir = make_model_dir(str(tmp_path / "model"), cfg, seed=40, sharpen=SHARPEN[dtype])
     reqs = random_prompts(cfg, [70, 40, 90], seed=8)
-    refs = [plain_logits(t, model_dirs[name], cfg) for t in reqs]
+    refs = [plain_logits(t, model_dir, cfg) for t in reqs]
     a, b, c = reqs
     steps = [
         {"step": 0, "entries": [{"id": "a", "tokens": a, "want": list(range(len(a)))}], "end": ["a"]},
@@ -162,7 +164,7 @@ def test_trace_replay(model_dirs, tmp_path, dtype):
         steps.append({"step": len(steps), "entries": [{"id": "c", "tokens": [c[i]], "want": [0]}],
                       "end": ["c"] if i == 89 else []})
     out = str(tmp_path / "out")
-    _replay(model_dirs[name], dtype, steps, out, max_tokens=256)
+    _replay(model_dir, dtype, steps, out, max_tokens=256)
     assert_logits_close(_read(out, 0, V), refs[0], dtype, "whole request")
     assert_logits_close(_read(out, 1, V), refs[1][29:30], dtype, "prefix")
     for k, i in enumerate(range(30, 40)):
