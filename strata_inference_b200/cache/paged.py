@@ -113,8 +113,10 @@ class KVGroup:
         self.n_pages = min(n_pages, max_slots * self.pages_per_seq)
         self.pool = PagePool(self.n_pages)
         shape = (len(entries), self.n_pages, need.n_kv_heads, page_tokens, need.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # zeroed once: kernels that work on whole tiles of positions may load a
+        # cell that is masked out, and its bits must at least be a number
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
         self.table_host = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32)
         self.table = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32, device=device)
         self.pages: List[List[int]] = [[] for _ in range(max_slots)]

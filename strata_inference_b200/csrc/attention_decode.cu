@@ -1,0 +1,279 @@
+// Attention of single query rows over the paged bfloat16 cache: the
+// bandwidth-bound kernel of decoding.  Same mathematics as attention_rows.cu
+// (scale, soft cap, causal and window mask, softmax in 32-bit, weighted sum of
+// v); this file only changes how the work is laid out:
+//
+// * one warp per (row, kv head, split): the G = n_heads / n_kv query heads that
+//   share a kv head are done together, so each key and value is read once;
+// * keys are walked in tiles of 16 positions, aligned so that a tile lies in
+//   one page.  Scores of a tile are one mma.m16n8k16 chain: the 16 keys are the
+//   A operand, the (up to 8) query heads the B operand, fragments loaded
+//   straight from global memory with 16-byte loads under the same permutation of
+//   the head dimension on both operands (see linear_skinny.cu);
+// * probabilities go through a few hundred bytes of shared memory per warp; the
+//   weighted sum of v runs on the CUDA cores with each lane owning 8 consecutive
+//   dimensions of a value row (a 16-byte load), several keys per pass when the
+//   head is narrower than 256;
+// * with splits > 1 the partial (max, sum, accumulator) of each split goes to
+//   scratch memory in the layout attention_combine reads.
+//
+// Plain counterpart: tests/plain_gemma2.py attention().
+// Reference: src/backend/cuda/kernels.rs:2851-3180 (grouped_attn_decode: one block
+// per head, two passes over the keys), src/backend/cpu.rs:1352-1434.
+#include "common.cuh"
+
+struct AttnDecodeArgs {
+    const __nv_bfloat16* q;   // row r, head h at q + r * q_stride + h * head_dim
+    const __nv_bfloat16* k_pool;
+    const __nv_bfloat16* v_pool;
+    __nv_bfloat16* out;       // [rows, n_heads * head_dim]
+    float* partial;           // [rows, n_heads, splits, head_dim + 2]
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* page_table;
+    int q_stride;
+    int rows, n_heads, n_kv;
+    int max_pages, page_tokens, ring_tokens;
+    int window, splits;
+    float scale, softcap;
+};
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const __nv_bfloat16* p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        o[2 * i] = __uint_as_float(w[i] << 16);
+        o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// HD: head size (64, 128 or 256).  G: query heads per kv head (1, 2, 4 or 8).
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p) {
+    constexpr int KB = HD / 32;          // 32-wide blocks of the head dimension
+    constexpr int LPK = HD / 8;          // lanes that cover one value row
+    constexpr int KPP = 32 / LPK;        // keys per pass of the weighted sum
+    __shared__ float sm_all[4][2][16][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float(*s_sm)[8] = sm_all[warp][0];
+    float(*p_sm)[8] = sm_all[warp][1];
+    const long long unit = (long long)blockIdx.x * 4 + warp;
+    if (unit >= (long long)p.rows * p.n_kv * p.splits) return;
+    const int split = (int)(unit % p.splits);
+    const int kvh = (int)((unit / p.splits) % p.n_kv);
+    const int r = (int)(unit / ((long long)p.splits * p.n_kv));
+    const int g = lane >> 2, t = lane & 3;
+
+    const int pos = p.row_pos[r];
+    const int slot = p.seq_slot[p.row_seq[r]];
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int tile_lo = lo >> 4, tile_hi = pos >> 4;             // inclusive
+    const int n_tiles = tile_hi - tile_lo + 1;
+    const int per = (n_tiles + p.splits - 1) / p.splits;
+    const int t0 = tile_lo + split * per;
+    const int t1 = min(t0 + per, tile_hi + 1);
+    const int* table = p.page_table + (size_t)slot * p.max_pages;
+
+    // query heads of this kv head as the B operand: lane (g, t) holds head g
+    uint4 qf[KB];
+    {
+        const __nv_bfloat16* qp = p.q + (size_t)r * p.q_stride + (size_t)(kvh * G + g) * HD;
+#pragma unroll
+        for (int j = 0; j < KB; ++j)
+            qf[j] = g < G ? __ldg(reinterpret_cast<const uint4*>(qp + 32 * j + 8 * t))
+                          : make_uint4(0, 0, 0, 0);
+    }
+
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+    }
+    const int sub = lane / LPK;          // which key of a pass this lane works on
+    const int dim0 = (lane % LPK) * 8;   // its 8 dimensions
+
+    for (int tile = t0; tile < t1; ++tile) {
+        const int base = tile << 4;                               // first position of the tile
+        const int cell = p.ring_tokens > 0 ? base % p.ring_tokens : base;
+        const int page = table[cell / p.page_tokens];
+        const size_t tile_off =
+            (((size_t)page * p.n_kv + kvh) * p.page_tokens + cell % p.page_tokens) * HD;
+        const __nv_bfloat16* kt = p.k_pool + tile_off;
+        const __nv_bfloat16* vt = p.v_pool + tile_off;
+        const int last = pos - base;                              // keys beyond `last` do not exist
+        // ---- scores: 16 keys x G heads ----
+        const int ka = min(g, last), kb2 = min(g + 8, last);      // clamped: loads stay in the sequence
+        // every load of the tile is issued before anything waits on one
+        uint4 ka_r[KB], kb_r[KB], v_r[16 / KPP];
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+            ka_r[j] = ld_stream16(kt + (size_t)ka * HD + 32 * j + 8 * t);
+            kb_r[j] = ld_stream16(kt + (size_t)kb2 * HD + 32 * j + 8 * t);
+        }
+#pragma unroll
+        for (int i = 0; i < 16 / KPP; ++i)
+            v_r[i] = ld_stream16(vt + (size_t)min(i * KPP + sub, last) * HD + dim0);
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+            mma16816(c, ka_r[j].x, kb_r[j].x, ka_r[j].y, kb_r[j].y, qf[j].x, qf[j].y);
+            mma16816(c, ka_r[j].z, kb_r[j].z, ka_r[j].w, kb_r[j].w, qf[j].z, qf[j].w);
+        }
+        // c[0], c[1]: key g, heads 2t, 2t+1;  c[2], c[3]: key g + 8
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = g + (i >= 2 ? 8 : 0), head = 2 * t + (i & 1);
+            if (head < G) {
+                float s = c[i] * p.scale;
+                if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+                const int kpos = base + key;
+                s_sm[key][head] = (kpos >= lo && kpos <= pos) ? s : -INFINITY;
+            }
+        }
+        __syncwarp();
+        float corr[G];
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float mx = m[h];
+#pragma unroll
+            for (int key = 0; key < 16; ++key) mx = fmaxf(mx, s_sm[key][h]);
+            corr[h] = expf(m[h] - mx);
+            m[h] = mx;
+            l[h] *= corr[h];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] *= corr[h];
+        }
+        if (lane < 16) {
+#pragma unroll
+            for (int h = 0; h < G; ++h) p_sm[lane][h] = expf(s_sm[lane][h] - m[h]);
+        }
+        __syncwarp();
+        // ---- weighted sum of v: KPP keys per pass, 8 dimensions per lane ----
+#pragma unroll
+        for (int k0 = 0; k0 < 16; k0 += KPP) {
+            const int key = k0 + sub;
+            float vf[8];
+            unpack8(v_r[k0 / KPP], vf);
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                const float w = p_sm[key][h];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[h][e] += w * vf[e];
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+#pragma unroll
+            for (int key = 0; key < 16; ++key) l[h] += p_sm[key][h];
+        }
+        __syncwarp();
+    }
+
+    // lanes that worked on different keys of a pass hold partial sums of the same dimensions
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
+    }
+    if (sub != 0) return;
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        const int head = kvh * G + h;
+        if (p.splits == 1) {
+            const float inv = 1.0f / l[h];
+            __nv_bfloat16* op = p.out + (size_t)r * p.n_heads * HD + (size_t)head * HD + dim0;
+            uint4 packed;
+            __nv_bfloat162* pk = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                pk[e] = __floats2bfloat162_rn(acc[h][2 * e] * inv, acc[h][2 * e + 1] * inv);
+            *reinterpret_cast<uint4*>(op) = packed;
+        } else {
+            float* pp = p.partial + (((size_t)r * p.n_heads + head) * p.splits + split) * (HD + 2);
+            if (lane == 0) { pp[0] = m[h]; pp[1] = l[h]; }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) pp[2 + dim0 + e] = acc[h][e];
+        }
+    }
+}
+
+// 1 if this kernel takes the shape (else the caller uses attention_rows).
+SIB_EXPORT int sib_attention_decode_supports(int n_heads, int n_kv, int head_dim, int page_tokens) {
+    if (n_kv <= 0 || n_heads % n_kv) return 0;
+    const int G = n_heads / n_kv;
+    const bool g_ok = G == 1 || G == 2 || G == 4 || G == 8;
+    const bool hd_ok = head_dim == 64 || head_dim == 128 || head_dim == 256;
+    return g_ok && hd_ok && page_tokens % 16 == 0;
+}
+
+int sib_launch_attention_combine_bf16(const float* partial, void* out, int units, int splits,
+                                      int head_dim, cudaStream_t s);
+
+SIB_EXPORT int sib_attention_decode(
+    const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+    int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
+    const int* seq_slot, void* out, float* partial, int rows, int n_heads, int n_kv, int head_dim,
+    float scale, float softcap, int window, int splits, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(sib_attention_decode_supports(n_heads, n_kv, head_dim, page_tokens),
+                "attention_decode: heads=%d kv_heads=%d head_dim=%d page_tokens=%d is not a shape "
+                "this kernel takes (groups of 1, 2, 4 or 8 heads; head_dim 64, 128 or 256; pages "
+                "in multiples of 16)", n_heads, n_kv, head_dim, page_tokens);
+    SIB_REQUIRE(rows > 0 && splits >= 1 && (splits == 1 || partial != nullptr),
+                "attention_decode: rows=%d splits=%d", rows, splits);
+    SIB_REQUIRE(k_pool && v_pool && page_table && max_pages > 0,
+                "attention_decode: incomplete cache description");
+    SIB_REQUIRE(ring_tokens >= 0 && ring_tokens % 16 == 0 && window >= 0,
+                "attention_decode: ring=%d window=%d", ring_tokens, window);
+    SIB_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 &&
+                    ((uintptr_t)v_pool % 16) == 0 && ((uintptr_t)out % 16) == 0,
+                "attention_decode: operands must be 16-byte aligned");
+    AttnDecodeArgs p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+                     (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, partial, row_pos, row_seq,
+                     seq_slot, page_table, q_stride, rows, n_heads, n_kv, max_pages, page_tokens,
+                     ring_tokens, window, splits, scale, softcap};
+    const long long units = (long long)rows * n_kv * splits;
+    const long long blocks = (units + 3) / 4;
+    SIB_REQUIRE(blocks < (1ll << 31), "attention_decode: too many rows (%d)", rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int G = n_heads / n_kv;
+#define GO(HD, GG) attention_decode_kernel<HD, GG><<<(unsigned)blocks, 128, 0, s>>>(p)
+#define BY_G(HD)                  \
+    do {                          \
+        if (G == 1) GO(HD, 1);    \
+        else if (G == 2) GO(HD, 2); \
+        else if (G == 4) GO(HD, 4); \
+        else GO(HD, 8);           \
+    } while (0)
+    if (head_dim == 64) BY_G(64);
+    else if (head_dim == 128) BY_G(128);
+    else BY_G(256);
+#undef BY_G
+#undef GO
+    int rc = sib_check_launch("attention_decode");
+    if (rc || splits == 1) return rc;
+    return sib_launch_attention_combine_bf16(partial, out, rows * n_heads, splits, head_dim, s);
+}

@@ -232,6 +232,16 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     }
 }
 
+// Shared with attention_decode.cu, whose partial results have the same layout.
+int sib_launch_attention_combine_bf16(const float* partial, void* out, int units, int splits,
+                                      int head_dim, cudaStream_t s) {
+    int threads = 32;
+    while (threads < 256 && threads < head_dim) threads *= 2;
+    attention_combine_kernel<__nv_bfloat16><<<units, threads, 0, s>>>(
+        partial, (__nv_bfloat16*)out, splits, head_dim);
+    return sib_check_launch("attention_combine");
+}
+
 SIB_EXPORT long long sib_attention_rows_scratch_bytes(int rows, int n_heads, int head_dim,
                                                       int splits) {
     if (splits <= 1) return 0;

@@ -238,6 +238,42 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
     return out
 
 
+def attention_decode_supports(n_heads: int, n_kv: int, head_dim: int, page_tokens: int) -> bool:
+    return bool(library().sib_attention_decode_supports(c_int(n_heads), c_int(n_kv),
+                                                        c_int(head_dim), c_int(page_tokens)))
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                     page_table: torch.Tensor, page_tokens: int, ring_tokens: int, row_pos,
+                     row_seq, seq_slot, out: torch.Tensor, scratch: Optional[torch.Tensor],
+                     n_heads: int, n_kv: int, head_dim: int, scale: float, softcap: float,
+                     window: int, splits: int) -> torch.Tensor:
+    """Attention of single rows over the bfloat16 cache (see csrc/attention_decode.cu)."""
+    global _launches
+    rows = out.shape[0]
+    _want(out, torch.bfloat16, "out")
+    _want(k_pool, torch.bfloat16, "k_pool")
+    _want(v_pool, torch.bfloat16, "v_pool")
+    _want(page_table, torch.int32, "page_table")
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: q must be bfloat16")
+    if tuple(k_pool.shape[1:]) != (n_kv, page_tokens, head_dim):
+        raise KernelError("attention_decode: pool layout must be [pages, kv_heads, page_tokens, head_dim]")
+    if splits > 1:
+        need = attention_rows_scratch_bytes(rows, n_heads, head_dim, splits)
+        if scratch is None or scratch.numel() * scratch.element_size() < need:
+            raise KernelError(f"attention_decode: {need} bytes of scratch memory are needed")
+    _check(library().sib_attention_decode(
+        _ptr(q), c_int(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+        c_int(page_table.shape[1]), c_int(page_tokens), c_int(ring_tokens), _ptr(row_pos),
+        _ptr(row_seq), _ptr(seq_slot), _ptr(out), _ptr(scratch), c_int(rows), c_int(n_heads),
+        c_int(n_kv), c_int(head_dim), c_float(scale), c_float(softcap), c_int(window),
+        c_int(splits), _stream()))
+    if splits > 1:
+        _launches += 1
+    return out
+
+
 SKINNY_MAX_ROWS = 64
 
 

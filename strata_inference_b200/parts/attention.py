@@ -72,14 +72,17 @@ class Attention:
         return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
 
     # ------------------------------------------------------------------
-    def _splits(self, ctx, capacity: int) -> int:
-        """How many runs of keys each (row, head) is cut into when it reads the cache."""
+    def _splits(self, ctx, capacity: int, per_kv_head: bool = False) -> int:
+        """How many runs of keys each unit of work (a row's head, or the heads
+        of one kv head) is cut into when it reads the cache: enough to fill
+        the device, no run shorter than a few tiles of keys."""
         longest = capacity if ctx.graph_capture else ctx.max_end
         if self.window > 0:
             longest = min(longest, self.window)
-        units = max(1, ctx.n_rows * self.nh)
+        units = max(1, ctx.n_rows * (self.nkv if per_kv_head else self.nh))
         want = -(-_TARGET_WARPS // units)
-        return max(1, min(want, -(-longest // 32), 128))
+        shortest = 64 if per_kv_head else 32
+        return max(1, min(want, -(-longest // shortest), 128))
 
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
@@ -120,6 +123,16 @@ class Attention:
                                   view.page_tokens, view.ring_tokens, ctx.row_pos, ctx.row_seq,
                                   ctx.seq_slot, ctx.seq_start, ctx.seq_row0, out, None, nh,
                                   self.nkv, hd, self.scale, self.softcap, self.window, 1)
+        elif qkv.dtype == torch.bfloat16 and native.attention_decode_supports(
+                nh, self.nkv, hd, view.page_tokens):
+            splits = self._splits(ctx, ctx.cache.max_seq_len, per_kv_head=True)
+            scratch = None
+            if splits > 1:
+                scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, hd, splits))
+            native.attention_decode(qkv, width, view.k, view.v, view.page_table, view.page_tokens,
+                                    view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot, out,
+                                    scratch, nh, self.nkv, hd, self.scale, self.softcap,
+                                    self.window, splits)
         else:
             splits = self._splits(ctx, ctx.cache.max_seq_len)
             scratch = None

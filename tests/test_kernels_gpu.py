@@ -166,6 +166,56 @@ def test_attention_rows_over_cache_and_fresh(dtype, nh, nkv, hd, window, cap, sp
     _close(out[T:].view(T2, nh, hd), ref[:T2], dtype, "fresh rows, sequence 1", factor=4)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,cap,splits", [
+    (4, 2, 64, 0, 0.0, 1), (8, 4, 256, 40, 50.0, 5), (8, 1, 128, 0, 30.0, 3),
+    (2, 2, 128, 21, 0.0, 16), (8, 4, 256, 0, 0.0, 2), (4, 1, 256, 100, 50.0, 1)])
+def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits):
+    """The bfloat16 decode kernel: rows at tile and page edges, with and
+    without a ring, several rows of different sequences in one launch."""
+    n = _native()
+    assert n.attention_decode_supports(nh, nkv, hd, 16)
+    assert not n.attention_decode_supports(nh, nkv, 48, 16)
+    assert not n.attention_decode_supports(nh, nkv, hd, 8)
+    g = torch.Generator().manual_seed(13)
+    T = 150
+    dtype = torch.bfloat16
+    q = torch.randn(T, nh, hd, generator=g).to(dtype)
+    k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+    v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+    scale = 3.0 / math.sqrt(hd)
+    ref = plain.attention(q.double(), k.double(), v.double(), scale, cap, window)
+    page = 16
+    ring = (-(-window // page) + 1) * page if window else 0
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    rows = [T - 1, 100, 64, 63, 48, 47, 33, 32, 31, 17, 16, 15, 1, 0]
+    for r in rows:
+        keep = range(max(0, r + 1 - ring), r + 1) if ring else range(r + 1)
+        kp, vp, table = _paged(k, v, page, ring, nkv, hd, dtype, keep)
+        kp, vp = torch.nan_to_num(kp, nan=1e4), torch.nan_to_num(vp, nan=1e4)   # loud if read
+        out = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
+        scratch = torch.empty(max(1, n.attention_rows_scratch_bytes(1, nh, hd, splits)),
+                              dtype=torch.uint8, device=DEV)
+        qr = q[r].reshape(1, nh * hd).contiguous().to(DEV)
+        n.attention_decode(qr, nh * hd, kp.to(DEV), vp.to(DEV), table.to(DEV), page, ring,
+                           i32([r]), i32([0]), i32([1]), out, scratch, nh, nkv, hd, scale, cap,
+                           window, splits)
+        _close(out.view(nh, hd), ref[r], dtype, f"decode row {r}")
+    # several rows in one launch: rows of two sequences (slots 1 and 2 hold the same pages)
+    if not ring:
+        kp, vp, table = _paged(k, v, page, 0, nkv, hd, dtype, range(T))
+        table[2] = table[1]
+        picks = [T - 1, 77, 5]
+        qs = torch.stack([q[r].reshape(nh * hd) for r in picks]).contiguous().to(DEV)
+        out = torch.empty(3, nh * hd, dtype=dtype, device=DEV)
+        scratch = torch.empty(max(1, n.attention_rows_scratch_bytes(3, nh, hd, splits)),
+                              dtype=torch.uint8, device=DEV)
+        n.attention_decode(qs, nh * hd, kp.to(DEV), vp.to(DEV), table.to(DEV), page, 0,
+                           i32(picks), i32([0, 1, 1]), i32([1, 2]), out, scratch, nh, nkv, hd,
+                           scale, cap, window, splits)
+        for i, r in enumerate(picks):
+            _close(out[i].view(nh, hd), ref[r], dtype, f"decode rows together, row {r}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
 def test_rope_store(dtype, style):
