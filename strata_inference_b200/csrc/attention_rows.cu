@@ -212,22 +212,24 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          int splits, int head_dim) {
-    const size_t unit = blockIdx.x;  // r * n_heads + h
+    extern __shared__ float weight[];   // [splits] e^{m_s - M}, 0 for an empty split
+    const size_t unit = blockIdx.x;     // r * n_heads + h
     const float* pp = partial + unit * splits * (head_dim + 2);
+    // every thread finds M itself (the values come from L1/L2; splits is small)
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, pp[(size_t)s * (head_dim + 2)]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
         const float* ps = pp + (size_t)s * (head_dim + 2);
-        if (ps[1] > 0.f) L += ps[1] * expf(ps[0] - M);
+        weight[s] = ps[1] > 0.f ? expf(ps[0] - M) : 0.f;
     }
+    __syncthreads();
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L += pp[(size_t)s * (head_dim + 2) + 1] * weight[s];
     const float inv = 1.0f / L;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float* ps = pp + (size_t)s * (head_dim + 2);
-            if (ps[1] > 0.f) a += ps[2 + d] * expf(ps[0] - M);
-        }
+        for (int s = 0; s < splits; ++s)
+            if (weight[s] > 0.f) a += pp[(size_t)s * (head_dim + 2) + 2 + d] * weight[s];
         out[unit * head_dim + d] = from_f32<T>(a * inv);
     }
 }
@@ -237,7 +239,7 @@ int sib_launch_attention_combine_bf16(const float* partial, void* out, int units
                                       int head_dim, cudaStream_t s) {
     int threads = 32;
     while (threads < 256 && threads < head_dim) threads *= 2;
-    attention_combine_kernel<__nv_bfloat16><<<units, threads, 0, s>>>(
+    attention_combine_kernel<__nv_bfloat16><<<units, threads, splits * sizeof(float), s>>>(
         partial, (__nv_bfloat16*)out, splits, head_dim);
     return sib_check_launch("attention_combine");
 }
@@ -295,7 +297,8 @@ SIB_EXPORT int sib_attention_rows(
     if (rc || splits == 1) return rc;
     int threads = 32;
     while (threads < 256 && threads < head_dim) threads *= 2;
-    SIB_DISPATCH_DTYPE(dtype, (attention_combine_kernel<T><<<rows * n_heads, threads, 0, s>>>(
-                                  partial, (T*)out, splits, head_dim)));
+    SIB_DISPATCH_DTYPE(dtype, (attention_combine_kernel<T>
+                               <<<rows * n_heads, threads, splits * sizeof(float), s>>>(
+                                   partial, (T*)out, splits, head_dim)));
     return sib_check_launch("attention_combine");
 }

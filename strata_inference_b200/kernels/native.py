@@ -274,6 +274,27 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_poo
     return out
 
 
+def attention_prefill_supports(n_heads: int, n_kv: int, head_dim: int) -> bool:
+    return bool(library().sib_attention_prefill_supports(c_int(n_heads), c_int(n_kv),
+                                                         c_int(head_dim)))
+
+
+def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
+                      max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                      softcap: float, window: int) -> torch.Tensor:
+    """Attention of packed bfloat16 prompts that start at position 0 over their
+    own (rotated) keys and values (see csrc/attention_prefill.cu)."""
+    _want(qkv, torch.bfloat16, "qkv")
+    _want(out, torch.bfloat16, "out")
+    if out.shape[0] != qkv.shape[0] or out.shape[1] != n_heads * head_dim:
+        raise KernelError("attention_prefill: out must be [rows, heads * head_dim]")
+    _check(library().sib_attention_prefill(
+        _ptr(qkv), c_int(qkv.shape[1]), _ptr(out), _ptr(seq_row0), _ptr(seq_len), c_int(n_seqs),
+        c_int(max_len), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_float(scale),
+        c_float(softcap), c_int(window), _stream()))
+    return out
+
+
 SKINNY_MAX_ROWS = 64
 
 

@@ -116,7 +116,12 @@ class Attention:
 
         out = torch.empty((R, nh * hd), dtype=qkv.dtype, device=qkv.device)
         width = qkv.shape[1]
-        if fresh:
+        if fresh and qkv.dtype == torch.bfloat16 and \
+                native.attention_prefill_supports(nh, self.nkv, hd):
+            native.attention_prefill(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
+                                     ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,
+                                     self.window)
+        elif fresh:
             k_new = qkv[:, nh * hd:]
             v_new = qkv[:, (nh + nkv) * hd:]
             native.attention_rows(qkv, width, k_new, v_new, width, None, None, None,

@@ -216,6 +216,38 @@ def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits):
             _close(out[i].view(nh, hd), ref[r], dtype, f"decode rows together, row {r}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,cap", [
+    (4, 2, 64, 0, 0.0), (8, 4, 256, 100, 50.0), (4, 1, 128, 0, 30.0), (2, 2, 128, 70, 0.0),
+    (8, 4, 256, 0, 0.0), (3, 3, 64, 17, 20.0)])
+def test_attention_prefill_kernel(nh, nkv, hd, window, cap):
+    """The bfloat16 prompt kernel on packed prompts of unequal lengths (one
+    shorter than a tile, one that ends inside a tile, one of whole tiles)."""
+    n = _native()
+    assert n.attention_prefill_supports(nh, nkv, hd)
+    assert not n.attention_prefill_supports(8, 1, hd) and not n.attention_prefill_supports(nh, nkv, 48)
+    g = torch.Generator().manual_seed(14)
+    lens = [200, 5, 64, 131]
+    dtype = torch.bfloat16
+    scale = 3.0 / math.sqrt(hd)
+    qs, ks, vs, refs = [], [], [], []
+    for T in lens:
+        q = torch.randn(T, nh, hd, generator=g).to(dtype)
+        k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        refs.append(plain.attention(q.double(), k.double(), v.double(), scale, cap, window))
+        qs.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    packed = torch.cat(qs, dim=0).contiguous().to(DEV)
+    out = torch.full((sum(lens), nh * hd), float("nan"), dtype=dtype, device=DEV)
+    row0 = [0]
+    for T in lens[:-1]:
+        row0.append(row0[-1] + T)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n.attention_prefill(packed, out, i32(row0), i32(lens), len(lens), max(lens), nh, nkv, hd,
+                        scale, cap, window)
+    for r0, T, ref in zip(row0, lens, refs):
+        _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"prefill, sequence of {T}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
 def test_rope_store(dtype, style):
