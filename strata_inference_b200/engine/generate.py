@@ -140,6 +140,10 @@ def generate(stepper, prompts: Sequence[Sequence[int]], config: GenerationConfig
                             reason = CANCELLED
                         elif stepper.length(s) >= max_seq_len:
                             reason = CONTEXT_LENGTH
+                        elif limit >= 0 and len(out.token_ids) >= limit:
+                            # the reference runs one more step here and drops its
+                            # token; the outcome is the same without the step
+                            reason = MAX_TOKENS
                     if reason is None:
                         going.append((i, s, tok))
                     else:
