@@ -277,3 +277,70 @@ SIB_EXPORT int sib_attention_decode(
     if (rc || splits == 1) return rc;
     return sib_launch_attention_combine_bf16(partial, out, rows * n_heads, splits, head_dim, s);
 }
+
+// ---------------------------------------------------------------------------
+// The same kernels for callers that cannot allocate (attention_decode_no_alloc.h):
+// the splits' partial results go to an array that is part of this library.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+#include "attention_decode_no_alloc.h"
+
+static __device__ __align__(256) float g_no_alloc_scratch[NO_ALLOC_SCRATCH_FLOATS];
+
+// In host code the name g_no_alloc_scratch is only a handle; the address a kernel
+// can use is looked up once per device and kept here.
+static const int kMaxDevices = 64;
+static float* g_no_alloc_address[kMaxDevices] = {};
+static std::mutex g_no_alloc_mutex;
+
+static int no_alloc_scratch_address(float** address) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        sib_set_error("attention_decode_no_alloc: cannot tell the current device (%s)",
+                      e != cudaSuccess ? cudaGetErrorString(e) : "index out of range");
+        return e != cudaSuccess ? (int)e : -1;
+    }
+    std::lock_guard<std::mutex> guard(g_no_alloc_mutex);
+    if (g_no_alloc_address[device] == nullptr) {
+        void* found = nullptr;
+        e = cudaGetSymbolAddress(&found, g_no_alloc_scratch);
+        if (e != cudaSuccess || found == nullptr) {
+            sib_set_error("attention_decode_no_alloc: cudaGetSymbolAddress failed on device %d: %s",
+                          device, cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : -1;
+        }
+        g_no_alloc_address[device] = (float*)found;
+    }
+    *address = g_no_alloc_address[device];
+    return 0;
+}
+
+SIB_EXPORT long long sib_attention_decode_no_alloc_floats(int rows, int n_heads, int head_dim,
+                                                          int splits) {
+    if (splits <= 1) return 0;
+    return (long long)rows * n_heads * splits * (head_dim + 2);
+}
+
+SIB_EXPORT int sib_attention_decode_no_alloc(
+    const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+    int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
+    const int* seq_slot, void* out, int rows, int n_heads, int n_kv, int head_dim, float scale,
+    float softcap, int window, int splits, void* stream) {
+    SIB_REQUIRE(rows >= 0 && n_heads > 0 && head_dim > 0 && splits >= 1,
+                "attention_decode_no_alloc: rows=%d heads=%d head_dim=%d splits=%d", rows, n_heads,
+                head_dim, splits);
+    const long long need = sib_attention_decode_no_alloc_floats(rows, n_heads, head_dim, splits);
+    SIB_REQUIRE(need <= (long long)NO_ALLOC_SCRATCH_FLOATS,
+                "attention_decode_no_alloc: %d rows x %d heads x %d splits x (%d + 2) = %lld floats "
+                "of partial results, the built-in array holds %u; use fewer splits or rows, or "
+                "sib_attention_decode with memory of your own",
+                rows, n_heads, splits, head_dim, need, NO_ALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    const int rc = no_alloc_scratch_address(&scratch);   // the first call on a device sets it up
+    if (rc) return rc;
+    return sib_attention_decode(q, q_stride, k_pool, v_pool, page_table, max_pages, page_tokens,
+                                ring_tokens, row_pos, row_seq, seq_slot, out, scratch, rows, n_heads,
+                                n_kv, head_dim, scale, softcap, window, splits, stream);
+}

@@ -1,0 +1,107 @@
+"""sib_attention_decode_no_alloc, called the way its users call it: through the
+exported C symbol, with raw device pointers, without any help from this
+package's Python wrappers.
+
+The entry point is for hosts that cannot allocate device memory when they call
+(a C program without an allocator, a process whose memory is all in pools, a
+loop in which cudaMalloc's wait for the device is not acceptable): the partial
+results of the key splits live in an 8 MiB array inside the library instead of
+in memory the caller passes.  The checks: on two calls in a row, with different
+inputs and a different number of splits, it gives what the ordinary entry point
+gives with caller-provided scratch memory (the array keeps the first call's
+contents, which must not leak into the second); a request larger than the array
+is refused before anything is launched.
+
+This file is collected last on purpose: a run that stops at the first failure
+has then already run every other test.
+"""
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _library():
+    from strata_inference_b200.csrc.build import ensure_built
+    lib = ctypes.CDLL(ensure_built())
+    lib.sib_last_error.restype = ctypes.c_char_p
+    lib.sib_attention_decode_no_alloc_floats.restype = c_longlong
+    return lib
+
+
+def _case(seed, rows, nh, nkv, hd, lengths, page=16):
+    """Random queries, a paged cache holding `lengths[i]` positions for row i's
+    sequence (slot i), and the index tensors of a single-token step."""
+    g = torch.Generator().manual_seed(seed)
+    pages_per_seq = -(-max(lengths) // page)
+    n_pages = rows * pages_per_seq
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    table = perm.view(rows, pages_per_seq).contiguous()
+    k_pool = torch.randn(n_pages, nkv, page, hd, generator=g).to(torch.bfloat16)
+    v_pool = torch.randn(n_pages, nkv, page, hd, generator=g).to(torch.bfloat16)
+    q = torch.randn(rows, nh * hd, generator=g).to(torch.bfloat16)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    return dict(q=q.to(DEV), k=k_pool.to(DEV), v=v_pool.to(DEV), table=table.to(DEV),
+                row_pos=i32([n - 1 for n in lengths]), row_seq=i32(list(range(rows))),
+                seq_slot=i32(list(range(rows))), page=page, pages_per_seq=pages_per_seq)
+
+
+def _call(lib, symbol, c, rows, nh, nkv, hd, scale, cap, window, splits, scratch=None):
+    out = torch.full((rows, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    p = lambda t: c_void_p(t.data_ptr())  # noqa: E731
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    head = [p(c["q"]), c_int(nh * hd), p(c["k"]), p(c["v"]), p(c["table"]),
+            c_int(c["pages_per_seq"]), c_int(c["page"]), c_int(0), p(c["row_pos"]),
+            p(c["row_seq"]), p(c["seq_slot"]), p(out)]
+    if scratch is not None:
+        head.append(p(scratch))
+    tail = [c_int(rows), c_int(nh), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
+            c_int(window), c_int(splits), stream]
+    rc = getattr(lib, symbol)(*head, *tail)
+    torch.cuda.synchronize()
+    return rc, out
+
+
+def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
+    lib = _library()
+    nh, nkv, hd = 8, 4, 256
+    scale = 2.0 / math.sqrt(hd)
+    calls = [  # (seed, sequence lengths, window, soft cap, splits)
+        (1, [300, 17, 1024, 64], 0, 50.0, 7),
+        (2, [90, 500], 128, 0.0, 3),
+    ]
+    for seed, lengths, window, cap, splits in calls:
+        rows = len(lengths)
+        c = _case(seed, rows, nh, nkv, hd, lengths)
+        need = lib.sib_attention_decode_no_alloc_floats(c_int(rows), c_int(nh), c_int(hd),
+                                                        c_int(splits))
+        assert need == rows * nh * splits * (hd + 2)
+        scratch = torch.empty(need, dtype=torch.float32, device=DEV)
+        rc, want = _call(lib, "sib_attention_decode", c, rows, nh, nkv, hd, scale, cap, window,
+                         splits, scratch)
+        assert rc == 0, lib.sib_last_error().decode()
+        rc, got = _call(lib, "sib_attention_decode_no_alloc", c, rows, nh, nkv, hd, scale, cap,
+                        window, splits)
+        assert rc == 0, lib.sib_last_error().decode()
+        assert torch.isfinite(got.float()).all()
+        scale_of = want.float().abs().max().item()
+        err = (got.float() - want.float()).abs().max().item()
+        assert err <= 1e-2 * scale_of, f"call with seed {seed}: {err:.3e} vs {scale_of:.3e}"
+
+
+def test_no_alloc_entry_point_refuses_what_does_not_fit():
+    lib = _library()
+    nh, nkv, hd = 8, 4, 256
+    rows, splits = 64, 128                     # 64 * 8 * 128 * 258 floats: far beyond 8 MiB
+    c = _case(3, rows, nh, nkv, hd, [32] * rows)
+    rc, out = _call(lib, "sib_attention_decode_no_alloc", c, rows, nh, nkv, hd, 0.1, 0.0, 0, splits)
+    assert rc != 0
+    msg = lib.sib_last_error().decode()
+    assert "built-in array holds" in msg and str(rows * nh * splits * (hd + 2)) in msg
+    assert torch.isnan(out.float()).all()      # nothing was launched
