@@ -227,9 +227,10 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     for (int s = 0; s < splits; ++s) L += pp[(size_t)s * (head_dim + 2) + 1] * weight[s];
     const float inv = 1.0f / L;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        // an empty split wrote zeros and has weight 0: no branch, so the loads overlap
         float a = 0.f;
-        for (int s = 0; s < splits; ++s)
-            if (weight[s] > 0.f) a += pp[(size_t)s * (head_dim + 2) + 2 + d] * weight[s];
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) a += pp[(size_t)s * (head_dim + 2) + 2 + d] * weight[s];
         out[unit * head_dim + d] = from_f32<T>(a * inv);
     }
 }

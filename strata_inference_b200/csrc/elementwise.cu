@@ -47,6 +47,27 @@ __global__ void gelu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     }
 }
 
+// The bfloat16 case with groups of 8: a group is 32 contiguous bytes (8 gates,
+// 8 ups) and gives 16 contiguous bytes of output; one thread per group, every
+// access 16 bytes wide.
+__global__ void gelu_mul_group8_bf16_kernel(const uint4* __restrict__ gate_up,
+                                            uint4* __restrict__ out, size_t groups) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 gv = gate_up[2 * i], uv = gate_up[2 * i + 1];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+            const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+            const __nv_bfloat162 o = __floats2bfloat162_rn(gelu_tanh(g0) * u0, gelu_tanh(g1) * u1);
+            ow[k] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        out[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 SIB_EXPORT int sib_gelu_mul(const void* gate_up, void* out, int dtype, int rows, int inter,
                             int group, void* stream) {
     if (rows == 0) return 0;
@@ -54,6 +75,15 @@ SIB_EXPORT int sib_gelu_mul(const void* gate_up, void* out, int dtype, int rows,
     SIB_REQUIRE(group >= 0 && (group == 0 || inter % group == 0),
                 "gelu_mul: %d columns do not come in groups of %d", inter, group);
     const size_t total = (size_t)rows * inter;
+    if (dtype == SIB_BF16 && group == 8 && ((uintptr_t)gate_up % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0) {
+        const size_t groups = total / 8;
+        const size_t want = (groups + 255) / 256;
+        const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+        gelu_mul_group8_bf16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+            (const uint4*)gate_up, (uint4*)out, groups);
+        return sib_check_launch("gelu_mul");
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     SIB_DISPATCH_DTYPE(dtype, (gelu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(
                                   (const T*)gate_up, (T*)out, inter, group, total)));

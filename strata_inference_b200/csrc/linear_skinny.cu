@@ -16,7 +16,11 @@
 // rows, and y gets N / 2 columns.
 // Plain counterpart: tests/plain_gemma2.py (x @ W.T), gelu_tanh(), lm_head().
 // Reference: src/model/layer.rs:22-43 (x . W^T, weights [out, in]).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2 };
 
@@ -35,9 +39,9 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p) {
 // Weights are read once: keep them out of L1.
 __device__ __forceinline__ uint4 ld16_stream(const __nv_bfloat16* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p));
     return v;
 }
 
@@ -51,8 +55,13 @@ template <int NT, int MT, typename OutT, int EPI>
 __global__ void __launch_bounds__(256)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
                      OutT* __restrict__ y, int R, int N, int K, int x_stride, int y_stride,
-                     float cap) {
-    extern __shared__ float red[];  // [8 warps][MT][NT][32 lanes][4]
+                     float cap, int ksplit) {
+    // [8 warps][MT][NT][32 lanes][4], then [ksplit - 1][MT][NT][32][4] for the other
+    // blocks of the cluster (used in the cluster's first block only)
+    extern __shared__ float red[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = ksplit > 1 ? (int)cluster.block_rank() : 0;
+    if (ksplit > 1) cluster.sync();   // every block of the cluster is running: its memory can be written
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (16 * MT);
@@ -73,7 +82,8 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
-    for (int kb = warp * 64; kb < K; kb += 8 * 64) {
+#pragma unroll 2
+    for (int kb = (rank * 8 + warp) * 64; kb < K; kb += ksplit * 8 * 64) {
         const int k = kb + 16 * t;
         const bool v0 = k + 8 <= K, v1 = k + 16 <= K;  // K is a multiple of 8
         uint4 wa[MT][2], wb[MT][2];
@@ -112,11 +122,35 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
             mine[(m * NT + j) * 32 + lane] =
                 make_float4(acc[m][j][0], acc[m][j][1], acc[m][j][2], acc[m][j][3]);
     __syncthreads();
+    float4* peers = reinterpret_cast<float4*>(red) + (size_t)8 * (MT * NT * 32);
+    if (ksplit > 1) {
+        // the blocks of a cluster took alternating runs of k of the same weight rows:
+        // each adds its 8 warps and hands the sum to the first block
+        if (rank > 0) {
+            float4* remote = cluster.map_shared_rank(peers, 0) + (size_t)(rank - 1) * (MT * NT * 32);
+            for (int idx = threadIdx.x; idx < MT * NT * 32; idx += blockDim.x) {
+                float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    const float4 v =
+                        reinterpret_cast<const float4*>(red)[(size_t)w * (MT * NT * 32) + idx];
+                    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+                }
+                remote[idx] = s;
+            }
+        }
+        cluster.sync();
+        if (rank > 0) return;
+    }
     for (int idx = threadIdx.x; idx < MT * NT * 32; idx += blockDim.x) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
             const float4 v = reinterpret_cast<const float4*>(red)[(size_t)w * (MT * NT * 32) + idx];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        for (int b = 1; b < ksplit; ++b) {     // in block order
+            const float4 v = peers[(size_t)(b - 1) * (MT * NT * 32) + idx];
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
         const int l2 = idx & 31, j = (idx >> 5) % NT, m = idx / (32 * NT);
@@ -149,7 +183,12 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
 template <int NT, int MT, typename OutT, int EPI>
 static int launch_skinny(const void* W, const void* x, void* y, int R, int N, int K, int x_stride,
                          int y_stride, float cap, cudaStream_t s) {
-    const size_t smem = (size_t)8 * MT * NT * 32 * 4 * sizeof(float);
+    const int blocks = (N + 16 * MT - 1) / (16 * MT);
+    // few weight rows: several blocks (a cluster) share a tile of rows and split k, so
+    // that enough loads are in flight to fill the memory system
+    int ksplit = 1;
+    while (ksplit < 8 && blocks * ksplit < 3 * 148 && K >= 2 * ksplit * 8 * 64) ksplit *= 2;
+    const size_t smem = (size_t)(8 + ksplit - 1) * MT * NT * 32 * 4 * sizeof(float);
     auto kernel = skinny_linear_kernel<NT, MT, OutT, EPI>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -159,9 +198,25 @@ static int launch_skinny(const void* W, const void* x, void* y, int R, int N, in
             return (int)e;
         }
     }
-    const int blocks = (N + 16 * MT - 1) / (16 * MT);
-    kernel<<<blocks, 256, smem, s>>>((const __nv_bfloat16*)W, (const __nv_bfloat16*)x, (OutT*)y, R,
-                                     N, K, x_stride, y_stride, cap);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks, ksplit, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ksplit;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)W,
+                                       (const __nv_bfloat16*)x, (OutT*)y, R, N, K, x_stride,
+                                       y_stride, cap, ksplit);
+    if (e != cudaSuccess) {
+        sib_set_error("skinny_linear: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     return sib_check_launch("skinny_linear");
 }
 

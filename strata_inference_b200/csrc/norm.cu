@@ -69,6 +69,64 @@ __global__ void add_rms_norm_kernel(const T* __restrict__ a, const float* __rest
         out[base + c] = from_f32<T>(row[c] * inv2 * pre_gain[c]);
 }
 
+// The same for bfloat16 activations and a hidden size in whole groups of 8: every
+// access is 16 bytes wide (8 activations, 4 stream or gain values).
+__global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
+                                         const float* __restrict__ post_gain, float post_eps,
+                                         float* __restrict__ h, const float* __restrict__ pre_gain,
+                                         float pre_eps, __nv_bfloat16* __restrict__ out, int hidden) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    const int groups = hidden / 8;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < groups; v += blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(a + base + 8 * v);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float lo = __uint_as_float(w[k] << 16), hi = __uint_as_float(w[k] & 0xffff0000u);
+            row[8 * v + 2 * k] = lo;
+            row[8 * v + 2 * k + 1] = hi;
+            ss += lo * lo + hi * hi;
+        }
+    }
+    float inv = 1.f;
+    if (post_gain) {
+        ss = block_sum(ss, scratch);
+        inv = 1.0f / sqrtf(ss / (float)hidden + post_eps);
+    } else {
+        __syncthreads();   // the next pass reads the row in another order
+    }
+    float ss2 = 0.f;
+    for (int v = threadIdx.x; v < 2 * groups; v += blockDim.x) {   // float4 at a time
+        float4 hv = *reinterpret_cast<const float4*>(h + base + 4 * v);
+        float4 av = *reinterpret_cast<const float4*>(row + 4 * v);
+        if (post_gain) {
+            const float4 gv = *reinterpret_cast<const float4*>(post_gain + 4 * v);
+            av.x *= inv * gv.x; av.y *= inv * gv.y; av.z *= inv * gv.z; av.w *= inv * gv.w;
+        }
+        hv.x += av.x; hv.y += av.y; hv.z += av.z; hv.w += av.w;
+        *reinterpret_cast<float4*>(h + base + 4 * v) = hv;
+        *reinterpret_cast<float4*>(row + 4 * v) = hv;
+        ss2 += hv.x * hv.x + hv.y * hv.y + hv.z * hv.z + hv.w * hv.w;
+    }
+    if (!pre_gain) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    for (int v = threadIdx.x; v < groups; v += blockDim.x) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = 8 * v + 2 * k;
+            const __nv_bfloat162 o = __floats2bfloat162_rn(row[c] * inv2 * pre_gain[c],
+                                                           row[c + 1] * inv2 * pre_gain[c + 1]);
+            w[k] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(out + base + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 static int norm_threads(int hidden) {
     int t = 128;
     while (t < 1024 && t * 4 < hidden) t *= 2;
@@ -128,6 +186,17 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
                 "add_rms_norm: hidden=%d needs %zu bytes of shared memory; at most %d are supported",
                 hidden, smem, kMaxRowBytes);
     const int threads = norm_threads(hidden);
+    if (dtype == SIB_BF16 && hidden % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+        ((uintptr_t)h % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+        ((uintptr_t)post_gain % 16) == 0 && ((uintptr_t)pre_gain % 16) == 0) {
+        int rc = allow_row(add_rms_norm_bf16_kernel, smem);
+        if (rc) return rc;
+        add_rms_norm_bf16_kernel<<<n_rows, threads < 256 ? threads : 256, smem,
+                                   (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)a, post_gain, post_eps, h, pre_gain, pre_eps,
+            (__nv_bfloat16*)out, hidden);
+        return sib_check_launch("add_rms_norm");
+    }
     SIB_DISPATCH_DTYPE(dtype, {
         int rc = allow_row(add_rms_norm_kernel<T>, smem);
         if (rc) return rc;

@@ -76,6 +76,77 @@ __global__ void rope_store_kernel(RopeStoreArgs p) {
     }
 }
 
+// The common case in 16-byte accesses: bfloat16, half-split pairs, the whole
+// head rotated.  One block per row; a thread takes 8 pairs (x[i..i+8) with
+// x[i+half..i+half+8)) of a q or k head, or 8 elements of a v head.
+__global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
+    const int r = blockIdx.x;
+    const int hd = p.head_dim, half = hd / 2;
+    const int width = (p.n_heads + 2 * p.n_kv) * hd;
+    __nv_bfloat16* row = (__nv_bfloat16*)p.qkv + (size_t)r * width;
+    const int pos = p.row_pos[r];
+    size_t cell_off = 0;
+    bool keep = false;
+    if (p.k_pool) {
+        const int b = p.row_seq[r];
+        int cell = pos;
+        keep = true;
+        if (p.ring_tokens > 0) {
+            keep = pos >= p.seq_end[b] - p.ring_tokens;
+            cell = pos % p.ring_tokens;
+        }
+        if (keep) {
+            const int page = p.page_table[(size_t)p.seq_slot[b] * p.max_pages + cell / p.page_tokens];
+            cell_off = ((size_t)page * p.n_kv * p.page_tokens + cell % p.page_tokens) * hd;
+        }
+    }
+    const size_t head_step = (size_t)p.page_tokens * hd;    // between kv heads of a page
+    const int per_head = half / 8;
+    for (int u = threadIdx.x; u < (p.n_heads + p.n_kv) * per_head; u += blockDim.x) {
+        const int y = u / per_head, i0 = (u % per_head) * 8;
+        __nv_bfloat16* x = row + (size_t)y * hd;
+        const uint4 lo = *reinterpret_cast<const uint4*>(x + i0);
+        const uint4 hi = *reinterpret_cast<const uint4*>(x + i0 + half);
+        const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+        uint32_t ol[4], oh[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float a[2] = {__uint_as_float(lw[k] << 16), __uint_as_float(lw[k] & 0xffff0000u)};
+            float bq[2] = {__uint_as_float(hw[k] << 16), __uint_as_float(hw[k] & 0xffff0000u)};
+            float ra[2], rb[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float ang = (float)pos * p.inv_freq[i0 + 2 * k + e];
+                const float c = cosf(ang), s = sinf(ang);
+                ra[e] = a[e] * c - bq[e] * s;
+                rb[e] = a[e] * s + bq[e] * c;
+            }
+            const __nv_bfloat162 pa = __floats2bfloat162_rn(ra[0], ra[1]);
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(rb[0], rb[1]);
+            ol[k] = *reinterpret_cast<const uint32_t*>(&pa);
+            oh[k] = *reinterpret_cast<const uint32_t*>(&pb);
+        }
+        const uint4 vlo = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+        const uint4 vhi = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+        *reinterpret_cast<uint4*>(x + i0) = vlo;
+        *reinterpret_cast<uint4*>(x + i0 + half) = vhi;
+        if (keep && y >= p.n_heads) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.k_pool + cell_off + (size_t)(y - p.n_heads) * head_step;
+            *reinterpret_cast<uint4*>(dst + i0) = vlo;
+            *reinterpret_cast<uint4*>(dst + i0 + half) = vhi;
+        }
+    }
+    if (keep) {
+        const int per_v = hd / 8;
+        const __nv_bfloat16* v = row + (size_t)(p.n_heads + p.n_kv) * hd;
+        for (int u = threadIdx.x; u < p.n_kv * per_v; u += blockDim.x) {
+            const int y = u / per_v, i0 = (u % per_v) * 8;
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.v_pool + cell_off + (size_t)y * head_step;
+            *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(v + (size_t)y * hd + i0);
+        }
+    }
+}
+
 SIB_EXPORT int sib_rope_store(void* qkv, int dtype, const int* row_pos, const int* row_seq,
                               const int* seq_slot, const int* seq_end, const float* inv_freq,
                               int rot, int style, void* k_pool, void* v_pool,
@@ -95,6 +166,11 @@ SIB_EXPORT int sib_rope_store(void* qkv, int dtype, const int* row_pos, const in
                 "rope_store: ring of %d tokens is not whole pages of %d", ring_tokens, page_tokens);
     RopeStoreArgs p{qkv, row_pos, row_seq, seq_slot, seq_end, inv_freq, k_pool, v_pool, page_table,
                     n_heads, n_kv, head_dim, rot, style, max_pages, page_tokens, ring_tokens};
+    if (dtype == SIB_BF16 && style == 0 && rot == head_dim && head_dim % 16 == 0 &&
+        ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0) {
+        rope_store_bf16_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(p);
+        return sib_check_launch("rope_store");
+    }
     int threads = 32;
     while (threads < 128 && threads < head_dim / 2) threads *= 2;
     dim3 grid(rows, n_heads + 2 * n_kv);

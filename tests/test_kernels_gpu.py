@@ -250,10 +250,11 @@ def test_attention_prefill_kernel(nh, nkv, hd, window, cap):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
-def test_rope_store(dtype, style):
+@pytest.mark.parametrize("hd,rot", [(48, 32), (64, 64), (16, 16)])
+def test_rope_store(dtype, style, hd, rot):
     n = _native()
     g = torch.Generator().manual_seed(4)
-    nh, nkv, hd, rot = 3, 2, 48, 32
+    nh, nkv = 3, 2
     theta = 777.0
     positions = [0, 1, 2, 3, 4, 17, 18, 19, 20]        # two sequences: 5 rows from 0, 4 rows from 17
     R = len(positions)
