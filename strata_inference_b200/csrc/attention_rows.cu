@@ -211,37 +211,78 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
 // out[r, h, :] = sum_s acc_s e^{m_s - M} / sum_s l_s e^{m_s - M}, s in split order.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                         int splits, int head_dim) {
+                                         int splits, int head_dim, int groups) {
     extern __shared__ float weight[];   // [splits] e^{m_s - M}, 0 for an empty split
     const size_t unit = blockIdx.x;     // r * n_heads + h
     const float* pp = partial + unit * splits * (head_dim + 2);
-    // every thread finds M itself (the values come from L1/L2; splits is small)
+    __shared__ float scratch[33];
+    // thread s takes split s: the (max, sum) pairs are read in one round of loads
+    float mine = -INFINITY;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x)
+        mine = fmaxf(mine, pp[(size_t)s * (head_dim + 2)]);
+    mine = warp_max(mine);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = mine;
+    __syncthreads();
     float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, pp[(size_t)s * (head_dim + 2)]);
+    for (int w = 0; w < (int)((blockDim.x + 31) >> 5); ++w) M = fmaxf(M, scratch[w]);
+    float part = 0.f;
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
         const float* ps = pp + (size_t)s * (head_dim + 2);
-        weight[s] = ps[1] > 0.f ? expf(ps[0] - M) : 0.f;
+        const float w = ps[1] > 0.f ? expf(ps[0] - M) : 0.f;
+        weight[s] = w;
+        part += ps[1] * w;
+    }
+    const float L = block_sum(part, scratch);   // also makes weight[] visible to all
+    const float inv = 1.0f / L;
+    // `groups` groups of threads take alternating splits; a thread owns two dimensions.
+    // An empty split wrote zeros and has weight 0: no branch, so the loads overlap.
+    float2* sums = reinterpret_cast<float2*>(weight + ((splits + 1) & ~1));
+    const int nv = head_dim / 2;
+    const int grp = threadIdx.x / nv, v = threadIdx.x % nv;
+    if (grp < groups) {
+        float2 a = make_float2(0.f, 0.f);
+#pragma unroll 8
+        for (int s = grp; s < splits; s += groups) {
+            const float2 x =
+                *reinterpret_cast<const float2*>(pp + (size_t)s * (head_dim + 2) + 2 + 2 * v);
+            a.x += x.x * weight[s];
+            a.y += x.y * weight[s];
+        }
+        sums[grp * nv + v] = a;
     }
     __syncthreads();
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) L += pp[(size_t)s * (head_dim + 2) + 1] * weight[s];
-    const float inv = 1.0f / L;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        // an empty split wrote zeros and has weight 0: no branch, so the loads overlap
-        float a = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < splits; ++s) a += pp[(size_t)s * (head_dim + 2) + 2 + d] * weight[s];
-        out[unit * head_dim + d] = from_f32<T>(a * inv);
+    if (grp == 0) {
+        float2 a = sums[v];
+        for (int k = 1; k < groups; ++k) {     // in group order
+            a.x += sums[k * nv + v].x;
+            a.y += sums[k * nv + v].y;
+        }
+        out[unit * head_dim + 2 * v] = from_f32<T>(a.x * inv);
+        out[unit * head_dim + 2 * v + 1] = from_f32<T>(a.y * inv);
     }
+}
+
+struct CombineShape {
+    int threads, groups;
+    size_t smem;
+};
+static CombineShape combine_shape(int splits, int head_dim) {
+    const int nv = head_dim / 2;
+    int groups = 512 / nv;
+    groups = groups < 1 ? 1 : (groups > 8 ? 8 : groups);
+    CombineShape c;
+    c.groups = groups;
+    c.threads = (groups * nv + 31) / 32 * 32;
+    c.smem = (size_t)((splits + 1) & ~1) * sizeof(float) + (size_t)groups * nv * sizeof(float2);
+    return c;
 }
 
 // Shared with attention_decode.cu, whose partial results have the same layout.
 int sib_launch_attention_combine_bf16(const float* partial, void* out, int units, int splits,
                                       int head_dim, cudaStream_t s) {
-    int threads = 32;
-    while (threads < 256 && threads < head_dim) threads *= 2;
-    attention_combine_kernel<__nv_bfloat16><<<units, threads, splits * sizeof(float), s>>>(
-        partial, (__nv_bfloat16*)out, splits, head_dim);
+    const CombineShape c = combine_shape(splits, head_dim);
+    attention_combine_kernel<__nv_bfloat16><<<units, c.threads, c.smem, s>>>(
+        partial, (__nv_bfloat16*)out, splits, head_dim, c.groups);
     return sib_check_launch("attention_combine");
 }
 
@@ -296,10 +337,8 @@ SIB_EXPORT int sib_attention_rows(
 #undef LAUNCH
     int rc = sib_check_launch("attention_rows");
     if (rc || splits == 1) return rc;
-    int threads = 32;
-    while (threads < 256 && threads < head_dim) threads *= 2;
-    SIB_DISPATCH_DTYPE(dtype, (attention_combine_kernel<T>
-                               <<<rows * n_heads, threads, splits * sizeof(float), s>>>(
-                                   partial, (T*)out, splits, head_dim)));
+    const CombineShape c = combine_shape(splits, head_dim);
+    SIB_DISPATCH_DTYPE(dtype, (attention_combine_kernel<T><<<rows * n_heads, c.threads, c.smem, s>>>(
+                                  partial, (T*)out, splits, head_dim, c.groups)));
     return sib_check_launch("attention_combine");
 }
