@@ -316,6 +316,36 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     return out
 
 
+def gemm_tcgen05_supports(R: int, N: int, K: int, x_stride: int) -> bool:
+    return bool(library().sib_gemm_tcgen05_supports(c_int(R), c_int(N), c_int(K),
+                                                    c_longlong(x_stride)))
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+                 cap: float = 0.0) -> torch.Tensor:
+    """out = x . w^T for bfloat16 x and w on tcgen05 (see csrc/gemm_tcgen05.cu)."""
+    _want(x, torch.bfloat16, "x", contiguous=False)
+    _want(w, torch.bfloat16, "w")
+    _want(out, out.dtype, "out", contiguous=False)
+    R, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_tcgen05: shapes do not fit")
+    _check(library().sib_gemm_tcgen05(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
+                                      c_int(N), c_int(K), c_longlong(x.stride(0)),
+                                      c_int(out.stride(0)), c_int(epilogue), c_float(cap),
+                                      _stream()))
+    return out
+
+
+def gemm_tcgen05_error(clear: bool = True) -> int:
+    """0, or the code left by a block of gemm_tcgen05 whose bounded wait ran out
+    (synchronises the device)."""
+    torch.cuda.synchronize()
+    return int(library().sib_gemm_tcgen05_error(c_int(1 if clear else 0)))
+
+
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
                 rng_state: Optional[torch.Tensor], out: torch.Tensor,
                 rng_index: Optional[torch.Tensor] = None) -> torch.Tensor:

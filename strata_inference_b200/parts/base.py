@@ -59,7 +59,10 @@ class Runtime:
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
         torch.set_float32_matmul_precision("highest")
-        self.skinny_max_rows = native.SKINNY_MAX_ROWS
+        # Up to this many rows a product goes to the weight-streaming kernel (which
+        # takes up to native.SKINNY_MAX_ROWS); measured on a B200 at Gemma2-2B sizes it
+        # is ahead of the library product up to 16 rows and behind it from 32 on.
+        self.skinny_max_rows = 16
         self._scratch: Optional[torch.Tensor] = None
 
     def cast_matrix(self, w: torch.Tensor) -> torch.Tensor:
