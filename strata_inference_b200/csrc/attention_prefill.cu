@@ -87,12 +87,17 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
     constexpr int DN = HD / 8;           // n-tiles of the output
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* Ks = Qs + 64 * HD;            // two tiles
-    __nv_bfloat16* Vs = Ks + 2 * 64 * HD;        // two tiles
+    // Two key/value tiles in flight where two blocks per SM still fit (heads up to 128);
+    // one tile for wider heads, where the second block of the SM hides the loads instead.
+    constexpr bool DOUBLE = HD <= 128;
+    constexpr int NBUF = DOUBLE ? 2 : 1;
+    __nv_bfloat16* Ks = Qs + 64 * HD;
+    __nv_bfloat16* Vs = Ks + NBUF * 64 * HD;
 
     const int b = blockIdx.y, kvh = blockIdx.z;
     const int n = p.seq_len[b];
-    const int p0 = blockIdx.x * MP;
+    // late tiles see the most keys: they go first, so that the short ones fill the tail
+    const int p0 = (int)(gridDim.x - 1 - blockIdx.x) * MP;
     if (p0 >= n) return;
     const int row0 = p.seq_row0[b];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -117,6 +122,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
     const __nv_bfloat16* kbase = p.qkv + (size_t)row0 * p.width + (size_t)(p.n_heads + kvh) * HD;
     const __nv_bfloat16* vbase = kbase + (size_t)p.n_kv * HD;
     load_rows<HD>(Ks, kbase, p.width, kt0 * 64, n - kt0 * 64);
+    if (!DOUBLE) cp_async_commit();              // queries and keys first, values as a second group
     load_rows<HD>(Vs, vbase, p.width, kt0 * 64, n - kt0 * 64);
     cp_async_commit();
 
@@ -128,14 +134,24 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
     const int qpos0 = p0 + (16 * warp + g) % MP, qpos1 = p0 + (16 * warp + g + 8) % MP;
 
     for (int kt = kt0; kt < kt1; ++kt) {
-        const int buf = (kt - kt0) & 1;
-        if (kt + 1 < kt1) {
-            load_rows<HD>(Ks + (buf ^ 1) * 64 * HD, kbase, p.width, (kt + 1) * 64, n - (kt + 1) * 64);
-            load_rows<HD>(Vs + (buf ^ 1) * 64 * HD, vbase, p.width, (kt + 1) * 64, n - (kt + 1) * 64);
-            cp_async_commit();
-            cp_async_wait<1>();
+        const int buf = DOUBLE ? (kt - kt0) & 1 : 0;
+        if (DOUBLE) {
+            if (kt + 1 < kt1) {
+                load_rows<HD>(Ks + (buf ^ 1) * 64 * HD, kbase, p.width, (kt + 1) * 64, n - (kt + 1) * 64);
+                load_rows<HD>(Vs + (buf ^ 1) * 64 * HD, vbase, p.width, (kt + 1) * 64, n - (kt + 1) * 64);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
         } else {
-            cp_async_wait<0>();
+            if (kt > kt0) {
+                load_rows<HD>(Ks, kbase, p.width, kt * 64, n - kt * 64);
+                cp_async_commit();
+                load_rows<HD>(Vs, vbase, p.width, kt * 64, n - kt * 64);
+                cp_async_commit();
+            }
+            cp_async_wait<1>();                  // the keys (and the queries) are here
         }
         __syncthreads();
         __nv_bfloat16* Kt = Ks + buf * 64 * HD;
@@ -201,6 +217,10 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
         }
         l_run[0] += lsum[0];
         l_run[1] += lsum[1];
+        if (!DOUBLE) {
+            cp_async_wait<0>();                  // the values are here
+            __syncthreads();
+        }
         // ---- weighted sum: 16 keys per k-step, probabilities as the A operand ----
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
@@ -252,7 +272,7 @@ SIB_EXPORT int sib_attention_prefill_supports(int n_heads, int n_kv, int head_di
 
 template <int HD, int G>
 static int launch_prefill(const AttnPrefillArgs& p, int n_seqs, int max_len, cudaStream_t s) {
-    const size_t smem = (size_t)5 * 64 * HD * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(HD <= 128 ? 5 : 3) * 64 * HD * sizeof(__nv_bfloat16);
     auto kernel = attention_prefill_kernel<HD, G>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
