@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float(*s_sm)[8] = sm_all[warp][0];
     float(*p_sm)[8] = sm_all[warp][1];
+    pdl_trigger();
+    pdl_wait();
     const long long unit = (long long)blockIdx.x * 4 + warp;
     if (unit >= (long long)p.rows * p.n_kv * p.splits) return;
     const int split = (int)(unit % p.splits);
@@ -260,7 +262,8 @@ SIB_EXPORT int sib_attention_decode(
     SIB_REQUIRE(blocks < (1ll << 31), "attention_decode: too many rows (%d)", rows);
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;
-#define GO(HD, GG) attention_decode_kernel<HD, GG><<<(unsigned)blocks, 128, 0, s>>>(p)
+#define GO(HD, GG) \
+    sib_launch_chained(attention_decode_kernel<HD, GG>, dim3((unsigned)blocks), dim3(128), 0, s, p)
 #define BY_G(HD)                  \
     do {                          \
         if (G == 1) GO(HD, 1);    \

@@ -75,6 +75,8 @@ __device__ __forceinline__ const T* key_ptr(const AttnRowsArgs& p, const T* fres
 template <typename T, int NI>
 __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
     constexpr int V = Vec16<T>::N;
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= (long long)p.rows * p.n_heads * p.splits) return;
@@ -213,6 +215,8 @@ template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          int splits, int head_dim, int groups) {
     extern __shared__ float weight[];   // [splits] e^{m_s - M}, 0 for an empty split
+    pdl_trigger();
+    pdl_wait();
     const size_t unit = blockIdx.x;     // r * n_heads + h
     const float* pp = partial + unit * splits * (head_dim + 2);
     __shared__ float scratch[33];
@@ -281,8 +285,8 @@ static CombineShape combine_shape(int splits, int head_dim) {
 int sib_launch_attention_combine_bf16(const float* partial, void* out, int units, int splits,
                                       int head_dim, cudaStream_t s) {
     const CombineShape c = combine_shape(splits, head_dim);
-    attention_combine_kernel<__nv_bfloat16><<<units, c.threads, c.smem, s>>>(
-        partial, (__nv_bfloat16*)out, splits, head_dim, c.groups);
+    sib_launch_chained(attention_combine_kernel<__nv_bfloat16>, dim3(units), dim3(c.threads), c.smem,
+                       s, partial, (__nv_bfloat16*)out, splits, head_dim, c.groups);
     return sib_check_launch("attention_combine");
 }
 
@@ -328,7 +332,8 @@ SIB_EXPORT int sib_attention_rows(
     cudaStream_t s = (cudaStream_t)stream;
     const int vec = 16 / esz;
     const int ni = (head_dim + 32 * vec - 1) / (32 * vec);
-#define LAUNCH(NI) attention_rows_kernel<T, NI><<<(unsigned)blocks, 128, 0, s>>>(p)
+#define LAUNCH(NI) \
+    sib_launch_chained(attention_rows_kernel<T, NI>, dim3((unsigned)blocks), dim3(128), 0, s, p)
     SIB_DISPATCH_DTYPE(dtype, {
         if (ni == 1) LAUNCH(1);
         else if (ni == 2) LAUNCH(2);
@@ -338,7 +343,8 @@ SIB_EXPORT int sib_attention_rows(
     int rc = sib_check_launch("attention_rows");
     if (rc || splits == 1) return rc;
     const CombineShape c = combine_shape(splits, head_dim);
-    SIB_DISPATCH_DTYPE(dtype, (attention_combine_kernel<T><<<rows * n_heads, c.threads, c.smem, s>>>(
-                                  partial, (T*)out, splits, head_dim, c.groups)));
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(attention_combine_kernel<T>, dim3(rows * n_heads),
+                                                 dim3(c.threads), c.smem, s, partial, (T*)out,
+                                                 splits, head_dim, c.groups));
     return sib_check_launch("attention_combine");
 }

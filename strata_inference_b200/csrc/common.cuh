@@ -15,6 +15,37 @@ enum SibDtype { SIB_F32 = 0, SIB_BF16 = 1 };
 void sib_set_error(const char* fmt, ...);
 int sib_check_launch(const char* what);
 
+// Programmatic dependent launch: a kernel launched with sib_launch_chained may begin
+// while the kernel before it on the stream is still running.  It may do work
+// that reads nothing the earlier kernel writes (prefetching weights), then calls
+// pdl_wait(), which returns once the earlier kernel has completed and its writes
+// are visible.  pdl_trigger() lets the NEXT kernel of the stream begin in the same
+// way.  Without the launch attribute both are no-ops.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+#endif
+
+bool sib_chained_launches();   // false when the environment sets SIB_CHAINED_LAUNCH=0
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t sib_launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = sib_chained_launches() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define SIB_REQUIRE(cond, ...)            \
     do {                                  \
         if (!(cond)) {                    \

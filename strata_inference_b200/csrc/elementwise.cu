@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                   float* __restrict__ out, int hidden, float scale) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const T* src = table + (size_t)tokens[r] * hidden;
     float* dst = out + (size_t)r * hidden;
@@ -19,8 +21,10 @@ SIB_EXPORT int sib_embed_rows(const int* tokens, const void* table, int table_dt
                               int rows, int hidden, float scale, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && hidden > 0, "embed_rows: rows=%d hidden=%d", rows, hidden);
-    SIB_DISPATCH_DTYPE(table_dtype, (embed_rows_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>(
-                                        tokens, (const T*)table, out, hidden, scale)));
+    SIB_DISPATCH_DTYPE(table_dtype,
+                       sib_launch_chained(embed_rows_kernel<T>, dim3(rows), dim3(256), 0,
+                                          (cudaStream_t)stream, tokens, (const T*)table, out, hidden,
+                                          scale));
     return sib_check_launch("embed_rows");
 }
 

@@ -82,6 +82,20 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
+    // The weights do not depend on the kernel before this one: pull this warp's part
+    // of them towards L2 while that kernel is still running, then wait for it.
+    pdl_trigger();
+    if (t == 0) {
+        for (int kb = (rank * 8 + warp) * 64; kb < K; kb += ksplit * 8 * 64) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wrow[m][0] + kb));
+                asm volatile("prefetch.global.L2 [%0];\n" ::"l"(wrow[m][1] + kb));
+            }
+        }
+    }
+    pdl_wait();
+
 #pragma unroll 2
     for (int kb = (rank * 8 + warp) * 64; kb < K; kb += ksplit * 8 * 64) {
         const int k = kb + 16 * t;
@@ -203,13 +217,15 @@ static int launch_skinny(const void* W, const void* x, void* y, int R, int N, in
     cfg.blockDim = dim3(256, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ksplit;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = sib_chained_launches() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)W,
                                        (const __nv_bfloat16*)x, (OutT*)y, R, N, K, x_stride,
                                        y_stride, cap, ksplit);

@@ -17,6 +17,8 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, const int* __restrict
                                 int hidden, float eps) {
     extern __shared__ float row[];
     __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x;
     const Tin* src = x + (size_t)(rows ? rows[i] : i) * hidden;
     float ss = 0.f;
@@ -42,6 +44,8 @@ __global__ void add_rms_norm_kernel(const T* __restrict__ a, const float* __rest
                                     T* __restrict__ out, int hidden) {
     extern __shared__ float row[];
     __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
     const size_t base = (size_t)blockIdx.x * hidden;
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
@@ -77,6 +81,8 @@ __global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
                                          float pre_eps, __nv_bfloat16* __restrict__ out, int hidden) {
     extern __shared__ float row[];
     __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
     const size_t base = (size_t)blockIdx.x * hidden;
     const int groups = hidden / 8;
     float ss = 0.f;
@@ -163,8 +169,8 @@ SIB_EXPORT int sib_rms_norm(const void* x, int in_dtype, const int* rows, const 
     do {                                                                               \
         int rc = allow_row(rms_norm_kernel<TIN, TOUT>, smem);                          \
         if (rc) return rc;                                                             \
-        rms_norm_kernel<TIN, TOUT><<<n_rows, threads, smem, s>>>(                      \
-            (const TIN*)x, rows, gain, (TOUT*)out, hidden, eps);                       \
+        sib_launch_chained(rms_norm_kernel<TIN, TOUT>, dim3(n_rows), dim3(threads), smem, s, \
+                           (const TIN*)x, rows, gain, (TOUT*)out, hidden, eps);        \
     } while (0)
     if (in_dtype == SIB_F32 && out_dtype == SIB_F32) LAUNCH(float, float);
     else if (in_dtype == SIB_F32 && out_dtype == SIB_BF16) LAUNCH(float, __nv_bfloat16);
@@ -191,17 +197,18 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
         ((uintptr_t)post_gain % 16) == 0 && ((uintptr_t)pre_gain % 16) == 0) {
         int rc = allow_row(add_rms_norm_bf16_kernel, smem);
         if (rc) return rc;
-        add_rms_norm_bf16_kernel<<<n_rows, threads < 256 ? threads : 256, smem,
-                                   (cudaStream_t)stream>>>(
-            (const __nv_bfloat16*)a, post_gain, post_eps, h, pre_gain, pre_eps,
-            (__nv_bfloat16*)out, hidden);
+        sib_launch_chained(add_rms_norm_bf16_kernel, dim3(n_rows),
+                           dim3(threads < 256 ? threads : 256), smem, (cudaStream_t)stream,
+                           (const __nv_bfloat16*)a, post_gain, post_eps, h, pre_gain, pre_eps,
+                           (__nv_bfloat16*)out, hidden);
         return sib_check_launch("add_rms_norm");
     }
     SIB_DISPATCH_DTYPE(dtype, {
         int rc = allow_row(add_rms_norm_kernel<T>, smem);
         if (rc) return rc;
-        add_rms_norm_kernel<T><<<n_rows, threads, smem, (cudaStream_t)stream>>>(
-            (const T*)a, post_gain, post_eps, h, pre_gain, pre_eps, (T*)out, hidden);
+        sib_launch_chained(add_rms_norm_kernel<T>, dim3(n_rows), dim3(threads), smem,
+                           (cudaStream_t)stream, (const T*)a, post_gain, post_eps, h, pre_gain,
+                           pre_eps, (T*)out, hidden);
     });
     return sib_check_launch("add_rms_norm");
 }

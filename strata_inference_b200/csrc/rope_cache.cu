@@ -31,6 +31,8 @@ struct RopeStoreArgs {
 
 template <typename T>
 __global__ void rope_store_kernel(RopeStoreArgs p) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x, y = blockIdx.y;
     const int hd = p.head_dim;
     const int width = (p.n_heads + 2 * p.n_kv) * hd;
@@ -80,6 +82,8 @@ __global__ void rope_store_kernel(RopeStoreArgs p) {
 // head rotated.  One block per row; a thread takes 8 pairs (x[i..i+8) with
 // x[i+half..i+half+8)) of a q or k head, or 8 elements of a v head.
 __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const int hd = p.head_dim, half = hd / 2;
     const int width = (p.n_heads + 2 * p.n_kv) * hd;
@@ -168,12 +172,13 @@ SIB_EXPORT int sib_rope_store(void* qkv, int dtype, const int* row_pos, const in
                     n_heads, n_kv, head_dim, rot, style, max_pages, page_tokens, ring_tokens};
     if (dtype == SIB_BF16 && style == 0 && rot == head_dim && head_dim % 16 == 0 &&
         ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0) {
-        rope_store_bf16_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>(p);
+        sib_launch_chained(rope_store_bf16_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, p);
         return sib_check_launch("rope_store");
     }
     int threads = 32;
     while (threads < 128 && threads < head_dim / 2) threads *= 2;
     dim3 grid(rows, n_heads + 2 * n_kv);
-    SIB_DISPATCH_DTYPE(dtype, (rope_store_kernel<T><<<grid, threads, 0, (cudaStream_t)stream>>>(p)));
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(rope_store_kernel<T>, grid, dim3(threads), 0,
+                                                 (cudaStream_t)stream, p));
     return sib_check_launch("rope_store");
 }

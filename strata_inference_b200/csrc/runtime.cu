@@ -1,6 +1,7 @@
 // Error reporting shared by all exported launchers.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -19,6 +20,15 @@ int sib_check_launch(const char* what) {
     if (e == cudaSuccess) return 0;
     sib_set_error("%s: %s", what, cudaGetErrorString(e));
     return (int)e;
+}
+
+bool sib_chained_launches() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* v = getenv("SIB_CHAINED_LAUNCH");
+        enabled = (v && v[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
 }
 
 SIB_EXPORT const char* sib_last_error() { return g_error; }

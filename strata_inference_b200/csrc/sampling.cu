@@ -144,6 +144,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(SampleArgs 
     __shared__ int is2[33];
     __shared__ int result;
     __shared__ float draw;
+    pdl_trigger();
+    pdl_wait();
     const float* row = p.logits + (size_t)blockIdx.x * p.stride;
     const int V = p.vocab;
 
@@ -319,6 +321,6 @@ SIB_EXPORT int sib_sample_rows(const float* logits, long long stride, int rows, 
     SIB_REQUIRE(temperature <= 0.f || rng != nullptr, "sample_rows: sampling needs generator states");
     SIB_REQUIRE(top_k >= 0 && top_p > 0.f, "sample_rows: top_k=%d top_p=%f", top_k, top_p);
     SampleArgs p{logits, stride, vocab, temperature, top_k, top_p, rng, rng_index, out};
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(p);
+    sib_launch_chained(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, p);
     return sib_check_launch("sample_rows");
 }
