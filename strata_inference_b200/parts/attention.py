@@ -29,6 +29,8 @@ from ..weights.loader import TensorDecl
 from .registry import part_class, register_mixer
 
 _TARGET_WARPS = 148 * 16
+# the decode kernel keeps 3 blocks of 4 warps resident per SM (its registers decide)
+_RESIDENT_WARPS_DECODE = 148 * 12
 
 
 class Attention:
@@ -74,13 +76,15 @@ class Attention:
     # ------------------------------------------------------------------
     def _splits(self, ctx, capacity: int, per_kv_head: bool = False) -> int:
         """How many runs of keys each unit of work (a row's head, or the heads
-        of one kv head) is cut into when it reads the cache: enough to fill
-        the device, no run shorter than a few tiles of keys."""
+        of one kv head) is cut into when it reads the cache: as many as fit on
+        the device at once (a second, partly filled wave of blocks costs more
+        than it brings), no run shorter than a few tiles of keys."""
         longest = capacity if ctx.graph_capture else ctx.max_end
         if self.window > 0:
             longest = min(longest, self.window)
         units = max(1, ctx.n_rows * (self.nkv if per_kv_head else self.nh))
-        want = -(-_TARGET_WARPS // units)
+        resident = _RESIDENT_WARPS_DECODE if per_kv_head else _TARGET_WARPS
+        want = max(1, resident // units)
         shortest = 64 if per_kv_head else 32
         return max(1, min(want, -(-longest // shortest), 128))
 
