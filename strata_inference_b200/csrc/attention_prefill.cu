@@ -55,6 +55,13 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// tanh on the special-function unit (relative error about 2^-11: below the 2^-9 of the
+// bfloat16 operands the scores were computed from).
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -175,17 +182,25 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
             }
         }
         // ---- scale, cap, mask, online softmax ----
+        // Most tiles lie wholly below the diagonal and inside the window of all 16 rows
+        // of the warp (consecutive positions of one head): no per-element mask there.
+        const int wq_lo = p0 + (16 * warp) % MP;
+        const bool inside = kt * 64 + 63 <= wq_lo && kt * 64 + 63 < n &&
+                            (p.window <= 0 || wq_lo + 15 - kt * 64 < p.window);
+        const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
         float mx[2] = {m_run[0], m_run[1]};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int key = kt * 64 + 8 * j + 2 * t + (i & 1);
-                const int qp = (i < 2) ? qpos0 : qpos1;
                 float v = s[j][i] * p.scale;
-                if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
-                const bool seen = key <= qp && key < n && (p.window <= 0 || qp - key < p.window);
-                v = seen ? v : -INFINITY;
+                if (p.softcap > 0.f) v = p.softcap * tanh_fast(v * inv_cap);
+                if (!inside) {
+                    const int key = kt * 64 + 8 * j + 2 * t + (i & 1);
+                    const int qp = (i < 2) ? qpos0 : qpos1;
+                    const bool seen = key <= qp && key < n && (p.window <= 0 || qp - key < p.window);
+                    v = seen ? v : -INFINITY;
+                }
                 s[j][i] = v;
                 mx[i >> 1] = fmaxf(mx[i >> 1], v);
             }
@@ -196,7 +211,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             m_use[r] = mx[r] == -INFINITY ? 0.f : mx[r];     // a row that has seen no key yet
-            corr[r] = expf(m_run[r] - m_use[r]);
+            corr[r] = __expf(m_run[r] - m_use[r]);
             m_run[r] = mx[r];
             l_run[r] *= corr[r];
         }
@@ -210,7 +225,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(AttnPrefillArgs 
         for (int j = 0; j < 8; ++j) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float e = expf(s[j][i] - m_use[i >> 1]);
+                const float e = __expf(s[j][i] - m_use[i >> 1]);
                 s[j][i] = e;
                 lsum[i >> 1] += e;
             }

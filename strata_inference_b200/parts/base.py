@@ -91,8 +91,16 @@ class Runtime:
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             return native.skinny_linear(x, w, out, epilogue, cap)
+        aligned = (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                   and x.data_ptr() % 16 == 0)
+        if (x.dtype == torch.bfloat16 and out_dtype == torch.float32 and aligned):
+            # many rows of 32-bit outputs (logits of whole prompts): the tcgen05 product
+            # writes them once, soft-capped in its epilogue, where the library product
+            # would write them and a second kernel read and write them again
+            out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
+            return native.gemm_tcgen05(x, w, out, epilogue, cap)
         if epilogue == native.EPI_GEGLU:
-            raise ValueError("the gated epilogue exists in the weight-streaming kernel only")
+            raise ValueError("the gated epilogue exists in the hand-written products only")
         if out_dtype == x.dtype:
             y = torch.matmul(x, w.t())
         else:
