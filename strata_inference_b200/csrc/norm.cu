@@ -133,6 +133,86 @@ __global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
     }
 }
 
+// One warp per row, the row in registers, no block-wide barrier: for hidden sizes that
+// are NG x 256 (lane l owns the 8-element groups l, l + 32, ...).
+template <int NG>
+__global__ void __launch_bounds__(128)
+add_rms_norm_bf16_warp_kernel(const __nv_bfloat16* __restrict__ a, const float* __restrict__ post_gain,
+                              float post_eps, float* __restrict__ h,
+                              const float* __restrict__ pre_gain, float pre_eps,
+                              __nv_bfloat16* __restrict__ out, int n_rows) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int hidden = NG * 256;
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const size_t base = (size_t)r * hidden;
+    float v[NG][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(a + base + 8 * (lane + 32 * i));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[i][2 * k] = __uint_as_float(w[k] << 16);
+            v[i][2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+            ss += v[i][2 * k] * v[i][2 * k] + v[i][2 * k + 1] * v[i][2 * k + 1];
+        }
+    }
+    float inv = 1.f;
+    if (post_gain) inv = 1.0f / sqrtf(warp_sum(ss) / (float)hidden + post_eps);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+        const int c = 8 * (lane + 32 * i);
+        float4 h0 = *reinterpret_cast<const float4*>(h + base + c);
+        float4 h1 = *reinterpret_cast<const float4*>(h + base + c + 4);
+        if (post_gain) {
+            const float4 g0 = *reinterpret_cast<const float4*>(post_gain + c);
+            const float4 g1 = *reinterpret_cast<const float4*>(post_gain + c + 4);
+            v[i][0] *= inv * g0.x; v[i][1] *= inv * g0.y; v[i][2] *= inv * g0.z; v[i][3] *= inv * g0.w;
+            v[i][4] *= inv * g1.x; v[i][5] *= inv * g1.y; v[i][6] *= inv * g1.z; v[i][7] *= inv * g1.w;
+        }
+        h0.x += v[i][0]; h0.y += v[i][1]; h0.z += v[i][2]; h0.w += v[i][3];
+        h1.x += v[i][4]; h1.y += v[i][5]; h1.z += v[i][6]; h1.w += v[i][7];
+        *reinterpret_cast<float4*>(h + base + c) = h0;
+        *reinterpret_cast<float4*>(h + base + c + 4) = h1;
+        v[i][0] = h0.x; v[i][1] = h0.y; v[i][2] = h0.z; v[i][3] = h0.w;
+        v[i][4] = h1.x; v[i][5] = h1.y; v[i][6] = h1.z; v[i][7] = h1.w;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss2 += v[i][e] * v[i][e];
+    }
+    if (!pre_gain) return;
+    const float inv2 = 1.0f / sqrtf(warp_sum(ss2) / (float)hidden + pre_eps);
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+        const int c = 8 * (lane + 32 * i);
+        const float4 g0 = *reinterpret_cast<const float4*>(pre_gain + c);
+        const float4 g1 = *reinterpret_cast<const float4*>(pre_gain + c + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162 o = __floats2bfloat162_rn(v[i][2 * k] * inv2 * g[2 * k],
+                                                           v[i][2 * k + 1] * inv2 * g[2 * k + 1]);
+            w[k] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        *reinterpret_cast<uint4*>(out + base + c) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <int NG>
+static int launch_warp_norm(const void* a, const float* post_gain, float post_eps, float* h,
+                            const float* pre_gain, float pre_eps, void* out, int n_rows,
+                            cudaStream_t s) {
+    sib_launch_chained(add_rms_norm_bf16_warp_kernel<NG>, dim3((n_rows + 3) / 4), dim3(128), 0, s,
+                       (const __nv_bfloat16*)a, post_gain, post_eps, h, pre_gain, pre_eps,
+                       (__nv_bfloat16*)out, n_rows);
+    return sib_check_launch("add_rms_norm");
+}
+
 static int norm_threads(int hidden) {
     int t = 128;
     while (t < 1024 && t * 4 < hidden) t *= 2;
@@ -195,6 +275,19 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
     if (dtype == SIB_BF16 && hidden % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
         ((uintptr_t)h % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
         ((uintptr_t)post_gain % 16) == 0 && ((uintptr_t)pre_gain % 16) == 0) {
+        // many rows: a warp per row keeps the device full without block barriers; few rows
+        // (decoding): a block per row has the shorter latency
+        if (n_rows >= 512 && hidden % 256 == 0 && hidden / 256 <= 18) {
+            cudaStream_t s = (cudaStream_t)stream;
+#define NORM_CASE(NG) \
+    case NG: return launch_warp_norm<NG>(a, post_gain, post_eps, h, pre_gain, pre_eps, out, n_rows, s)
+            switch (hidden / 256) {
+                NORM_CASE(1); NORM_CASE(2); NORM_CASE(3); NORM_CASE(4); NORM_CASE(5); NORM_CASE(6);
+                NORM_CASE(7); NORM_CASE(8); NORM_CASE(9); NORM_CASE(10); NORM_CASE(11); NORM_CASE(12);
+                NORM_CASE(13); NORM_CASE(14); NORM_CASE(15); NORM_CASE(16); NORM_CASE(17); NORM_CASE(18);
+            }
+#undef NORM_CASE
+        }
         int rc = allow_row(add_rms_norm_bf16_kernel, smem);
         if (rc) return rc;
         sib_launch_chained(add_rms_norm_bf16_kernel, dim3(n_rows),

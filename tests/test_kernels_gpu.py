@@ -45,11 +45,11 @@ def test_embed_rows(dtype, hidden, vocab):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden", [48, 1000, 2304, 20000])
-def test_rms_norm_and_fused_add(dtype, hidden):
+@pytest.mark.parametrize("hidden", [48, 256, 1000, 2304, 4608, 20000])
+@pytest.mark.parametrize("rows", [9, 600])
+def test_rms_norm_and_fused_add(dtype, hidden, rows):
     n = _native()
     g = torch.Generator().manual_seed(1)
-    rows = 9
     h = torch.randn(rows, hidden, generator=g) * 3
     a = torch.randn(rows, hidden, generator=g).to(dtype)
     w1 = torch.randn(hidden, generator=g) * 0.3
