@@ -304,3 +304,138 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         got = eng.step([(sa, a[15:])], want=[list(range(8))])
         _close(got, ref_a[15:], torch.float32, f"toy tail {round_}")
         eng.end_sequence(sa)
+
+
+# ---------------------------------------------------------------- a toy position encoding
+
+class DampedPosition:
+    """Not a rotation: q and k are scaled by 1 / (1 + pos * slope_d), a slope per
+    dimension.  Has no ``rotary``: the mixer calls ``apply`` before it stores k."""
+
+    @staticmethod
+    def tensors(params, head_dim):
+        return {}
+
+    def __init__(self, params, head_dim, weights, rt):
+        self.slopes = (torch.arange(head_dim, dtype=torch.float32, device=rt.device) + 1) \
+            * float(params["slope"]) / head_dim
+
+    def apply(self, q, k, ctx):
+        factor = 1.0 / (1.0 + ctx.row_pos.to(torch.float32)[:, None, None] * self.slopes)
+        q.copy_((q.float() * factor).to(q.dtype))
+        if k is not None:
+            k.copy_((k.float() * factor).to(k.dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_position_encoding_through_apply(dtype):
+    from strata_inference_b200.cache.paged import SequenceCache
+    from strata_inference_b200.config.spec import PartSpec
+    from strata_inference_b200.parts import register_position
+    from strata_inference_b200.parts.attention import Attention
+    register_position("damped", DampedPosition)
+    rt = _rt(dtype)
+    g = torch.Generator().manual_seed(11)
+    H, nh, nkv, hd, slope = 64, 4, 2, 32, 0.05
+    ws = {"q_proj.weight": torch.randn(nh * hd, H, generator=g) * 0.2,
+          "k_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.2,
+          "v_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.1,
+          "o_proj.weight": torch.randn(H, nh * hd, generator=g) * 0.1}
+    ws = {k: v.to(torch.bfloat16) for k, v in ws.items()}
+    part = Attention({"num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "score_scale": 0.3,
+                      "logit_softcap": 0.0, "window": 0,
+                      "position": PartSpec("damped", {"slope": slope})}, H, ws, rt)
+    cache = SequenceCache([part.cache_need()], 256, 64, dtype, DEV, page_tokens=16)
+    T, cut = 40, 25
+    x = torch.randn(T, H, generator=g).to(dtype)
+    slot = cache.acquire()
+    cache.reserve([(slot, cut)])
+    cache.sync_tables()
+    got = [part.forward(x[:cut].to(DEV), _ctx(rt, cache, [(slot, 0, cut)]), 0, 0, True)]
+    cache.advance(slot, cut)
+    for t in range(cut, T):
+        cache.reserve([(slot, 1)])
+        cache.sync_tables()
+        got.append(part.forward(x[t:t + 1].to(DEV), _ctx(rt, cache, [(slot, t, 1)]), 0, 0, True))
+        cache.advance(slot, 1)
+    W = {k: v.double() for k, v in ws.items()}
+    factor = 1.0 / (1.0 + torch.arange(T).double()[:, None, None]
+                    * (torch.arange(hd).double() + 1) * slope / hd)
+    q = (x.double() @ W["q_proj.weight"].T).view(T, nh, hd) * factor
+    k = (x.double() @ W["k_proj.weight"].T).view(T, nkv, hd) * factor
+    v = (x.double() @ W["v_proj.weight"].T).view(T, nkv, hd)
+    ref = plain.attention(q, k, v, 0.3, 0.0, 0).reshape(T, nh * hd) @ W["o_proj.weight"].T
+    _close(torch.cat(got), ref, dtype, "attention with a toy position encoding")
+
+
+# ---------------------------------------------------------------- the schedule is data
+
+def _looped_spec(config):
+    """Gemma2's layers run as 0, 1, 0 again (shared weights, a cache of its own),
+    then layer 1 again on the keys and values its first run cached."""
+    from strata_inference_b200.config.gemma2 import Gemma2Config, gemma2_spec
+    from strata_inference_b200.config.spec import ModelSpec, ScheduleEntry
+    spec = gemma2_spec(Gemma2Config.from_dict(config))
+    fields = dict(spec.__dict__)
+    fields["architecture"] = "LoopedGemma2"
+    fields["schedule"] = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
+                          ScheduleEntry(1, cache_of=1))
+    return ModelSpec(**fields)
+
+
+def _looped_plain(tokens, W, cfg):
+    eps, T = cfg["rms_norm_eps"], len(tokens)
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    pos = torch.arange(T)
+    kept = {}
+
+    def layer(h, i, run, borrow=None):
+        p = f"model.layers.{i}."
+        n = plain.rms_norm(h, W[p + "input_layernorm.weight"], eps)
+        q = plain.rope_neox((n @ W[p + "self_attn.q_proj.weight"].T).view(T, nh, hd), pos,
+                            cfg["rope_theta"])
+        if borrow is None:
+            k = plain.rope_neox((n @ W[p + "self_attn.k_proj.weight"].T).view(T, nkv, hd), pos,
+                                cfg["rope_theta"])
+            v = (n @ W[p + "self_attn.v_proj.weight"].T).view(T, nkv, hd)
+            kept[run] = (k, v)
+        else:
+            k, v = kept[borrow]
+        window = cfg["sliding_window"] if plain.layer_is_sliding(cfg, i) else 0
+        o = plain.attention(q, k, v, cfg["query_pre_attn_scalar"] ** -0.5,
+                            cfg["attn_logit_softcapping"] or 0.0, window)
+        a = o.reshape(T, nh * hd) @ W[p + "self_attn.o_proj.weight"].T
+        r = h + plain.rms_norm(a, W[p + "post_attention_layernorm.weight"], eps)
+        n2 = plain.rms_norm(r, W[p + "pre_feedforward_layernorm.weight"], eps)
+        f = plain.geglu_ffn(n2, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
+                            W[p + "mlp.down_proj.weight"])
+        return r + plain.rms_norm(f, W[p + "post_feedforward_layernorm.weight"], eps)
+
+    h = plain.embed(tokens, W["model.embed_tokens.weight"], cfg["hidden_size"], torch.float64)
+    h = layer(h, 0, 0)
+    h = layer(h, 1, 1)
+    h = layer(h, 0, 2)
+    h = layer(h, 1, 3, borrow=1)
+    return plain.lm_head(h, W, cfg)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_names_a_layer_twice_and_lends_a_cache(tmp_path, dtype):
+    from safetensors.torch import load_file
+    from helpers import SHARPEN, assert_logits_close, make_model_dir, random_prompts
+    from strata_inference_b200 import Engine, register_architecture
+    from strata_inference_b200.config.gemma2 import Gemma2Config
+    register_architecture("LoopedGemma2", dict, _looped_spec)
+    cfg = dict(CONFIGS["A"], architectures=["LoopedGemma2"], model_type="looped")
+    d = make_model_dir(str(tmp_path / "m"), cfg, seed=8, sharpen=SHARPEN[dtype])
+    W = {k: v.double() for k, v in load_file(d + "/model.safetensors").items()}
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=512, page_tokens=16)
+    assert len(eng.cache.groups) == 2 and sum(len(g.entries) for g in eng.cache.groups) == 3
+    toks = random_prompts(cfg, [60], seed=9)[0]
+    ref = _looped_plain(toks, W, cfg)
+    slot = eng.new_sequence()
+    got = [eng.step([(slot, toks[:35])], want=[list(range(35))])]
+    for t in toks[35:]:
+        got.append(eng.step([(slot, [t])]))
+    eng.end_sequence(slot)
+    assert_logits_close(torch.cat(got), ref, dtype, "looped schedule with a lent cache")
