@@ -13,60 +13,29 @@
 // r = (x >> 40) / 2^24.
 // Plain counterpart: tests/plain_gemma2.py sample_token(), argmax(), XorShift64.
 //
-// The filtered modes never sort: the k-th largest value, the value at which
-// the mass reaches p and the value the draw lands on are each found by 32
-// rounds of bisection on the order-preserving integer image of z, each round
-// one pass over the row.
+// Layout of the work: a row of logits is shared by a cluster of 8 blocks, each
+// owning a contiguous eighth of the vocabulary; partial results meet in the
+// first block's shared memory (distributed shared memory) once per pass.
+// The filtered modes never sort.  "The k-th largest z", "the z at which the
+// running mass reaches p" and "the z the draw lands on" are each a search for
+// where a running count or mass, taken in descending order, crosses a target;
+// each is done by a radix walk over the order-preserving integer image of z,
+// 4 bits a pass (16 buckets of count and mass per pass, 8 passes a search).
+// All sums are taken in a fixed order, so a draw is reproducible.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
-#define SAMPLE_THREADS 1024
+namespace cg = cooperative_groups;
+
+#define SAMPLE_CLUSTER 8
+#define SAMPLE_THREADS 512
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
 
 __device__ __forceinline__ uint32_t order_key(float z) {
     const uint32_t u = __float_as_uint(z);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-
-struct ArgMax {
-    float v;
-    int i;
-};
-__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
-    // larger value wins; equal values: the lower index
-    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
-    return a;
-}
-
-__device__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        ArgMax b;
-        b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
-        b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
-        a = better(a, b);
-    }
-    __syncthreads();
-    if (lane == 0) scratch[warp] = a;
-    __syncthreads();
-    if (warp == 0) {
-        ArgMax t = lane < (int)(blockDim.x >> 5) ? scratch[lane] : ArgMax{-INFINITY, 0x7fffffff};
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            ArgMax b;
-            b.v = __shfl_xor_sync(0xffffffffu, t.v, o);
-            b.i = __shfl_xor_sync(0xffffffffu, t.i, o);
-            t = better(t, b);
-        }
-        if (lane == 0) scratch[32] = t;
-    }
-    __syncthreads();
-    return scratch[32];
-}
-
-struct Tally {       // elements at or above a threshold
-    float mass;      // sum of exp(z - max)
-    int count;
-};
 
 struct SampleArgs {
     const float* logits;   // [rows, stride]
@@ -80,236 +49,406 @@ struct SampleArgs {
     int* out;                 // [rows]
 };
 
-// Block-wide sums of (mass, count); every thread gets the result.
-__device__ Tally block_tally(Tally t, float* fs, int* is) {
+// What the blocks of a cluster exchange in one pass: 16 buckets of (count, mass),
+// or any 32 numbers.  Two buffers alternate so that one cluster barrier a pass is enough.
+struct Exchange {
+    float f[2][SAMPLE_CLUSTER][16];
+    int i[2][SAMPLE_CLUSTER][16];
+};
+
+struct SampleShared {
+    Exchange xchg;                       // used in the cluster's first block
+    float bins_f[16][SAMPLE_THREADS];    // per-thread private buckets
+    int bins_i[16][SAMPLE_THREADS];
+    float tot_f[16];
+    int tot_i[16];
+    float warp_f[SAMPLE_WARPS];
+    int warp_i[SAMPLE_WARPS];
+    int scan[SAMPLE_THREADS];
+    float scan_f[SAMPLE_THREADS];
+    int result;
+    float before_f, total_f;
+};
+
+struct Cluster {
+    cg::cluster_group g;
+    SampleShared* sh;       // this block's
+    SampleShared* first;    // the first block's (remote unless rank == 0)
+    int rank;
+    int pass;
+};
+
+// Sum the 16 per-thread buckets over the block (fixed order), then over the cluster
+// (block order).  Afterwards sh->tot_f / tot_i hold the cluster-wide totals in every
+// block, and the exchange buffer of this pass ((pass - 1) & 1 after the call) still
+// holds every block's own sums.
+__device__ void cluster_bucket_totals(Cluster& c) {
+    SampleShared* sh = c.sh;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        t.mass += __shfl_xor_sync(0xffffffffu, t.mass, o);
-        t.count += __shfl_xor_sync(0xffffffffu, t.count, o);
-    }
     __syncthreads();
-    if (lane == 0) { fs[warp] = t.mass; is[warp] = t.count; }
-    __syncthreads();
-    if (warp == 0) {
-        float m = lane < (int)(blockDim.x >> 5) ? fs[lane] : 0.f;
-        int c = lane < (int)(blockDim.x >> 5) ? is[lane] : 0;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            m += __shfl_xor_sync(0xffffffffu, m, o);
-            c += __shfl_xor_sync(0xffffffffu, c, o);
+    {   // warp w sums bucket w over all threads
+        float f = 0.f;
+        int n = 0;
+        for (int t = lane; t < SAMPLE_THREADS; t += 32) {
+            f += sh->bins_f[warp][t];
+            n += sh->bins_i[warp][t];
         }
-        if (lane == 0) { fs[32] = m; is[32] = c; }
+        f = warp_sum(f);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+        const int buf = c.pass & 1;
+        if (lane == 0) {
+            c.first->xchg.f[buf][c.rank][warp] = f;
+            c.first->xchg.i[buf][c.rank][warp] = n;
+        }
+    }
+    c.g.sync();
+    if (threadIdx.x < 16) {
+        const int buf = c.pass & 1;
+        float f = 0.f;
+        int n = 0;
+        for (int b = 0; b < SAMPLE_CLUSTER; ++b) {
+            f += c.first->xchg.f[buf][b][threadIdx.x];
+            n += c.first->xchg.i[buf][b][threadIdx.x];
+        }
+        sh->tot_f[threadIdx.x] = f;
+        sh->tot_i[threadIdx.x] = n;
     }
     __syncthreads();
-    Tally r;
-    r.mass = fs[32];
-    r.count = is[32];
+    c.pass++;
+}
+
+// A set of candidates in descending order of key: every element with key > floor_key,
+// followed by `floor_ties` elements equal to floor_key of mass `floor_q` each.
+struct Kept {
+    uint32_t floor_key;
+    int floor_ties;
+    float floor_q;
+};
+
+struct Crossing {
+    uint32_t key;      // the key at which the running count / mass crosses the target
+    int above_count;   // kept elements with a larger key
+    float above_mass;
+    int ties;          // kept elements with exactly this key
+    float q;           // mass of one of them
+    float total_mass;  // mass of the whole kept set (from the first pass)
+};
+
+// Walk the radix tree of keys, 4 bits a level, towards the element where, in
+// descending order, the running count reaches `want_count` (by_mass == false), or the
+// running mass reaches (inclusive) / exceeds (!inclusive) fraction x (mass of the set).
+__device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, float inv_t,
+                                  float zmax, const Kept& kept, bool by_mass, int want_count,
+                                  float fraction, bool inclusive) {
+    SampleShared* sh = c.sh;
+    Crossing r;
+    r.key = 0;
+    r.above_count = 0;
+    r.above_mass = 0.f;
+    r.ties = 0;
+    r.q = 0.f;
+    r.total_mass = 0.f;
+    float want_mass = 0.f;
+    for (int level = 0; level < 8; ++level) {
+        const int shift = 28 - 4 * level;
+        const uint32_t path_mask = level == 0 ? 0u : (0xffffffffu << (shift + 4));
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+            sh->bins_f[b][threadIdx.x] = 0.f;
+            sh->bins_i[b][threadIdx.x] = 0;
+        }
+        for (int i = lo + threadIdx.x; i < hi; i += SAMPLE_THREADS) {
+            const float z = row[i] * inv_t;
+            const uint32_t key = order_key(z);
+            if (key > kept.floor_key && (key & path_mask) == (r.key & path_mask)) {
+                const int b = (key >> shift) & 15;
+                sh->bins_f[b][threadIdx.x] += expf(z - zmax);
+                sh->bins_i[b][threadIdx.x] += 1;
+            }
+        }
+        cluster_bucket_totals(c);
+        float mass[16];
+        int count[16];
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {
+            mass[b] = sh->tot_f[b];
+            count[b] = sh->tot_i[b];
+        }
+        // the tied elements at the floor are candidates too
+        if (kept.floor_ties > 0 && (kept.floor_key & path_mask) == (r.key & path_mask)) {
+            const int fb = (kept.floor_key >> shift) & 15;
+#pragma unroll
+            for (int b = 0; b < 16; ++b)
+                if (b == fb) {
+                    mass[b] += (float)kept.floor_ties * kept.floor_q;
+                    count[b] += kept.floor_ties;
+                }
+        }
+        if (level == 0) {
+#pragma unroll
+            for (int b = 15; b >= 0; --b) r.total_mass += mass[b];
+            want_mass = fraction * r.total_mass;
+        }
+        // from the largest bucket down: the first one in which the target is crossed
+        int pick = -1, last_nonempty = -1, last_count = 0, pick_count = 0;
+        float last_mass = 0.f, pick_mass = 0.f;
+        int cnt = r.above_count;
+        float ms = r.above_mass;
+#pragma unroll
+        for (int b = 15; b >= 0; --b) {
+            if (pick < 0 && count[b] > 0) {
+                last_nonempty = b;
+                last_count = count[b];
+                last_mass = mass[b];
+                const int c2 = cnt + count[b];
+                const float m2 = ms + mass[b];
+                const bool crossed = by_mass ? (inclusive ? m2 >= want_mass : m2 > want_mass)
+                                             : c2 >= want_count;
+                if (crossed) {
+                    pick = b;
+                    pick_count = count[b];
+                    pick_mass = mass[b];
+                } else {
+                    cnt = c2;
+                    ms = m2;
+                }
+            }
+        }
+        if (pick < 0) {
+            // rounding left the target just beyond the end: the last candidate it is
+            pick = last_nonempty < 0 ? 0 : last_nonempty;
+            cnt -= last_count;
+            ms -= last_mass;
+            pick_count = last_count;
+            pick_mass = last_mass;
+        }
+        r.above_count = cnt;
+        r.above_mass = ms;
+        r.key |= (uint32_t)pick << shift;
+        if (level == 7) {
+            r.ties = pick_count;
+            r.q = pick_count > 0 ? pick_mass / (float)pick_count : 0.f;
+        }
+    }
     return r;
 }
 
-// Index of the `rank`-th (0-based) element, in index order, whose key equals `key`.
-__device__ int nth_with_key(const float* row, int vocab, float inv_t, uint32_t key, int rank,
-                            int* is, int* result) {
-    const int per = (vocab + blockDim.x - 1) / blockDim.x;
-    const int lo = min(vocab, (int)threadIdx.x * per), hi = min(vocab, lo + per);
+// Publish one integer per block (one block holds a value >= 0, the others -1) and
+// return that value in every block (-1 if nobody had one).
+__device__ int cluster_share_found(Cluster& c, int found) {
+    SampleShared* sh = c.sh;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        sh->bins_f[k][threadIdx.x] = 0.f;
+        sh->bins_i[k][threadIdx.x] = (k == 0 && threadIdx.x == 0) ? found + 1 : 0;
+    }
+    cluster_bucket_totals(c);
+    return sh->tot_i[0] - 1;
+}
+
+// Token index of the `rank`-th (0-based, by index) element whose key equals `key`;
+// every block returns it.
+__device__ int nth_with_key(Cluster& c, const float* row, int lo, int hi, float inv_t,
+                            uint32_t key, int rank) {
+    SampleShared* sh = c.sh;
+    const int n = hi - lo;
+    const int per = (n + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int a = min(hi, lo + (int)threadIdx.x * per), b = min(hi, a + per);
     int mine = 0;
-    for (int i = lo; i < hi; ++i) mine += order_key(row[i] * inv_t) == key;
-    __syncthreads();
-    is[threadIdx.x] = mine;
-    __syncthreads();
+    for (int i = a; i < b; ++i) mine += order_key(row[i] * inv_t) == key;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        sh->bins_f[k][threadIdx.x] = 0.f;
+        sh->bins_i[k][threadIdx.x] = k == 0 ? mine : 0;
+    }
+    sh->scan[threadIdx.x] = mine;
+    cluster_bucket_totals(c);
     if (threadIdx.x == 0) {
+        // matches in the blocks before this one (blocks are in index order), then in the
+        // threads before each thread
+        const int buf = (c.pass - 1) & 1;
         int run = 0;
-        for (int w = 0; w < (int)blockDim.x; ++w) { const int c = is[w]; is[w] = run; run += c; }
-        *result = -1;
+        for (int k = 0; k < c.rank; ++k) run += c.first->xchg.i[buf][k][0];
+        for (int t = 0; t < SAMPLE_THREADS; ++t) {
+            const int v = sh->scan[t];
+            sh->scan[t] = run;
+            run += v;
+        }
+        sh->result = -1;
     }
     __syncthreads();
-    const int before = is[threadIdx.x];
+    const int before = sh->scan[threadIdx.x];
     if (rank >= before && rank < before + mine) {
         int seen = before;
-        for (int i = lo; i < hi; ++i)
+        for (int i = a; i < b; ++i)
             if (order_key(row[i] * inv_t) == key) {
-                if (seen == rank) { *result = i; break; }
+                if (seen == rank) { sh->result = i; break; }
                 ++seen;
             }
     }
     __syncthreads();
-    return *result;
+    return cluster_share_found(c, sh->result);
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(SampleArgs p) {
-    __shared__ ArgMax am[33];
-    __shared__ float fs[33];
-    __shared__ int is[SAMPLE_THREADS];
-    __shared__ int is2[33];
-    __shared__ int result;
-    __shared__ float draw;
+__global__ void __cluster_dims__(SAMPLE_CLUSTER, 1, 1) __launch_bounds__(SAMPLE_THREADS)
+sample_rows_kernel(SampleArgs p) {
+    extern __shared__ __align__(16) unsigned char sample_smem[];
+    SampleShared* sh = reinterpret_cast<SampleShared*>(sample_smem);
     pdl_trigger();
     pdl_wait();
-    const float* row = p.logits + (size_t)blockIdx.x * p.stride;
+    Cluster c{cg::this_cluster(), sh, nullptr, 0, 0};
+    c.rank = (int)c.g.block_rank();
+    c.first = c.g.map_shared_rank(sh, 0);
+    const int rowi = blockIdx.y;
+    const float* row = p.logits + (size_t)rowi * p.stride;
     const int V = p.vocab;
+    const int per_block = (V + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER;
+    const int lo = min(V, c.rank * per_block), hi = min(V, lo + per_block);
+    const int which = p.rng_index ? p.rng_index[rowi] : rowi;
+    const unsigned long long rng_before = p.temperature > 0.f ? p.rng[which] : 0ull;
+    c.g.sync();   // every block is running and has read the generator's state
 
-    ArgMax a{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) a = better(a, ArgMax{row[i], i});
-    a = block_argmax(a, am);
-    if (p.temperature <= 0.f) {
-        if (threadIdx.x == 0) p.out[blockIdx.x] = a.i == 0x7fffffff ? 0 : a.i;
-        return;
+    // ---- the maximum and its first index ----
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += SAMPLE_THREADS) {
+        const float v = row[i];
+        if (v > best) { best = v; best_i = i; }     // ascending i per thread: first maximum
     }
-    // The reference divides by T; 1/T times z differs from that in the last bit
-    // at most, and every pass below uses the same product.
-    const float inv_t = 1.0f / p.temperature;
-    const float zmax = a.v * inv_t;
-
-    if (threadIdx.x == 0) {
-        const int which = p.rng_index ? p.rng_index[blockIdx.x] : (int)blockIdx.x;
-        unsigned long long x = p.rng[which];
-        x ^= x << 13;
-        x ^= x >> 7;
-        x ^= x << 17;
-        p.rng[which] = x;
-        draw = (float)(x >> 40) / 16777216.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sh->warp_f[threadIdx.x >> 5] = best;
+        sh->warp_i[threadIdx.x >> 5] = best_i;
     }
     __syncthreads();
-    const float r = draw;
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < SAMPLE_WARPS; ++w) {
+            const float ov = sh->warp_f[w];
+            const int oi = sh->warp_i[w];
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
+        c.first->xchg.f[c.pass & 1][c.rank][0] = best;
+        c.first->xchg.i[c.pass & 1][c.rank][0] = best_i;
+    }
+    c.g.sync();
+    {
+        const int buf = c.pass & 1;
+        best = c.first->xchg.f[buf][0][0];
+        best_i = c.first->xchg.i[buf][0][0];
+        for (int b = 1; b < SAMPLE_CLUSTER; ++b) {
+            const float ov = c.first->xchg.f[buf][b][0];
+            const int oi = c.first->xchg.i[buf][b][0];
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
+        c.pass++;
+    }
+    if (p.temperature <= 0.f) {
+        if (c.rank == 0 && threadIdx.x == 0) p.out[rowi] = best_i == 0x7fffffff ? 0 : best_i;
+        c.g.sync();     // the first block's memory stays until every block has read it
+        return;
+    }
+    // The reference divides by T; 1/T times z differs from that in the last bit at most,
+    // and every pass uses the same product.
+    const float inv_t = 1.0f / p.temperature;
+    const float zmax = best * inv_t;
+    unsigned long long x = rng_before;
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    const float r = (float)(x >> 40) / 16777216.0f;
+    if (c.rank == 0 && threadIdx.x == 0) p.rng[which] = x;
 
     const bool use_k = p.top_k > 0 && p.top_k < V;
     const bool use_p = p.top_p < 1.0f;
+    int token;
 
     if (!use_k && !use_p) {
-        // running sum by token index over contiguous runs, one run per thread
-        const int per = (V + blockDim.x - 1) / blockDim.x;
-        const int lo = min(V, (int)threadIdx.x * per), hi = min(V, lo + per);
+        // running sum by token index: blocks, then threads, own contiguous runs
+        const int n = hi - lo;
+        const int per = (n + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+        const int a = min(hi, lo + (int)threadIdx.x * per), b = min(hi, a + per);
         float mine = 0.f;
-        for (int i = lo; i < hi; ++i) mine += expf(row[i] * inv_t - zmax);
-        __shared__ float runs[SAMPLE_THREADS];
-        runs[threadIdx.x] = mine;
+        for (int i = a; i < b; ++i) mine += expf(row[i] * inv_t - zmax);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            sh->bins_f[k][threadIdx.x] = 0.f;
+            sh->bins_i[k][threadIdx.x] = 0;
+        }
+        sh->scan_f[threadIdx.x] = mine;
         __syncthreads();
         if (threadIdx.x == 0) {
-            float run = 0.f;
-            for (int w = 0; w < (int)blockDim.x; ++w) { const float c = runs[w]; runs[w] = run; run += c; }
-            fs[0] = run;
-            result = V - 1;  // the reference's fallback: the last candidate
+            float run = 0.f;      // this block's mass, threads in order
+            for (int t = 0; t < SAMPLE_THREADS; ++t) run += sh->scan_f[t];
+            sh->bins_f[0][0] = run;
+        }
+        cluster_bucket_totals(c);
+        if (threadIdx.x == 0) {
+            const int buf = (c.pass - 1) & 1;
+            float acc = 0.f, all = 0.f;
+            for (int k = 0; k < SAMPLE_CLUSTER; ++k) {
+                if (k == c.rank) acc = all;
+                all += c.first->xchg.f[buf][k][0];
+            }
+            sh->before_f = acc;
+            sh->total_f = all;
+            float run = acc;
+            for (int t = 0; t < SAMPLE_THREADS; ++t) {
+                const float v = sh->scan_f[t];
+                sh->scan_f[t] = run;
+                run += v;
+            }
+            sh->result = -1;
         }
         __syncthreads();
-        const float target = r * fs[0];
-        const float before = runs[threadIdx.x];
-        if (hi > lo && target >= before && target < before + mine) {
+        const float target = r * sh->total_f;
+        const float before = sh->scan_f[threadIdx.x];
+        if (b > a && target >= before && target < before + mine) {
             float cum = before;
-            int pick = hi - 1;
-            for (int i = lo; i < hi; ++i) {
+            int pick = b - 1;
+            for (int i = a; i < b; ++i) {
                 cum += expf(row[i] * inv_t - zmax);
                 if (target < cum) { pick = i; break; }
             }
-            result = pick;
+            sh->result = pick;
         }
         __syncthreads();
-        if (threadIdx.x == 0) p.out[blockIdx.x] = result;
-        return;
-    }
-
-    // ---- filtered modes: thresholds on the ordered keys ------------------
-    // kth: key of the k-th largest z; k_ties: how many elements equal to it are kept.
-    uint32_t kth = 0;
-    int k_ties = 0x7fffffff;
-    if (use_k) {
-        uint32_t prefix = 0;
-        for (int bit = 31; bit >= 0; --bit) {
-            const uint32_t cand = prefix | (1u << bit);
-            Tally t{0.f, 0};
-            for (int i = threadIdx.x; i < V; i += blockDim.x) t.count += order_key(row[i] * inv_t) >= cand;
-            t = block_tally(t, fs, is2);
-            if (t.count >= p.top_k) prefix = cand;
+        token = cluster_share_found(c, sh->result);
+        if (token < 0) token = V - 1;      // the reference's fallback: the last candidate
+    } else {
+        Kept kept{0u, 0, 0.f};
+        if (use_k) {
+            const Crossing k = find_crossing(c, row, lo, hi, inv_t, zmax, kept, false, p.top_k, 0.f,
+                                             true);
+            kept.floor_key = k.key;
+            kept.floor_ties = max(0, min(k.ties, p.top_k - k.above_count));
+            kept.floor_q = k.q;
         }
-        kth = prefix;
-        Tally t{0.f, 0};
-        for (int i = threadIdx.x; i < V; i += blockDim.x) t.count += order_key(row[i] * inv_t) > kth;
-        t = block_tally(t, fs, is2);
-        k_ties = p.top_k - t.count;
-    }
-    // mass of the kept set after top-k
-    float q_kth = 0.f;   // exp(z - max) of one element equal to kth
-    Tally all{0.f, 0};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float z = row[i] * inv_t;
-        const uint32_t key = order_key(z);
-        if (key > kth || !use_k) all.mass += expf(z - zmax);
-        if (use_k && key == kth) q_kth = expf(z - zmax);
-    }
-    {
-        // every thread that saw an element equal to kth computed the same q_kth
-        __syncthreads();
-        if (threadIdx.x == 0) draw = 0.f;
-        __syncthreads();
-        if (q_kth > 0.f) draw = q_kth;
-        __syncthreads();
-        q_kth = draw;
-    }
-    all = block_tally(all, fs, is2);
-    float Z = all.mass + (use_k ? (float)k_ties * q_kth : 0.f);
-
-    // mass(c) = kept mass of keys >= c, in units of exp(z - max)
-    // A key equal to kth contributes at most k_ties elements.
-    auto mass_at_least = [&](uint32_t c, bool strict_only) {
-        Tally t{0.f, 0};
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const float z = row[i] * inv_t;
-            const uint32_t key = order_key(z);
-            const bool in = use_k ? key > kth : true;
-            if (in && (strict_only ? key > c : key >= c)) { t.mass += expf(z - zmax); t.count += 1; }
+        if (use_p) {
+            const Crossing q = find_crossing(c, row, lo, hi, inv_t, zmax, kept, true, 0, p.top_p,
+                                             true);
+            const float want = p.top_p * q.total_mass;
+            int need = q.ties;
+            if (q.q > 0.f) need = max(1, min(q.ties, (int)ceilf((want - q.above_mass) / q.q)));
+            kept.floor_key = q.key;
+            kept.floor_ties = need;
+            kept.floor_q = q.q;
         }
-        t = block_tally(t, fs, is2);
-        if (use_k && (strict_only ? kth > c : kth >= c)) { t.mass += (float)k_ties * q_kth; t.count += k_ties; }
-        return t;
-    };
-
-    // top-p: the key at which the running mass (descending) first reaches p * Z
-    uint32_t pth = 0;          // keys > pth are kept whole
-    int p_ties = 0x7fffffff;   // elements equal to pth that are kept
-    float Z2 = Z;
-    if (use_p) {
-        const float want = p.top_p * Z;
-        uint32_t prefix = 0;
-        for (int bit = 31; bit >= 0; --bit) {
-            const uint32_t cand = prefix | (1u << bit);
-            if (mass_at_least(cand, false).mass >= want) prefix = cand;
-        }
-        pth = prefix;
-        const Tally above = mass_at_least(pth, true);
-        const Tally upto = mass_at_least(pth, false);
-        const int ties = upto.count - above.count;
-        const float q = ties > 0 ? (upto.mass - above.mass) / (float)ties : 0.f;
-        int need = ties;
-        if (q > 0.f) {
-            need = (int)ceilf((want - above.mass) / q);
-            need = max(1, min(need, ties));
-        }
-        p_ties = need;
-        Z2 = above.mass + (float)need * q;
-        if (upto.mass < want) { pth = 0; p_ties = 0x7fffffff; Z2 = Z; }  // never reached: keep all
+        // the draw lands on the first candidate whose running mass exceeds r x total
+        const Crossing d = find_crossing(c, row, lo, hi, inv_t, zmax, kept, true, 0, r, false);
+        const float target = r * d.total_mass;
+        int rank = d.q > 0.f ? (int)floorf((target - d.above_mass) / d.q) : 0;
+        rank = max(0, min(rank, d.ties - 1));
+        token = nth_with_key(c, row, lo, hi, inv_t, d.key, rank);
+        if (token < 0) token = best_i;
     }
-
-    // the draw: first element, by descending key then index, whose running mass exceeds r * Z2
-    const float target = r * Z2;
-    uint32_t prefix = 0;
-    for (int bit = 31; bit >= 0; --bit) {
-        const uint32_t cand = prefix | (1u << bit);
-        if (mass_at_least(cand, false).mass > target) prefix = cand;
-    }
-    // keys below the filters' thresholds are not candidates
-    uint32_t floor_key = 0;
-    if (use_k) floor_key = kth;
-    if (use_p && pth > floor_key) floor_key = pth;
-    uint32_t hit = prefix < floor_key ? floor_key : prefix;
-    const Tally above = mass_at_least(hit, true);
-    const Tally upto = mass_at_least(hit, false);
-    int ties = upto.count - above.count;
-    const float q = ties > 0 ? (upto.mass - above.mass) / (float)ties : 0.f;
-    if (use_p && hit == pth) ties = min(ties, p_ties);
-    int rank = q > 0.f ? (int)floorf((target - above.mass) / q) : 0;
-    rank = max(0, min(rank, ties - 1));
-    const int tok = nth_with_key(row, V, inv_t, hit, rank, is, &result);
-    if (threadIdx.x == 0) p.out[blockIdx.x] = tok >= 0 ? tok : a.i;
+    if (c.rank == 0 && threadIdx.x == 0) p.out[rowi] = token;
+    c.g.sync();         // the first block's memory stays until every block has read it
 }
 
 SIB_EXPORT int sib_sample_rows(const float* logits, long long stride, int rows, int vocab,
@@ -317,10 +456,23 @@ SIB_EXPORT int sib_sample_rows(const float* logits, long long stride, int rows, 
                                unsigned long long* rng, const int* rng_index, int* out,
                                void* stream) {
     if (rows == 0) return 0;
-    SIB_REQUIRE(rows > 0 && vocab > 0 && stride >= vocab, "sample_rows: rows=%d vocab=%d", rows, vocab);
+    SIB_REQUIRE(rows > 0 && rows < 65536 && vocab > 0 && stride >= vocab,
+                "sample_rows: rows=%d vocab=%d", rows, vocab);
     SIB_REQUIRE(temperature <= 0.f || rng != nullptr, "sample_rows: sampling needs generator states");
     SIB_REQUIRE(top_k >= 0 && top_p > 0.f, "sample_rows: top_k=%d top_p=%f", top_k, top_p);
     SampleArgs p{logits, stride, vocab, temperature, top_k, top_p, rng, rng_index, out};
-    sib_launch_chained(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, p);
+    const size_t smem = sizeof(SampleShared);
+    cudaError_t e = cudaFuncSetAttribute(sample_rows_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+        sib_set_error("sample_rows: shared memory: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    e = sib_launch_chained(sample_rows_kernel, dim3(SAMPLE_CLUSTER, rows), dim3(SAMPLE_THREADS),
+                           smem, (cudaStream_t)stream, p);
+    if (e != cudaSuccess) {
+        sib_set_error("sample_rows: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     return sib_check_launch("sample_rows");
 }
