@@ -1,0 +1,518 @@
+// Attention of whole prompts on the fifth-generation tensor cores (bfloat16):
+// both products of flash attention as tcgen05.mma with the score tile and the
+// output accumulator in tensor memory.  Same mathematics as attention_rows.cu
+// (scale, soft cap, causal and window mask, softmax in 32-bit, weighted sum of
+// v); attention_prefill.cu is the mma.sync kernel this one supersedes where its
+// shapes fit (1 or 2 query heads per kv head, head size 64, 128 or 256).
+//
+// A block takes 128 query rows of one (sequence, kv head): G heads x 128/G
+// consecutive positions.  Keys and values are walked in tiles of 64 positions.
+//
+//   warp 0      TMA: the query tile once, then key and value tiles into a ring of 2,
+//               straight from the step's packed q|k|v rows (boxes of 64 rows x 64
+//               columns, 128-byte swizzle)
+//   warp 1      one lane issues S = Q K^T (128 x 64, K-major operands) and, once the
+//               probabilities are in shared memory, O += P V (128 x head_dim; V is the
+//               MN-major operand: its rows are keys, as they lie in memory)
+//   warps 2-5   one thread per query row: read S from tensor memory, scale, cap,
+//               mask, exponentiate against a running maximum, write P (bfloat16) into
+//               shared memory in the swizzled K-major layout the MMA reads, and at the
+//               end read O, divide by the row sum and store
+//
+// The running maximum is only raised (and O rescaled in tensor memory) when a
+// row's maximum has grown by more than 5.5: until then probabilities may exceed 1
+// by at most e^5.5, which bfloat16 and the 32-bit sums hold easily, and the
+// division by the row sum at the end makes the result the same.
+// Every mbarrier wait is bounded; a wait that runs out sets an error flag.
+//
+// Plain counterpart: tests/plain_gemma2.py attention().
+// Reference: src/backend/cuda/kernels.rs:3183-3430 (batched_causal_attention).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;   // query rows per block
+constexpr int BN = 64;    // keys per tile
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+// K-major operand: rows of 128 bytes (64 elements of k), 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand: rows are k (keys), 64 elements of n (128 bytes) per row; 8-row groups
+// 1024 bytes apart along k, blocks of 64 n `n_block_bytes` apart.
+__device__ __forceinline__ uint64_t desc_mn_major(const void* tile, uint32_t n_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) >> 4) & 0x3FFF);
+    d |= (uint64_t)((n_block_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+struct TcArgs {
+    __nv_bfloat16* out;      // [rows, n_heads * head_dim]
+    const int* seq_row0;
+    const int* seq_len;
+    int* error_flag;
+    int n_heads, n_kv;
+    int window;
+    float scale, softcap;
+};
+
+// Barriers of one block.
+struct Bars {
+    uint64_t q_full, kv_full[2], kv_empty[2], s_full, s_free, p_full, pv_done;
+};
+
+}  // namespace
+
+template <int HD, int G>
+__global__ void __launch_bounds__(192)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
+    constexpr int MP = BM / G;                 // positions per block
+    constexpr int CH = HD / 64;                // 64-wide column chunks of a head
+    constexpr uint32_t Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2, P_BYTES = BM * BN * 2;
+    // S: columns [0, 64); O: columns [64, 64 + HD); a power of two of columns is allocated
+    constexpr uint32_t TMEM_COLS = HD == 256 ? 512 : HD == 128 ? 256 : 128;
+    constexpr uint32_t O_COL = 64;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;                              // CH blocks of [128 rows x 128 B]
+    unsigned char* Ks = Qs + Q_BYTES;                      // 2 stages of CH blocks of [64 x 128 B]
+    unsigned char* Vs = Ks + 2 * KV_BYTES;                 // the same
+    unsigned char* Ps = Vs + 2 * KV_BYTES;                 // [128 rows x 128 B]
+    Bars* bars = reinterpret_cast<Bars*>(Ps + P_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
+    int* failed = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y, kvh = blockIdx.z;
+    const int n = p.seq_len[b];
+    const int p0 = (int)(gridDim.x - 1 - blockIdx.x) * MP;   // the longest tiles first
+    if (p0 >= n) return;
+    const int row0 = p.seq_row0[b];
+    const int k_hi = min(n, p0 + MP);
+    const int k_lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
+    const int kt0 = k_lo >> 6, nt = ((k_hi + 63) >> 6) - kt0;
+    const int q_col = kvh * G * HD;                        // first column of the group's heads
+    const int k_col = (p.n_heads + kvh) * HD;
+    const int v_col = (p.n_heads + p.n_kv + kvh) * HD;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->kv_full[s], 1);
+            mbar_init(&bars->kv_empty[s], 1);
+        }
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->s_free, 4);
+        mbar_init(&bars->p_full, 4);
+        mbar_init(&bars->pv_done, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // the query tile: per 64-column chunk two boxes of 64 rows
+            mbar_arrive_expect_tx(&bars->q_full, Q_BYTES);
+            for (int c = 0; c < CH; ++c)
+                for (int half = 0; half < 2; ++half) {
+                    const int head = (half * 64) / MP, off = (half * 64) % MP;
+                    tma_load_2d(Qs + c * (BM * 128) + half * (64 * 128), &map, &bars->q_full,
+                                q_col + head * HD + 64 * c, row0 + p0 + off);
+                }
+            for (int t = 0; t < nt; ++t) {
+                const int s = t & 1;
+                if (t >= 2 && !mbar_wait(&bars->kv_empty[s], ((t >> 1) - 1) & 1)) { *failed = 1; break; }
+                mbar_arrive_expect_tx(&bars->kv_full[s], 2 * KV_BYTES);
+                const int krow = row0 + (kt0 + t) * 64;
+                for (int c = 0; c < CH; ++c) {
+                    tma_load_2d(Ks + s * KV_BYTES + c * (BN * 128), &map, &bars->kv_full[s],
+                                k_col + 64 * c, krow);
+                    tma_load_2d(Vs + s * KV_BYTES + c * (BN * 128), &map, &bars->kv_full[s],
+                                v_col + 64 * c, krow);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) |
+                                          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                          ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            if (!ok) *failed = 2;
+            // S(t) = Q K(t)^T: HD / 16 steps of k
+            auto issue_qk = [&](int t) {
+                const unsigned char* kt = Ks + (t & 1) * KV_BYTES;
+#pragma unroll
+                for (int j = 0; j < HD / 16; ++j) {
+                    const uint64_t da = desc_k_major(Qs + (j >> 2) * (BM * 128)) + 2 * (j & 3);
+                    const uint64_t db = desc_k_major(kt + (j >> 2) * (BN * 128)) + 2 * (j & 3);
+                    umma_bf16(tmem, da, db, IDESC_QK, j > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars->s_full);
+            };
+            if (ok) {
+                if (!mbar_wait(&bars->kv_full[0], 0)) { *failed = 3; ok = false; }
+            }
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                issue_qk(0);
+            }
+            for (int t = 0; t < nt && ok; ++t) {
+                if (t + 1 < nt) {
+                    // the next tile's scores as soon as this tile's have been read
+                    if (!mbar_wait(&bars->kv_full[(t + 1) & 1], ((t + 1) >> 1) & 1) ||
+                        !mbar_wait(&bars->s_free, t & 1)) { *failed = 4; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    issue_qk(t + 1);
+                }
+                if (!mbar_wait(&bars->p_full, t & 1)) { *failed = 5; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // O += P V(t): 4 steps of 16 keys; V rows are keys (MN-major operand)
+                const unsigned char* vt = Vs + (t & 1) * KV_BYTES;
+#pragma unroll
+                for (int j = 0; j < BN / 16; ++j) {
+                    const uint64_t da = desc_k_major(Ps) + 2 * j;
+                    const uint64_t db = desc_mn_major(vt + j * (16 * 128), BN * 128);
+                    umma_bf16(tmem + O_COL, da, db, IDESC_PV, (t > 0 || j > 0) ? 1u : 0u);
+                }
+                umma_commit(&bars->kv_empty[t & 1]);
+                umma_commit(&bars->pv_done);
+            }
+            if (!ok) {   // let nobody wait for what will not come
+                umma_commit(&bars->s_full);
+                umma_commit(&bars->pv_done);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row = 32 * quarter + lane;               // tensor-memory lane = query row
+        const int head = kvh * G + row / MP;
+        const int pos = p0 + row % MP;
+        const uint32_t lane_addr = tmem + ((uint32_t)(32 * quarter) << 16);
+        const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int t = 0; t < nt && ok; ++t) {
+            if (!mbar_wait(&bars->s_full, t & 1)) { if (lane == 0) *failed = 6; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            uint32_t raw[2][32];
+            tmem_ld32(lane_addr, raw[0]);
+            tmem_ld32(lane_addr + 32, raw[1]);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->s_free);
+            // scale, cap, mask; the row's maximum
+            const int key0 = (kt0 + t) * 64;
+            const bool inside = key0 + 63 <= pos && key0 + 63 < n &&
+                                (p.window <= 0 || pos - key0 < p.window);
+            float mx = -INFINITY;
+            float sc[64];
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                float v = __uint_as_float(raw[j >> 5][j & 31]) * p.scale;
+                if (p.softcap > 0.f) v = p.softcap * tanh_fast(v * inv_cap);
+                if (!inside) {
+                    const int key = key0 + j;
+                    const bool seen = key <= pos && key < n && (p.window <= 0 || pos - key < p.window);
+                    v = seen ? v : -INFINITY;
+                }
+                sc[j] = v;
+                mx = fmaxf(mx, v);
+            }
+            // the reference the exponentials are taken against: raised only by big steps
+            float factor = 1.f;
+            bool raise = false;
+            if (t == 0) {
+                m_ref = mx;
+            } else if (mx > m_ref + 5.5f) {
+                raise = true;
+                factor = __expf(m_ref - mx);          // 0 when the row had seen no key yet
+                m_ref = mx;
+            }
+            if (t > 0) {
+                // P's buffer and O are free once the previous tile's P V has run
+                if (!mbar_wait(&bars->pv_done, (t - 1) & 1)) { if (lane == 0) *failed = 7; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            }
+            if (__any_sync(0xffffffffu, raise)) {
+                l *= factor;
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(lane_addr + O_COL + 32 * c, o);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
+                    tmem_st32(lane_addr + O_COL + 32 * c, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            }
+            const float ref = m_ref == -INFINITY ? 0.f : m_ref;
+            // probabilities into the K-major, 128-byte-swizzled tile the MMA reads
+            unsigned char* prow = Ps + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float e0 = __expf(sc[8 * c + 2 * k] - ref);
+                    const float e1 = __expf(sc[8 * c + 2 * k + 1] - ref);
+                    l += e0 + e1;
+                    w[k] = pack_bf16(e0, e1);
+                }
+                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_full);
+        }
+        if (ok && nt > 0) {
+            if (!mbar_wait(&bars->pv_done, (nt - 1) & 1)) { if (lane == 0) *failed = 8; ok = false; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        }
+        if (ok) {
+            const float inv = 1.0f / l;
+            const bool store = pos < n;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(lane_addr + O_COL + 32 * c, o);
+                if (store) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            w[k] = pack_bf16(__uint_as_float(o[8 * q4 + 2 * k]) * inv,
+                                             __uint_as_float(o[8 * q4 + 2 * k + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + 32 * c + 8 * q4) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+    if (threadIdx.x == 0 && *failed) atomicExch(p.error_flag, *failed);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn tc_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = (EncodeTiledFn)ptr;
+    return fn;
+}
+
+static int* g_tc_error_flag[64] = {};
+
+SIB_EXPORT int sib_attention_prefill_tc_error(int clear) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_tc_error_flag[dev]) return 0;
+    int v = 0;
+    cudaMemcpy(&v, g_tc_error_flag[dev], sizeof(int), cudaMemcpyDeviceToHost);
+    if (clear && v) cudaMemset(g_tc_error_flag[dev], 0, sizeof(int));
+    return v;
+}
+
+SIB_EXPORT int sib_attention_prefill_tc_supports(int n_heads, int n_kv, int head_dim, int width) {
+    if (n_kv <= 0 || n_heads % n_kv) return 0;
+    const int G = n_heads / n_kv;
+    return (G == 1 || G == 2) && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+           width % 8 == 0;
+}
+
+template <int HD, int G>
+static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int max_len,
+                     cudaStream_t s) {
+    const size_t smem = 1024 + (size_t)BM * HD * 2 + 4 * (size_t)BN * HD * 2 + BM * BN * 2 +
+                        sizeof(Bars) + 16;
+    auto kernel = attention_prefill_tc_kernel<HD, G>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+        sib_set_error("attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    constexpr int MP = BM / G;
+    dim3 grid((max_len + MP - 1) / MP, n_seqs, p.n_kv);
+    kernel<<<grid, 192, smem, s>>>(map, p);
+    return sib_check_launch("attention_prefill_tc");
+}
+
+// Attention of `n_seqs` packed prompts that all start at position 0; `total_rows`
+// is the number of rows of the packed buffer.
+SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_rows, void* out,
+                                        const int* seq_row0, const int* seq_len, int n_seqs,
+                                        int max_len, int n_heads, int n_kv, int head_dim,
+                                        float scale, float softcap, int window, void* stream) {
+    if (n_seqs == 0 || max_len == 0) return 0;
+    SIB_REQUIRE(sib_attention_prefill_tc_supports(n_heads, n_kv, head_dim, width),
+                "attention_prefill_tc: heads=%d kv_heads=%d head_dim=%d is not a shape this kernel "
+                "takes (1 or 2 heads per kv head; head_dim 64, 128 or 256)", n_heads, n_kv, head_dim);
+    SIB_REQUIRE(width == (n_heads + 2 * n_kv) * head_dim && ((uintptr_t)qkv % 16) == 0 &&
+                    ((uintptr_t)out % 16) == 0 && total_rows > 0,
+                "attention_prefill_tc: packed rows of %d elements do not fit the head counts", width);
+    SIB_REQUIRE(n_seqs > 0 && n_seqs < 65536 && n_kv < 65536 && max_len > 0 && window >= 0,
+                "attention_prefill_tc: seqs=%d max_len=%d", n_seqs, max_len);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    SIB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, "attention_prefill_tc: no current device");
+    if (!g_tc_error_flag[dev]) {
+        e = cudaMalloc(&g_tc_error_flag[dev], sizeof(int));
+        SIB_REQUIRE(e == cudaSuccess, "attention_prefill_tc: %s", cudaGetErrorString(e));
+        cudaMemset(g_tc_error_flag[dev], 0, sizeof(int));
+    }
+    EncodeTiledFn enc = tc_encode_fn();
+    SIB_REQUIRE(enc != nullptr, "attention_prefill_tc: cuTensorMapEncodeTiled is not available");
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)total_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SIB_REQUIRE(r == CUDA_SUCCESS, "attention_prefill_tc: cuTensorMapEncodeTiled failed with code %d",
+                (int)r);
+    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, g_tc_error_flag[dev], n_heads, n_kv, window,
+             scale, softcap};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int G = n_heads / n_kv;
+#define BY_G(HD)                                                         \
+    do {                                                                 \
+        if (G == 1) return launch_tc<HD, 1>(map, p, n_seqs, max_len, s); \
+        return launch_tc<HD, 2>(map, p, n_seqs, max_len, s);             \
+    } while (0)
+    if (head_dim == 64) BY_G(64);
+    if (head_dim == 128) BY_G(128);
+    BY_G(256);
+#undef BY_G
+}

@@ -295,6 +295,33 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n
     return out
 
 
+def attention_prefill_tc_supports(n_heads: int, n_kv: int, head_dim: int, width: int) -> bool:
+    return bool(library().sib_attention_prefill_tc_supports(c_int(n_heads), c_int(n_kv),
+                                                            c_int(head_dim), c_int(width)))
+
+
+def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
+                         max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                         softcap: float, window: int) -> torch.Tensor:
+    """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu)."""
+    _want(qkv, torch.bfloat16, "qkv")
+    _want(out, torch.bfloat16, "out")
+    if out.shape[0] != qkv.shape[0] or out.shape[1] != n_heads * head_dim:
+        raise KernelError("attention_prefill_tc: out must be [rows, heads * head_dim]")
+    _check(library().sib_attention_prefill_tc(
+        _ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _ptr(out), _ptr(seq_row0),
+        _ptr(seq_len), c_int(n_seqs), c_int(max_len), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+        c_float(scale), c_float(softcap), c_int(window), _stream()))
+    return out
+
+
+def attention_prefill_tc_error(clear: bool = True) -> int:
+    """0, or the code left by a block of attention_prefill_tc whose bounded wait ran out
+    (synchronises the device)."""
+    torch.cuda.synchronize()
+    return int(library().sib_attention_prefill_tc_error(c_int(1 if clear else 0)))
+
+
 SKINNY_MAX_ROWS = 64
 
 

@@ -18,6 +18,7 @@ borrows another schedule entry's cache projects q only and reads that cache.
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Mapping, Optional
 
 import torch
@@ -31,6 +32,8 @@ from .registry import part_class, register_mixer
 _TARGET_WARPS = 148 * 16
 # the decode kernel keeps 3 blocks of 4 warps resident per SM (its registers decide)
 _RESIDENT_WARPS_DECODE = 148 * 12
+# SIB_PREFILL_TCGEN05=0 selects the mma.sync prompt kernel instead of the tcgen05 one
+_USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 
 
 class Attention:
@@ -120,7 +123,12 @@ class Attention:
 
         out = torch.empty((R, nh * hd), dtype=qkv.dtype, device=qkv.device)
         width = qkv.shape[1]
-        if fresh and qkv.dtype == torch.bfloat16 and \
+        if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and \
+                native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
+            native.attention_prefill_tc(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
+                                        ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,
+                                        self.window)
+        elif fresh and qkv.dtype == torch.bfloat16 and \
                 native.attention_prefill_supports(nh, self.nkv, hd):
             native.attention_prefill(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
                                      ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,

@@ -248,6 +248,38 @@ def test_attention_prefill_kernel(nh, nkv, hd, window, cap):
         _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"prefill, sequence of {T}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,cap", [
+    (4, 2, 64, 0, 0.0), (8, 4, 256, 100, 50.0), (2, 2, 128, 70, 0.0), (8, 4, 256, 0, 0.0),
+    (3, 3, 64, 17, 20.0), (4, 2, 128, 0, 30.0)])
+def test_attention_prefill_tc_kernel(nh, nkv, hd, window, cap):
+    """The tcgen05 prompt kernel on packed prompts of unequal lengths."""
+    n = _native()
+    assert n.attention_prefill_tc_supports(nh, nkv, hd, (nh + 2 * nkv) * hd)
+    assert not n.attention_prefill_tc_supports(8, 2, hd, 12 * hd)
+    g = torch.Generator().manual_seed(15)
+    lens = [200, 5, 64, 131, 300]
+    dtype = torch.bfloat16
+    scale = 3.0 / math.sqrt(hd)
+    qs, refs = [], []
+    for T in lens:
+        q = torch.randn(T, nh, hd, generator=g).to(dtype)
+        k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        refs.append(plain.attention(q.double(), k.double(), v.double(), scale, cap, window))
+        qs.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    packed = torch.cat(qs, dim=0).contiguous().to(DEV)
+    out = torch.full((sum(lens), nh * hd), float("nan"), dtype=dtype, device=DEV)
+    row0 = [0]
+    for T in lens[:-1]:
+        row0.append(row0[-1] + T)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n.attention_prefill_tc(packed, out, i32(row0), i32(lens), len(lens), max(lens), nh, nkv, hd,
+                           scale, cap, window)
+    assert n.attention_prefill_tc_error() == 0
+    for r0, T, ref in zip(row0, lens, refs):
+        _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"tcgen05 prefill, sequence of {T}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
 @pytest.mark.parametrize("hd,rot", [(48, 32), (64, 64), (16, 16)])
