@@ -109,7 +109,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                      smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -120,7 +120,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    tmem_ld32_issue(taddr, r);
+    tmem_ld_wait();
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -139,9 +145,61 @@ __device__ __forceinline__ float tanh_fast(float x) {
     asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Whether key j of the tile is one the row sees.
+__device__ __forceinline__ bool sees(int j, int j_lo, int j_hi) { return j >= j_lo && j <= j_hi; }
+
+// The largest of a row's 64 raw products (of those it sees, with MASK).
+template <bool MASK>
+__device__ __forceinline__ float row_max(const uint32_t (&raw)[64], int j_lo, int j_hi) {
+    float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 64; ++j) {
+        float v = __uint_as_float(raw[j]);
+        if (MASK) v = sees(j, j_lo, j_hi) ? v : -INFINITY;
+        m[j & 3] = fmaxf(m[j & 3], v);
+    }
+    return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
+
+// A row's 64 probabilities 2^(score - ref) as bfloat16 into its 128 bytes of the
+// swizzled tile; returns their sum.  CAP: score = c2 * tanh(product * c1), else
+// product * c1.
+template <bool CAP, bool MASK>
+__device__ __forceinline__ float probabilities(const uint32_t (&raw)[64], float c1, float c2,
+                                               float ref, int j_lo, int j_hi, unsigned char* prow,
+                                               int row) {
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float e[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int j = 8 * c + 2 * k + h;
+                float x = __uint_as_float(raw[j]);
+                if (CAP) x = fmaf(c2, tanh_fast(x * c1), -ref);
+                else x = fmaf(x, c1, -ref);
+                if (MASK) x = sees(j, j_lo, j_hi) ? x : -INFINITY;
+                e[h] = exp2_fast(x);
+            }
+            sum[k] += e[0] + e[1];
+            w[k] = pack_bf16(e[0], e[1]);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
 
 struct TcArgs {
@@ -156,7 +214,7 @@ struct TcArgs {
 
 // Barriers of one block.
 struct Bars {
-    uint64_t q_full, kv_full[2], kv_empty[2], s_full, s_free, p_full, pv_done;
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_free, p_full, pv_done, o_done;
 };
 
 }  // namespace
@@ -175,8 +233,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     unsigned char* Qs = base;                              // CH blocks of [128 rows x 128 B]
     unsigned char* Ks = Qs + Q_BYTES;                      // 2 stages of CH blocks of [64 x 128 B]
     unsigned char* Vs = Ks + 2 * KV_BYTES;                 // the same
-    unsigned char* Ps = Vs + 2 * KV_BYTES;                 // [128 rows x 128 B]
-    Bars* bars = reinterpret_cast<Bars*>(Ps + P_BYTES);
+    unsigned char* Ps = Vs + 2 * KV_BYTES;                 // 2 buffers of [128 rows x 128 B]
+    Bars* bars = reinterpret_cast<Bars*>(Ps + 2 * P_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
     int* failed = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -196,13 +254,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&bars->kv_full[s], 1);
-            mbar_init(&bars->kv_empty[s], 1);
+            mbar_init(&bars->k_full[s], 1);
+            mbar_init(&bars->k_empty[s], 1);
+            mbar_init(&bars->v_full[s], 1);
+            mbar_init(&bars->v_empty[s], 1);
         }
         mbar_init(&bars->s_full, 1);
         mbar_init(&bars->s_free, 4);
         mbar_init(&bars->p_full, 4);
         mbar_init(&bars->pv_done, 1);
+        mbar_init(&bars->o_done, 1);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -228,18 +289,32 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
                     tma_load_2d(Qs + c * (BM * 128) + half * (64 * 128), &map, &bars->q_full,
                                 q_col + head * HD + 64 * c, row0 + p0 + off);
                 }
-            for (int t = 0; t < nt; ++t) {
+            // Keys run one tile ahead of values: a key tile is free again once its scores
+            // have been formed, a value tile only after the product that follows them.
+            auto load_k = [&](int t) -> bool {
                 const int s = t & 1;
-                if (t >= 2 && !mbar_wait(&bars->kv_empty[s], ((t >> 1) - 1) & 1)) { *failed = 1; break; }
-                mbar_arrive_expect_tx(&bars->kv_full[s], 2 * KV_BYTES);
-                const int krow = row0 + (kt0 + t) * 64;
-                for (int c = 0; c < CH; ++c) {
-                    tma_load_2d(Ks + s * KV_BYTES + c * (BN * 128), &map, &bars->kv_full[s],
-                                k_col + 64 * c, krow);
-                    tma_load_2d(Vs + s * KV_BYTES + c * (BN * 128), &map, &bars->kv_full[s],
-                                v_col + 64 * c, krow);
-                }
+                if (t >= 2 && !mbar_wait(&bars->k_empty[s], ((t >> 1) - 1) & 1)) return false;
+                mbar_arrive_expect_tx(&bars->k_full[s], KV_BYTES);
+                for (int c = 0; c < CH; ++c)
+                    tma_load_2d(Ks + s * KV_BYTES + c * (BN * 128), &map, &bars->k_full[s],
+                                k_col + 64 * c, row0 + (kt0 + t) * 64);
+                return true;
+            };
+            auto load_v = [&](int t) -> bool {
+                const int s = t & 1;
+                if (t >= 2 && !mbar_wait(&bars->v_empty[s], ((t >> 1) - 1) & 1)) return false;
+                mbar_arrive_expect_tx(&bars->v_full[s], KV_BYTES);
+                for (int c = 0; c < CH; ++c)
+                    tma_load_2d(Vs + s * KV_BYTES + c * (BN * 128), &map, &bars->v_full[s],
+                                v_col + 64 * c, row0 + (kt0 + t) * 64);
+                return true;
+            };
+            bool fed = nt == 0 || load_k(0);
+            for (int t = 0; t < nt && fed; ++t) {
+                if (t + 1 < nt) fed = load_k(t + 1);
+                fed = fed && load_v(t);
             }
+            if (!fed) *failed = 1;
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -258,10 +333,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
                     const uint64_t db = desc_k_major(kt + (j >> 2) * (BN * 128)) + 2 * (j & 3);
                     umma_bf16(tmem, da, db, IDESC_QK, j > 0 ? 1u : 0u);
                 }
+                umma_commit(&bars->k_empty[t & 1]);
                 umma_commit(&bars->s_full);
             };
             if (ok) {
-                if (!mbar_wait(&bars->kv_full[0], 0)) { *failed = 3; ok = false; }
+                if (!mbar_wait(&bars->k_full[0], 0)) { *failed = 3; ok = false; }
             }
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -270,27 +346,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             for (int t = 0; t < nt && ok; ++t) {
                 if (t + 1 < nt) {
                     // the next tile's scores as soon as this tile's have been read
-                    if (!mbar_wait(&bars->kv_full[(t + 1) & 1], ((t + 1) >> 1) & 1) ||
+                    if (!mbar_wait(&bars->k_full[(t + 1) & 1], ((t + 1) >> 1) & 1) ||
                         !mbar_wait(&bars->s_free, t & 1)) { *failed = 4; ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     issue_qk(t + 1);
                 }
-                if (!mbar_wait(&bars->p_full, t & 1)) { *failed = 5; ok = false; break; }
+                if (!mbar_wait(&bars->p_full, t & 1) ||
+                    !mbar_wait(&bars->v_full[t & 1], (t >> 1) & 1)) { *failed = 5; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // O += P V(t): 4 steps of 16 keys; V rows are keys (MN-major operand)
                 const unsigned char* vt = Vs + (t & 1) * KV_BYTES;
 #pragma unroll
                 for (int j = 0; j < BN / 16; ++j) {
-                    const uint64_t da = desc_k_major(Ps) + 2 * j;
+                    const uint64_t da = desc_k_major(Ps + (t & 1) * P_BYTES) + 2 * j;
                     const uint64_t db = desc_mn_major(vt + j * (16 * 128), BN * 128);
                     umma_bf16(tmem + O_COL, da, db, IDESC_PV, (t > 0 || j > 0) ? 1u : 0u);
                 }
-                umma_commit(&bars->kv_empty[t & 1]);
+                umma_commit(&bars->v_empty[t & 1]);
                 umma_commit(&bars->pv_done);
+                if (t == nt - 1) umma_commit(&bars->o_done);
             }
             if (!ok) {   // let nobody wait for what will not come
                 umma_commit(&bars->s_full);
                 umma_commit(&bars->pv_done);
+                umma_commit(&bars->o_done);
             }
         }
     } else {
@@ -299,52 +378,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
         const int head = kvh * G + row / MP;
         const int pos = p0 + row % MP;
         const uint32_t lane_addr = tmem + ((uint32_t)(32 * quarter) << 16);
-        const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
+        // score in units of log 2: c2 * tanh(product * c1) with a cap, product * c1 without
+        constexpr float LOG2E = 1.4426950408889634f;
+        constexpr float RAISE_BY = 8.0f;
+        const bool capped = p.softcap > 0.f;
+        const float c1 = capped ? p.scale / p.softcap : p.scale * LOG2E;
+        const float c2 = p.softcap * LOG2E;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int t = 0; t < nt && ok; ++t) {
             if (!mbar_wait(&bars->s_full, t & 1)) { if (lane == 0) *failed = 6; ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t raw[2][32];
-            tmem_ld32(lane_addr, raw[0]);
-            tmem_ld32(lane_addr + 32, raw[1]);
+            uint32_t raw[64];
+            tmem_ld32_issue(lane_addr, raw);
+            tmem_ld32_issue(lane_addr + 32, raw + 32);
+            tmem_ld_wait();
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->s_free);
-            // scale, cap, mask; the row's maximum
+            // Which of the tile's keys the row sees: j in [j_lo, j_hi].  A warp whose rows
+            // all see the whole tile takes the path without the mask.
             const int key0 = (kt0 + t) * 64;
-            const bool inside = key0 + 63 <= pos && key0 + 63 < n &&
-                                (p.window <= 0 || pos - key0 < p.window);
-            float mx = -INFINITY;
-            float sc[64];
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                float v = __uint_as_float(raw[j >> 5][j & 31]) * p.scale;
-                if (p.softcap > 0.f) v = p.softcap * tanh_fast(v * inv_cap);
-                if (!inside) {
-                    const int key = key0 + j;
-                    const bool seen = key <= pos && key < n && (p.window <= 0 || pos - key < p.window);
-                    v = seen ? v : -INFINITY;
-                }
-                sc[j] = v;
-                mx = fmaxf(mx, v);
-            }
+            const int j_hi = min(pos, n - 1) - key0;
+            const int j_lo = p.window > 0 ? pos - p.window + 1 - key0 : -(1 << 30);
+            const bool whole = __all_sync(0xffffffffu, j_lo <= 0 && j_hi >= 63);
+            // The row's maximum, taken on the raw products: scaling by a positive factor and
+            // the cap are both increasing, so the largest product gives the largest score.
+            float mx_raw;
+            if (whole) mx_raw = row_max<false>(raw, j_lo, j_hi);
+            else mx_raw = row_max<true>(raw, j_lo, j_hi);
+            // scores are kept in units of log 2: probabilities are 2^(score - reference)
+            float mx = mx_raw * c1;
+            if (capped) mx = c2 * tanh_fast(mx);
+            if (mx_raw == -INFINITY) mx = -INFINITY;
             // the reference the exponentials are taken against: raised only by big steps
             float factor = 1.f;
             bool raise = false;
             if (t == 0) {
                 m_ref = mx;
-            } else if (mx > m_ref + 5.5f) {
+            } else if (mx > m_ref + RAISE_BY) {
                 raise = true;
-                factor = __expf(m_ref - mx);          // 0 when the row had seen no key yet
+                factor = exp2_fast(m_ref - mx);       // 0 when the row had seen no key yet
                 m_ref = mx;
             }
-            if (t > 0) {
-                // P's buffer and O are free once the previous tile's P V has run
+            if (__any_sync(0xffffffffu, raise)) {
+                // O may be touched once the previous tile's P V has run
                 if (!mbar_wait(&bars->pv_done, (t - 1) & 1)) { if (lane == 0) *failed = 7; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            }
-            if (__any_sync(0xffffffffu, raise)) {
                 l *= factor;
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
@@ -358,18 +438,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             }
             const float ref = m_ref == -INFINITY ? 0.f : m_ref;
             // probabilities into the K-major, 128-byte-swizzled tile the MMA reads
-            unsigned char* prow = Ps + row * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float e0 = __expf(sc[8 * c + 2 * k] - ref);
-                    const float e1 = __expf(sc[8 * c + 2 * k + 1] - ref);
-                    l += e0 + e1;
-                    w[k] = pack_bf16(e0, e1);
-                }
-                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            // (this buffer's last reader, the product two tiles back, was issued before the
+            // scores of this tile, so it has run)
+            unsigned char* prow = Ps + (t & 1) * P_BYTES + row * 128;
+            if (capped) {
+                if (whole) l += probabilities<true, false>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
+                else l += probabilities<true, true>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
+            } else {
+                if (whole) l += probabilities<false, false>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
+                else l += probabilities<false, true>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -377,7 +454,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             if (lane == 0) mbar_arrive(&bars->p_full);
         }
         if (ok && nt > 0) {
-            if (!mbar_wait(&bars->pv_done, (nt - 1) & 1)) { if (lane == 0) *failed = 8; ok = false; }
+            // (pv_done is not waited for tile by tile, so its phase cannot tell the last
+            // product from the one before it)
+            if (!mbar_wait(&bars->o_done, 0)) { if (lane == 0) *failed = 8; ok = false; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         }
         if (ok) {
@@ -453,7 +532,7 @@ SIB_EXPORT int sib_attention_prefill_tc_supports(int n_heads, int n_kv, int head
 template <int HD, int G>
 static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int max_len,
                      cudaStream_t s) {
-    const size_t smem = 1024 + (size_t)BM * HD * 2 + 4 * (size_t)BN * HD * 2 + BM * BN * 2 +
+    const size_t smem = 1024 + (size_t)BM * HD * 2 + 4 * (size_t)BN * HD * 2 + 2 * BM * BN * 2 +
                         sizeof(Bars) + 16;
     auto kernel = attention_prefill_tc_kernel<HD, G>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -482,6 +561,9 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
                 "attention_prefill_tc: packed rows of %d elements do not fit the head counts", width);
     SIB_REQUIRE(n_seqs > 0 && n_seqs < 65536 && n_kv < 65536 && max_len > 0 && window >= 0,
                 "attention_prefill_tc: seqs=%d max_len=%d", n_seqs, max_len);
+    // the row maximum is taken before scaling, which holds for a positive factor only
+    SIB_REQUIRE(scale > 0.f && softcap >= 0.f, "attention_prefill_tc: score scale %g and cap %g "
+                "must be positive (cap 0: none)", (double)scale, (double)softcap);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     SIB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, "attention_prefill_tc: no current device");

@@ -123,7 +123,7 @@ class Attention:
 
         out = torch.empty((R, nh * hd), dtype=qkv.dtype, device=qkv.device)
         width = qkv.shape[1]
-        if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and \
+        if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
                 native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
             native.attention_prefill_tc(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
                                         ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,
