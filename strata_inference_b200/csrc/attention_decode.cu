@@ -3,8 +3,9 @@
 // (scale, soft cap, causal and window mask, softmax in 32-bit, weighted sum of
 // v); this file only changes how the work is laid out:
 //
-// * one warp per (row, kv head, split): the G = n_heads / n_kv query heads that
-//   share a kv head are done together, so each key and value is read once;
+// * one block of 1, 2 or 4 warps per (row, kv head, split), each warp an equal
+//   share of the split's keys: the G = n_heads / n_kv query heads that share a kv
+//   head are done together, so each key and value is read once;
 // * keys are walked in tiles of 16 positions, aligned so that a tile lies in
 //   one page.  Scores of a tile are one mma.m16n8k16 chain: the 16 keys are the
 //   A operand, the (up to 8) query heads the B operand, fragments loaded
@@ -14,8 +15,11 @@
 //   weighted sum of v runs on the CUDA cores with each lane owning 8 consecutive
 //   dimensions of a value row (a 16-byte load), several keys per pass when the
 //   head is narrower than 256;
-// * with splits > 1 the partial (max, sum, accumulator) of each split goes to
-//   scratch memory in the layout attention_combine reads.
+// * the warps' partial (max, sum, accumulator) are joined in shared memory.  With
+//   splits > 1 the block's partial goes to scratch memory and the block takes a
+//   ticket of its (row, kv head); the block that draws the last ticket joins all
+//   the splits and writes the output, so no second kernel is needed.  The ticket
+//   counters are zero between launches: the last block puts its counter back.
 //
 // Plain counterpart: tests/plain_gemma2.py attention().
 // Reference: src/backend/cuda/kernels.rs:2851-3180 (grouped_attn_decode: one block
@@ -28,6 +32,7 @@ struct AttnDecodeArgs {
     const __nv_bfloat16* v_pool;
     __nv_bfloat16* out;       // [rows, n_heads * head_dim]
     float* partial;           // [rows, n_heads, splits, head_dim + 2]
+    int* tickets;             // [rows, n_kv], zero between launches
     const int* row_pos;
     const int* row_seq;
     const int* seq_slot;
@@ -65,23 +70,30 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
     }
 }
 
+// The most splits of a (row, kv head) a launch takes.
+constexpr int MAX_SPLITS = 128;
+
 // HD: head size (64, 128 or 256).  G: query heads per kv head (1, 2, 4 or 8).
 template <int HD, int G>
 __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p) {
     constexpr int KB = HD / 32;          // 32-wide blocks of the head dimension
     constexpr int LPK = HD / 8;          // lanes that cover one value row
     constexpr int KPP = 32 / LPK;        // keys per pass of the weighted sum
+    constexpr int PW = HD + 2;           // a partial: max, sum, HD accumulators
     __shared__ float sm_all[4][2][16][8];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    extern __shared__ __align__(16) float part_dyn[];          // [warps][G][PW]
+    float(*part_sm)[G][PW] = reinterpret_cast<float(*)[G][PW]>(part_dyn);
+    __shared__ float w_sm[G][MAX_SPLITS];
+    __shared__ float ml_sm[G][2];
+    __shared__ int ticket_sm;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float(*s_sm)[8] = sm_all[warp][0];
     float(*p_sm)[8] = sm_all[warp][1];
     pdl_trigger();
     pdl_wait();
-    const long long unit = (long long)blockIdx.x * 4 + warp;
-    if (unit >= (long long)p.rows * p.n_kv * p.splits) return;
-    const int split = (int)(unit % p.splits);
-    const int kvh = (int)((unit / p.splits) % p.n_kv);
-    const int r = (int)(unit / ((long long)p.splits * p.n_kv));
+    const int split = (int)(blockIdx.x % p.splits);
+    const int kvh = (int)((blockIdx.x / p.splits) % p.n_kv);
+    const int r = (int)(blockIdx.x / ((unsigned)p.splits * p.n_kv));
     const int g = lane >> 2, t = lane & 3;
 
     const int pos = p.row_pos[r];
@@ -89,8 +101,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int tile_lo = lo >> 4, tile_hi = pos >> 4;             // inclusive
     const int n_tiles = tile_hi - tile_lo + 1;
-    const int per = (n_tiles + p.splits - 1) / p.splits;
-    const int t0 = tile_lo + split * per;
+    const int per = (n_tiles + nw * p.splits - 1) / (nw * p.splits);
+    const int t0 = tile_lo + (split * nw + warp) * per;
     const int t1 = min(t0 + per, tile_hi + 1);
     const int* table = p.page_table + (size_t)slot * p.max_pages;
 
@@ -200,26 +212,96 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
     }
-    if (sub != 0) return;
+    // ---- the warps' partials joined in shared memory ----
+    if (sub == 0) {
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        const int head = kvh * G + h;
-        if (p.splits == 1) {
-            const float inv = 1.0f / l[h];
-            __nv_bfloat16* op = p.out + (size_t)r * p.n_heads * HD + (size_t)head * HD + dim0;
-            uint4 packed;
-            __nv_bfloat162* pk = reinterpret_cast<__nv_bfloat162*>(&packed);
+        for (int h = 0; h < G; ++h) {
+            if (lane == 0) { part_sm[warp][h][0] = m[h]; part_sm[warp][h][1] = l[h]; }
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                pk[e] = __floats2bfloat162_rn(acc[h][2 * e] * inv, acc[h][2 * e + 1] * inv);
-            *reinterpret_cast<uint4*>(op) = packed;
-        } else {
-            float* pp = p.partial + (((size_t)r * p.n_heads + head) * p.splits + split) * (HD + 2);
-            if (lane == 0) { pp[0] = m[h]; pp[1] = l[h]; }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) pp[2 + dim0 + e] = acc[h][e];
+            for (int e = 0; e < 8; ++e) part_sm[warp][h][2 + dim0 + e] = acc[h][e];
         }
     }
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const int h = threadIdx.x;
+        float mx = -INFINITY;
+        for (int w = 0; w < nw; ++w) mx = fmaxf(mx, part_sm[w][h][0]);
+        float sum = 0.f;
+        for (int w = 0; w < nw; ++w) {
+            const float mw = part_sm[w][h][0];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - mx);   // a warp without keys
+            w_sm[h][w] = f;
+            sum += f * part_sm[w][h][1];
+        }
+        ml_sm[h][0] = mx;
+        ml_sm[h][1] = sum;
+    }
+    __syncthreads();
+    __nv_bfloat16* out_row = p.out + (size_t)r * p.n_heads * HD + (size_t)kvh * G * HD;
+    float* my_partial = p.partial + (((size_t)r * p.n_heads + kvh * G) * p.splits + split) * PW;
+    for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
+        const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
+        float2 a = make_float2(0.f, 0.f);
+        for (int w = 0; w < nw; ++w) {
+            const float f = w_sm[h][w];
+            const float2 v = *reinterpret_cast<const float2*>(&part_sm[w][h][2 + d]);
+            a.x += f * v.x;
+            a.y += f * v.y;
+        }
+        if (p.splits == 1) {
+            const float inv = 1.0f / ml_sm[h][1];
+            *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
+                __floats2bfloat162_rn(a.x * inv, a.y * inv);
+        } else {
+            float* pp = my_partial + (size_t)h * p.splits * PW;
+            if (d == 0) *reinterpret_cast<float2*>(pp) = make_float2(ml_sm[h][0], ml_sm[h][1]);
+            *reinterpret_cast<float2*>(pp + 2 + d) = a;
+        }
+    }
+    if (p.splits == 1) return;
+
+    // ---- the block that finishes last joins the splits ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_sm = atomicAdd(p.tickets + r * p.n_kv + kvh, 1);
+    __syncthreads();
+    if (ticket_sm != p.splits - 1) return;
+    __threadfence();
+    const float* unit_partial = p.partial + ((size_t)r * p.n_heads + kvh * G) * p.splits * PW;
+    for (int i = threadIdx.x; i < G * p.splits; i += blockDim.x)
+        w_sm[i / p.splits][i % p.splits] = __ldcg(unit_partial + (size_t)i * PW);       // the maxima
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const int h = threadIdx.x;
+        float mx = -INFINITY;
+        for (int b = 0; b < p.splits; ++b) mx = fmaxf(mx, w_sm[h][b]);
+        ml_sm[h][0] = mx;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * p.splits; i += blockDim.x) {
+        const int h = i / p.splits, b = i % p.splits;
+        const float mb = w_sm[h][b];
+        w_sm[h][b] = mb == -INFINITY ? 0.f : expf(mb - ml_sm[h][0]);
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
+        const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
+        const float* pp = unit_partial + (size_t)h * p.splits * PW;
+        float2 a = make_float2(0.f, 0.f);
+        float sum = 0.f;
+#pragma unroll 4
+        for (int b = 0; b < p.splits; ++b) {
+            const float f = w_sm[h][b];
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + (size_t)b * PW + 2 + d));
+            sum += f * __ldcg(pp + (size_t)b * PW + 1);
+            a.x += f * v.x;
+            a.y += f * v.y;
+        }
+        const float inv = 1.0f / sum;
+        *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
+            __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    }
+    if (threadIdx.x == 0) p.tickets[r * p.n_kv + kvh] = 0;
 }
 
 // 1 if this kernel takes the shape (else the caller uses attention_rows).
@@ -231,21 +313,24 @@ SIB_EXPORT int sib_attention_decode_supports(int n_heads, int n_kv, int head_dim
     return g_ok && hd_ok && page_tokens % 16 == 0;
 }
 
-int sib_launch_attention_combine_bf16(const float* partial, void* out, int units, int splits,
-                                      int head_dim, cudaStream_t s);
-
 SIB_EXPORT int sib_attention_decode(
     const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
     int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
-    const int* seq_slot, void* out, float* partial, int rows, int n_heads, int n_kv, int head_dim,
-    float scale, float softcap, int window, int splits, void* stream) {
+    const int* seq_slot, void* out, float* partial, int* tickets, int rows, int n_heads, int n_kv,
+    int head_dim, float scale, float softcap, int window, int splits, int warps, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(sib_attention_decode_supports(n_heads, n_kv, head_dim, page_tokens),
                 "attention_decode: heads=%d kv_heads=%d head_dim=%d page_tokens=%d is not a shape "
                 "this kernel takes (groups of 1, 2, 4 or 8 heads; head_dim 64, 128 or 256; pages "
                 "in multiples of 16)", n_heads, n_kv, head_dim, page_tokens);
-    SIB_REQUIRE(rows > 0 && splits >= 1 && (splits == 1 || partial != nullptr),
-                "attention_decode: rows=%d splits=%d", rows, splits);
+    SIB_REQUIRE(rows > 0 && splits >= 1 && splits <= MAX_SPLITS,
+                "attention_decode: rows=%d splits=%d (1 to %d)", rows, splits, MAX_SPLITS);
+    SIB_REQUIRE(warps == 1 || warps == 2 || warps == 4,
+                "attention_decode: %d warps a block; 1, 2 or 4", warps);
+    SIB_REQUIRE(splits == 1 || (partial != nullptr && tickets != nullptr &&
+                                ((uintptr_t)partial % 16) == 0),
+                "attention_decode: %d splits need memory for their partial results and the "
+                "ticket counters of the (row, kv head) pairs", splits);
     SIB_REQUIRE(k_pool && v_pool && page_table && max_pages > 0,
                 "attention_decode: incomplete cache description");
     SIB_REQUIRE(ring_tokens >= 0 && ring_tokens % 16 == 0 && window >= 0,
@@ -254,16 +339,16 @@ SIB_EXPORT int sib_attention_decode(
                     ((uintptr_t)v_pool % 16) == 0 && ((uintptr_t)out % 16) == 0,
                 "attention_decode: operands must be 16-byte aligned");
     AttnDecodeArgs p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-                     (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, partial, row_pos, row_seq,
+                     (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, partial, tickets, row_pos, row_seq,
                      seq_slot, page_table, q_stride, rows, n_heads, n_kv, max_pages, page_tokens,
                      ring_tokens, window, splits, scale, softcap};
-    const long long units = (long long)rows * n_kv * splits;
-    const long long blocks = (units + 3) / 4;
+    const long long blocks = (long long)rows * n_kv * splits;
     SIB_REQUIRE(blocks < (1ll << 31), "attention_decode: too many rows (%d)", rows);
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;
 #define GO(HD, GG) \
-    sib_launch_chained(attention_decode_kernel<HD, GG>, dim3((unsigned)blocks), dim3(128), 0, s, p)
+    sib_launch_chained(attention_decode_kernel<HD, GG>, dim3((unsigned)blocks), dim3(32 * warps), \
+                       (size_t)warps * GG * (HD + 2) * sizeof(float), s, p)
 #define BY_G(HD)                  \
     do {                          \
         if (G == 1) GO(HD, 1);    \
@@ -276,9 +361,7 @@ SIB_EXPORT int sib_attention_decode(
     else BY_G(256);
 #undef BY_G
 #undef GO
-    int rc = sib_check_launch("attention_decode");
-    if (rc || splits == 1) return rc;
-    return sib_launch_attention_combine_bf16(partial, out, rows * n_heads, splits, head_dim, s);
+    return sib_check_launch("attention_decode");
 }
 
 // ---------------------------------------------------------------------------
@@ -320,10 +403,16 @@ static int no_alloc_scratch_address(float** address) {
     return 0;
 }
 
+// The ticket counters come first, one per (row, kv head) and never more than one per
+// (row, head), rounded up to 64 entries; the partial results follow.
+static long long no_alloc_ticket_floats(int rows, int n_heads) {
+    return ((long long)rows * n_heads + 63) / 64 * 64;
+}
+
 SIB_EXPORT long long sib_attention_decode_no_alloc_floats(int rows, int n_heads, int head_dim,
                                                           int splits) {
     if (splits <= 1) return 0;
-    return (long long)rows * n_heads * splits * (head_dim + 2);
+    return no_alloc_ticket_floats(rows, n_heads) + (long long)rows * n_heads * splits * (head_dim + 2);
 }
 
 SIB_EXPORT int sib_attention_decode_no_alloc(
@@ -336,14 +425,15 @@ SIB_EXPORT int sib_attention_decode_no_alloc(
                 head_dim, splits);
     const long long need = sib_attention_decode_no_alloc_floats(rows, n_heads, head_dim, splits);
     SIB_REQUIRE(need <= (long long)NO_ALLOC_SCRATCH_FLOATS,
-                "attention_decode_no_alloc: %d rows x %d heads x %d splits x (%d + 2) = %lld floats "
-                "of partial results, the built-in array holds %u; use fewer splits or rows, or "
-                "sib_attention_decode with memory of your own",
+                "attention_decode_no_alloc: %d rows x %d heads x %d splits x (%d + 2) floats of "
+                "partial results and the ticket counters come to %lld floats, the built-in array "
+                "holds %u; use fewer splits or rows, or sib_attention_decode with memory of your own",
                 rows, n_heads, splits, head_dim, need, NO_ALLOC_SCRATCH_FLOATS);
     float* scratch = nullptr;
     const int rc = no_alloc_scratch_address(&scratch);   // the first call on a device sets it up
     if (rc) return rc;
     return sib_attention_decode(q, q_stride, k_pool, v_pool, page_table, max_pages, page_tokens,
-                                ring_tokens, row_pos, row_seq, seq_slot, out, scratch, rows, n_heads,
-                                n_kv, head_dim, scale, softcap, window, splits, stream);
+                                ring_tokens, row_pos, row_seq, seq_slot, out,
+                                scratch + no_alloc_ticket_floats(rows, n_heads), (int*)scratch, rows,
+                                n_heads, n_kv, head_dim, scale, softcap, window, splits, 4, stream);
 }

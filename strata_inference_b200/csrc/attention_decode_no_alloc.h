@@ -16,21 +16,26 @@
 // Every GPU on which this library is loaded holds it from load until the process
 // exits, whether or not this entry point is ever called.
 //
-// Limits.  rows * n_heads * splits * (head_dim + 2) must not exceed
-// NO_ALLOC_SCRATCH_FLOATS when splits > 1; a larger request is refused with an
-// error (sib_last_error() says how many floats were asked for), nothing is
+// Limits.  With splits > 1 a call uses rows * n_heads * splits * (head_dim + 2)
+// floats for partial results and, in front of them, rows * n_heads ticket
+// counters rounded up to 64 (sib_attention_decode_no_alloc_floats gives the sum);
+// that must not exceed NO_ALLOC_SCRATCH_FLOATS.  A larger request is refused with
+// an error (sib_last_error() says how many floats were asked for), nothing is
 // launched.  With splits == 1 the array is not used.
 //
 // Behaviour.  Arguments, result and arithmetic are those of sib_attention_decode
-// without its `partial` argument.  It calls no cudaMalloc, no cudaFree and no
+// without its `partial` and `tickets` arguments.  It calls no cudaMalloc, no cudaFree and no
 // allocating library routine.  The first call on a device looks up the array's
 // device address (cudaGetSymbolAddress, with that device current) and keeps it;
 // make that first call on each device before any stream capture begins.  All
-// calls share the one array and it keeps what the last call left there.  Nothing
-// in it has to start at zero: every element the merge step reads is written by
-// the same call's first kernel beforehand.  Two calls that overlap on the GPU
+// calls share the one array.  The partial results need no initial value: every
+// element that is read was written earlier in the same launch.  The ticket
+// counters have to be zero when a launch begins; they are, because the array is
+// zero when the library is loaded and the block that draws the last ticket of a
+// (row, kv head) puts that counter back.  Two calls that overlap on the GPU
 // (different streams, or several host threads) write over each other's partial
-// results: run calls that use splits > 1 one after another on a device.
+// results and tickets: run calls that use splits > 1 one after another on a
+// device.
 #pragma once
 
 #include "common.cuh"

@@ -30,7 +30,7 @@ from ..weights.loader import TensorDecl
 from .registry import part_class, register_mixer
 
 _TARGET_WARPS = 148 * 16
-# the decode kernel keeps 3 blocks of 4 warps resident per SM (its registers decide)
+# the decode kernel keeps 12 warps resident per SM (its registers decide)
 _RESIDENT_WARPS_DECODE = 148 * 12
 # SIB_PREFILL_TCGEN05=0 selects the mma.sync prompt kernel instead of the tcgen05 one
 _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
@@ -77,19 +77,29 @@ class Attention:
         return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
 
     # ------------------------------------------------------------------
-    def _splits(self, ctx, capacity: int, per_kv_head: bool = False) -> int:
-        """How many runs of keys each unit of work (a row's head, or the heads
-        of one kv head) is cut into when it reads the cache: as many as fit on
-        the device at once (a second, partly filled wave of blocks costs more
-        than it brings), no run shorter than a few tiles of keys."""
+    def _longest(self, ctx, capacity: int) -> int:
         longest = capacity if ctx.graph_capture else ctx.max_end
-        if self.window > 0:
-            longest = min(longest, self.window)
-        units = max(1, ctx.n_rows * (self.nkv if per_kv_head else self.nh))
-        resident = _RESIDENT_WARPS_DECODE if per_kv_head else _TARGET_WARPS
-        want = max(1, resident // units)
-        shortest = 64 if per_kv_head else 32
-        return max(1, min(want, -(-longest // shortest), 128))
+        return min(longest, self.window) if self.window > 0 else longest
+
+    def _splits(self, ctx, capacity: int) -> int:
+        """How many runs of keys the general kernel cuts a (row, head) into, one
+        warp each: as many as fill the device once, none shorter than 32 keys."""
+        want = max(1, _TARGET_WARPS // max(1, ctx.n_rows * self.nh))
+        return max(1, min(want, -(-self._longest(ctx, capacity) // 32), 128))
+
+    def _decode_shape(self, ctx, capacity: int):
+        """(runs, warps) for the decode kernel: each (row, kv head) is read by
+        ``runs`` blocks of ``warps`` warps.  All of them should be resident at
+        once (a second, partly filled wave of blocks costs more than it brings)
+        and be about as many warps as that allows; a warp takes no fewer than 32
+        keys."""
+        units = max(1, ctx.n_rows * self.nkv)
+        most = max(1, min(_RESIDENT_WARPS_DECODE // units, -(-self._longest(ctx, capacity) // 32)))
+        for warps in (4, 2):     # wider blocks leave fewer partial results to join
+            runs = min(most // warps, 128)
+            if runs >= 1 and runs * warps >= 0.9 * most:
+                return runs, warps
+        return min(most, 128), 1
 
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
@@ -142,14 +152,15 @@ class Attention:
                                   self.nkv, hd, self.scale, self.softcap, self.window, 1)
         elif qkv.dtype == torch.bfloat16 and native.attention_decode_supports(
                 nh, self.nkv, hd, view.page_tokens):
-            splits = self._splits(ctx, ctx.cache.max_seq_len, per_kv_head=True)
-            scratch = None
+            splits, warps = self._decode_shape(ctx, ctx.cache.max_seq_len)
+            scratch = tickets = None
             if splits > 1:
                 scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, hd, splits))
+                tickets = rt.tickets(R * self.nkv)
             native.attention_decode(qkv, width, view.k, view.v, view.page_table, view.page_tokens,
                                     view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot, out,
-                                    scratch, nh, self.nkv, hd, self.scale, self.softcap,
-                                    self.window, splits)
+                                    scratch, tickets, nh, self.nkv, hd, self.scale, self.softcap,
+                                    self.window, splits, warps)
         else:
             splits = self._splits(ctx, ctx.cache.max_seq_len)
             scratch = None

@@ -64,6 +64,8 @@ class Runtime:
         # is ahead of the library product up to 16 rows and behind it from 32 on.
         self.skinny_max_rows = 16
         self._scratch: Optional[torch.Tensor] = None
+        self._tickets: Optional[torch.Tensor] = None
+        self._retired: list = []       # outgrown buffers that captured graphs may still name
 
     def cast_matrix(self, w: torch.Tensor) -> torch.Tensor:
         """A weight matrix in the compute type, contiguous, on the device."""
@@ -75,6 +77,14 @@ class Runtime:
             self._scratch = torch.empty(max(n_bytes, 1 << 20), dtype=torch.uint8,
                                         device=self.device)
         return self._scratch
+
+    def tickets(self, n: int) -> torch.Tensor:
+        """At least ``n`` int32 counters that are zero whenever no kernel is
+        running: kernels that count their blocks through them put them back."""
+        if self._tickets is None or self._tickets.numel() < n:
+            self._retired.append(self._tickets)
+            self._tickets = torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device)
+        return self._tickets
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                epilogue: int = native.EPI_NONE, cap: float = 0.0) -> torch.Tensor:

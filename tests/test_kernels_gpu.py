@@ -166,10 +166,11 @@ def test_attention_rows_over_cache_and_fresh(dtype, nh, nkv, hd, window, cap, sp
     _close(out[T:].view(T2, nh, hd), ref[:T2], dtype, "fresh rows, sequence 1", factor=4)
 
 
-@pytest.mark.parametrize("nh,nkv,hd,window,cap,splits", [
-    (4, 2, 64, 0, 0.0, 1), (8, 4, 256, 40, 50.0, 5), (8, 1, 128, 0, 30.0, 3),
-    (2, 2, 128, 21, 0.0, 16), (8, 4, 256, 0, 0.0, 2), (4, 1, 256, 100, 50.0, 1)])
-def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits):
+@pytest.mark.parametrize("nh,nkv,hd,window,cap,splits,warps", [
+    (4, 2, 64, 0, 0.0, 1, 4), (8, 4, 256, 40, 50.0, 5, 4), (8, 1, 128, 0, 30.0, 3, 2),
+    (2, 2, 128, 21, 0.0, 16, 1), (8, 4, 256, 0, 0.0, 2, 1), (4, 1, 256, 100, 50.0, 1, 2),
+    (8, 4, 256, 0, 50.0, 1, 1), (16, 2, 64, 0, 0.0, 7, 4)])
+def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits, warps):
     """The bfloat16 decode kernel: rows at tile and page edges, with and
     without a ring, several rows of different sequences in one launch."""
     n = _native()
@@ -188,6 +189,7 @@ def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits):
     ring = (-(-window // page) + 1) * page if window else 0
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
     rows = [T - 1, 100, 64, 63, 48, 47, 33, 32, 31, 17, 16, 15, 1, 0]
+    tickets = torch.zeros(3 * nkv, dtype=torch.int32, device=DEV)
     for r in rows:
         keep = range(max(0, r + 1 - ring), r + 1) if ring else range(r + 1)
         kp, vp, table = _paged(k, v, page, ring, nkv, hd, dtype, keep)
@@ -197,8 +199,9 @@ def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits):
                               dtype=torch.uint8, device=DEV)
         qr = q[r].reshape(1, nh * hd).contiguous().to(DEV)
         n.attention_decode(qr, nh * hd, kp.to(DEV), vp.to(DEV), table.to(DEV), page, ring,
-                           i32([r]), i32([0]), i32([1]), out, scratch, nh, nkv, hd, scale, cap,
-                           window, splits)
+                           i32([r]), i32([0]), i32([1]), out, scratch, tickets, nh, nkv, hd, scale,
+                           cap, window, splits, warps)
+        assert int(tickets.abs().sum()) == 0, "the ticket counters are put back"
         _close(out.view(nh, hd), ref[r], dtype, f"decode row {r}")
     # several rows in one launch: rows of two sequences (slots 1 and 2 hold the same pages)
     if not ring:
@@ -210,8 +213,8 @@ def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits):
         scratch = torch.empty(max(1, n.attention_rows_scratch_bytes(3, nh, hd, splits)),
                               dtype=torch.uint8, device=DEV)
         n.attention_decode(qs, nh * hd, kp.to(DEV), vp.to(DEV), table.to(DEV), page, 0,
-                           i32(picks), i32([0, 1, 1]), i32([1, 2]), out, scratch, nh, nkv, hd,
-                           scale, cap, window, splits)
+                           i32(picks), i32([0, 1, 1]), i32([1, 2]), out, scratch, tickets, nh, nkv,
+                           hd, scale, cap, window, splits, warps)
         for i, r in enumerate(picks):
             _close(out[i].view(nh, hd), ref[r], dtype, f"decode rows together, row {r}")
 

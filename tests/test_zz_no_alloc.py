@@ -59,10 +59,14 @@ def _call(lib, symbol, c, rows, nh, nkv, hd, scale, cap, window, splits, scratch
     head = [p(c["q"]), c_int(nh * hd), p(c["k"]), p(c["v"]), p(c["table"]),
             c_int(c["pages_per_seq"]), c_int(c["page"]), c_int(0), p(c["row_pos"]),
             p(c["row_seq"]), p(c["seq_slot"]), p(out)]
-    if scratch is not None:
-        head.append(p(scratch))
+    if scratch is not None:      # the ordinary entry point: its caller brings both
+        tickets = torch.zeros(rows * nkv, dtype=torch.int32, device=DEV)
+        head += [p(scratch), p(tickets)]
     tail = [c_int(rows), c_int(nh), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
-            c_int(window), c_int(splits), stream]
+            c_int(window), c_int(splits)]
+    if scratch is not None:
+        tail.append(c_int(4))    # warps a block; the entry point under test always takes 4
+    tail.append(stream)
     rc = getattr(lib, symbol)(*head, *tail)
     torch.cuda.synchronize()
     return rc, out
@@ -81,7 +85,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         c = _case(seed, rows, nh, nkv, hd, lengths)
         need = lib.sib_attention_decode_no_alloc_floats(c_int(rows), c_int(nh), c_int(hd),
                                                         c_int(splits))
-        assert need == rows * nh * splits * (hd + 2)
+        assert need == rows * nh * splits * (hd + 2) + 64     # partial results and ticket counters
         scratch = torch.empty(need, dtype=torch.float32, device=DEV)
         rc, want = _call(lib, "sib_attention_decode", c, rows, nh, nkv, hd, scale, cap, window,
                          splits, scratch)
@@ -103,5 +107,5 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     rc, out = _call(lib, "sib_attention_decode_no_alloc", c, rows, nh, nkv, hd, 0.1, 0.0, 0, splits)
     assert rc != 0
     msg = lib.sib_last_error().decode()
-    assert "built-in array holds" in msg and str(rows * nh * splits * (hd + 2)) in msg
+    assert "built-in array holds" in msg and str(rows * nh * splits * (hd + 2) + rows * nh) in msg
     assert torch.isnan(out.float()).all()      # nothing was launched
