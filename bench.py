@@ -50,6 +50,29 @@ def baseline_config():
     }
 
 
+# Other shapes of the same architecture (BASELINE.json's configs[3] and [4]); the default
+# run and the recorded line are the 2B shape.
+SHAPES = {
+    "2b": {},
+    "9b": {"num_hidden_layers": 42, "hidden_size": 3584, "num_attention_heads": 16,
+           "num_key_value_heads": 8, "head_dim": 256, "intermediate_size": 14336,
+           "query_pre_attn_scalar": 256},
+    "27b": {"num_hidden_layers": 46, "hidden_size": 4608, "num_attention_heads": 32,
+            "num_key_value_heads": 16, "head_dim": 128, "intermediate_size": 36864,
+            "query_pre_attn_scalar": 144},
+}
+
+
+def kv_bytes_per_sequence(cfg, context):
+    """Bytes of cache one sequence of `context` tokens holds (bfloat16 keys and values)."""
+    per_token = cfg["num_key_value_heads"] * cfg["head_dim"] * 2 * 2
+    total = 0
+    for i in range(cfg["num_hidden_layers"]):
+        kept = min(context, cfg["sliding_window"] + 64) if i % 2 == 0 else context
+        total += kept * per_token
+    return total
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
@@ -198,12 +221,20 @@ def run_ours(args):
     from strata_inference_b200 import GenerationConfig, GenerationEngine
 
     cfg = baseline_config()
+    cfg.update(SHAPES[args.shape])
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     context, batch = args.context, args.batch
     peaks = measured_peaks()
-    biggest = max(batch, 64 if not args.no_points else batch)
+    point_batches = [] if args.no_points else [1, 64]
+    weights_estimate = 2 * (cfg["vocab_size"] * cfg["hidden_size"] + cfg["num_hidden_layers"] * (
+        cfg["hidden_size"] * (2 * cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"])
+        * cfg["head_dim"] + 3 * cfg["hidden_size"] * cfg["intermediate_size"]))
+    # a point whose cache would not fit beside the weights is left out
+    point_batches = [b for b in point_batches
+                     if weights_estimate + b * kv_bytes_per_sequence(cfg, context) < 150e9]
+    biggest = max([batch] + point_batches)
     gen = GenerationEngine.from_random(cfg, seed=5, dtype="bfloat16", ctx=context,
                                        max_tokens=biggest * context, max_slots=biggest)
     engine = gen.engine
@@ -217,8 +248,8 @@ def run_ours(args):
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
     points = {}
-    if not args.no_points:
-        for b in (1, 64):
+    if point_batches:
+        for b in point_batches:
             pms, _, _ = time_decode(engine, b, context, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
 
@@ -246,13 +277,13 @@ def run_ours(args):
     e2e_value = timed_tokens / (t_end - stamps[args.warmup - 1])
 
     line = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
+        "metric": METRIC.replace("2B", args.shape.upper()), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
         "impl": "ours",
         "config": {
-            "model": "Gemma2-2B shape", "global_batch": batch, "seq_len": context,
+            "model": "Gemma2-%s shape" % args.shape.upper(), "global_batch": batch, "seq_len": context,
             "parallelism": "none", "layers": cfg["num_hidden_layers"],
             "layers_of_named_config": full_layers, "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
@@ -286,6 +317,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the named configuration (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
+                    help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -1,5 +1,6 @@
 """The engine at the layer sizes of Gemma2-2B (hidden 2304, 8 heads of 256 in
-4 groups, intermediate 9216, vocabulary 256000), two layers deep, against the
+4 groups, intermediate 9216, vocabulary 256000) and of Gemma2-27B (hidden 4608,
+32 heads of 128 in 16 groups, intermediate 36864), two layers deep, against the
 plain implementation: whole prompt, last tokens one by one, unequal batch.
 The tiny configurations never reach the code paths that these sizes select
 (head size 256, the 16-byte vector paths, the cluster split of the products,
@@ -13,7 +14,7 @@ from helpers import REL_TOL, plain_weights, random_prompts
 
 pytestmark = pytest.mark.gpu
 
-CFG = {
+CFG_2B = {
     "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
     "num_hidden_layers": 2, "hidden_size": 2304, "num_attention_heads": 8,
     "num_key_value_heads": 4, "head_dim": 256, "intermediate_size": 9216, "vocab_size": 256000,
@@ -22,6 +23,12 @@ CFG = {
     "max_position_embeddings": 512, "hidden_activation": "gelu_pytorch_tanh",
     "tie_word_embeddings": True,
 }
+# the layer sizes of Gemma2-27B (32 heads of 128 in 16 groups) with a shorter vocabulary,
+# which keeps the plain implementation's 32-bit weights to a few GB
+CFG_27B = dict(CFG_2B, hidden_size=4608, num_attention_heads=32, num_key_value_heads=16,
+               head_dim=128, intermediate_size=36864, vocab_size=32000, query_pre_attn_scalar=144,
+               sliding_window=80)
+CONFIGS = {"2b": CFG_2B, "27b": CFG_27B}
 
 
 def _rel(got, ref):
@@ -29,20 +36,21 @@ def _rel(got, ref):
     return (got - ref).abs().max().item() / ref.abs().max().item()
 
 
-@pytest.fixture(scope="module")
-def model(tmp_path_factory):
+@pytest.fixture(scope="module", params=sorted(CONFIGS))
+def model(request, tmp_path_factory):
     """The model folder, the requests and the plain logits, shared by both types."""
     from strata_inference_b200.weights.random_init import write_random_model
-    d = str(tmp_path_factory.mktemp("gemma2_2b_sizes"))
-    write_random_model(d, CFG, seed=17, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1)
+    cfg = CONFIGS[request.param]
+    d = str(tmp_path_factory.mktemp("gemma2_%s_sizes" % request.param))
+    write_random_model(d, cfg, seed=17, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1)
     W = {k: v.float() for k, v in plain_weights(d).items()}
-    reqs = random_prompts(CFG, [200, 37, 150], seed=18)
-    refs = [plain.forward(t, W, CFG, dtype=torch.float32) for t in reqs]
+    reqs = random_prompts(cfg, [200, 37, 150], seed=18)
+    refs = [plain.forward(t, W, cfg, dtype=torch.float32) for t in reqs]
     return d, reqs, refs
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_two_layers_of_gemma2_2b_sizes(model, dtype):
+def test_two_layers_of_real_sizes(model, dtype):
     from strata_inference_b200 import Engine
     d, reqs, refs = model
     tol = REL_TOL[dtype]
