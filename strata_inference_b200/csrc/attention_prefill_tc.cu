@@ -1,27 +1,32 @@
 // Attention of whole prompts on the fifth-generation tensor cores (bfloat16):
-// both products of flash attention as tcgen05.mma with the score tile and the
-// output accumulator in tensor memory.  Same mathematics as attention_rows.cu
-// (scale, soft cap, causal and window mask, softmax in 32-bit, weighted sum of
-// v); attention_prefill.cu is the mma.sync kernel this one supersedes where its
-// shapes fit (1 or 2 query heads per kv head, head size 64, 128 or 256).
+// both products of flash attention as tcgen05.mma with the score tile, the
+// probabilities and the output accumulator in tensor memory.  Same mathematics as
+// attention_rows.cu (scale, soft cap, causal and window mask, softmax in 32-bit,
+// weighted sum of v); attention_prefill.cu is the mma.sync kernel this one
+// supersedes where its shapes fit (1 or 2 query heads per kv head, head size 64,
+// 128 or 256).
 //
 // A block takes 128 query rows of one (sequence, kv head): G heads x 128/G
-// consecutive positions.  Keys and values are walked in tiles of 64 positions.
+// consecutive positions.  Keys and values are walked in tiles of 128 positions.
+// Tensor memory (512 columns): two score tiles S0, S1 of 128 columns, then O.
 //
-//   warp 0      TMA: the query tile once, then key and value tiles into a ring of 2,
-//               straight from the step's packed q|k|v rows (boxes of 64 rows x 64
-//               columns, 128-byte swizzle)
-//   warp 1      one lane issues S = Q K^T (128 x 64, K-major operands) and, once the
-//               probabilities are in shared memory, O += P V (128 x head_dim; V is the
-//               MN-major operand: its rows are keys, as they lie in memory)
-//   warps 2-5   one thread per query row: read S from tensor memory, scale, cap,
-//               mask, exponentiate against a running maximum, write P (bfloat16) into
-//               shared memory in the swizzled K-major layout the MMA reads, and at the
-//               end read O, divide by the row sum and store
+//   warp 0      TMA: the query tile once, then key and value tiles (one of each in
+//               flight for head size 256, two for smaller heads), straight from the
+//               step's packed q|k|v rows (boxes of 64 rows x 64 columns, 128-byte swizzle)
+//   warp 1      one lane issues S(t+1) = Q K^T (128 x 128, operands K-major in shared
+//               memory) while the softmax warps work on S(t), and O += P(t) V (128 x
+//               head_dim; P read from tensor memory, V the MN-major operand: its rows
+//               are keys, as they lie in memory) once P(t) is there
+//   warps 2-9   two threads per query row, 64 of the tile's keys each: read S from
+//               tensor memory, scale, cap, mask, exponentiate against a running
+//               maximum the two agree on, and write P (bfloat16) over the first columns
+//               of the same score tile; at the end read O, divide by the row sum, store
 //
+// The tensor pipe runs what one thread issues in order, so S(t+2) is not written
+// before P(t) V has read P(t) from the same columns.
 // The running maximum is only raised (and O rescaled in tensor memory) when a
-// row's maximum has grown by more than 5.5: until then probabilities may exceed 1
-// by at most e^5.5, which bfloat16 and the 32-bit sums hold easily, and the
+// row's maximum has grown by more than 8 in units of log 2: until then probabilities
+// may exceed 1 by at most 2^8, which bfloat16 and the 32-bit sums hold easily, and the
 // division by the row sum at the end makes the result the same.
 // Every mbarrier wait is bounded; a wait that runs out sets an error flag.
 //
@@ -34,7 +39,7 @@
 namespace {
 
 constexpr int BM = 128;   // query rows per block
-constexpr int BN = 64;    // keys per tile
+constexpr int BN = 128;   // keys per tile
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -104,6 +109,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a, uint64_t 
         "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the A operand from tensor memory (128 lanes x 8 columns: 16 bfloat16 of k per lane)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
                      smem_u32(bar))
@@ -155,10 +170,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Whether key j of the tile is one the row sees.
+// Whether key j of the thread's 64 keys is one the row sees.
 __device__ __forceinline__ bool sees(int j, int j_lo, int j_hi) { return j >= j_lo && j <= j_hi; }
 
-// The largest of a row's 64 raw products (of those it sees, with MASK).
+// The largest of 64 raw products (of those the row sees, with MASK).
 template <bool MASK>
 __device__ __forceinline__ float row_max(const uint32_t (&raw)[64], int j_lo, int j_hi) {
     float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -171,33 +186,26 @@ __device__ __forceinline__ float row_max(const uint32_t (&raw)[64], int j_lo, in
     return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
 }
 
-// A row's 64 probabilities 2^(score - ref) as bfloat16 into its 128 bytes of the
-// swizzled tile; returns their sum.  CAP: score = c2 * tanh(product * c1), else
-// product * c1.
+// 64 probabilities 2^(score - ref) as 32 packed bfloat16 pairs (in place of the raw
+// products); returns their sum.  CAP: score = c2 * tanh(product * c1), else product * c1.
 template <bool CAP, bool MASK>
-__device__ __forceinline__ float probabilities(const uint32_t (&raw)[64], float c1, float c2,
-                                               float ref, int j_lo, int j_hi, unsigned char* prow,
-                                               int row) {
+__device__ __forceinline__ float probabilities(uint32_t (&raw)[64], float c1, float c2, float ref,
+                                               int j_lo, int j_hi) {
     float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        uint32_t w[4];
+    for (int k = 0; k < 32; ++k) {
+        float e[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            float e[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int j = 8 * c + 2 * k + h;
-                float x = __uint_as_float(raw[j]);
-                if (CAP) x = fmaf(c2, tanh_fast(x * c1), -ref);
-                else x = fmaf(x, c1, -ref);
-                if (MASK) x = sees(j, j_lo, j_hi) ? x : -INFINITY;
-                e[h] = exp2_fast(x);
-            }
-            sum[k] += e[0] + e[1];
-            w[k] = pack_bf16(e[0], e[1]);
+        for (int h = 0; h < 2; ++h) {
+            const int j = 2 * k + h;
+            float x = __uint_as_float(raw[j]);
+            if (CAP) x = fmaf(c2, tanh_fast(x * c1), -ref);
+            else x = fmaf(x, c1, -ref);
+            if (MASK) x = sees(j, j_lo, j_hi) ? x : -INFINITY;
+            e[h] = exp2_fast(x);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        sum[k & 3] += e[0] + e[1];
+        raw[k] = pack_bf16(e[0], e[1]);       // slot k <= 2k: not read again
     }
     return (sum[0] + sum[1]) + (sum[2] + sum[3]);
 }
@@ -214,28 +222,30 @@ struct TcArgs {
 
 // Barriers of one block.
 struct Bars {
-    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_free, p_full, pv_done, o_done;
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pair[4],
+        pv_done, o_done;
 };
 
 }  // namespace
 
 template <int HD, int G>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     constexpr int MP = BM / G;                 // positions per block
     constexpr int CH = HD / 64;                // 64-wide column chunks of a head
-    constexpr uint32_t Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2, P_BYTES = BM * BN * 2;
-    // S: columns [0, 64); O: columns [64, 64 + HD); a power of two of columns is allocated
-    constexpr uint32_t TMEM_COLS = HD == 256 ? 512 : HD == 128 ? 256 : 128;
-    constexpr uint32_t O_COL = 64;
+    constexpr int ST = HD == 256 ? 1 : 2;      // key tiles (and value tiles) in flight
+    constexpr uint32_t Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;
+    constexpr uint32_t CHUNK = BN * 128;       // one 64-column chunk of a key or value tile
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t O_COL = 256;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* Qs = base;                              // CH blocks of [128 rows x 128 B]
-    unsigned char* Ks = Qs + Q_BYTES;                      // 2 stages of CH blocks of [64 x 128 B]
-    unsigned char* Vs = Ks + 2 * KV_BYTES;                 // the same
-    unsigned char* Ps = Vs + 2 * KV_BYTES;                 // 2 buffers of [128 rows x 128 B]
-    Bars* bars = reinterpret_cast<Bars*>(Ps + 2 * P_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
+    unsigned char* Qs = base;                              // CH chunks of [128 rows x 128 B]
+    unsigned char* Ks = Qs + Q_BYTES;                      // ST stages of CH chunks of [128 x 128 B]
+    unsigned char* Vs = Ks + ST * KV_BYTES;                // the same
+    Bars* bars = reinterpret_cast<Bars*>(Vs + ST * KV_BYTES);
+    float* xch = reinterpret_cast<float*>(bars + 1);       // [2 tiles][2 halves][128 rows]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch + 2 * 2 * BM);
     int* failed = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -246,7 +256,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     const int row0 = p.seq_row0[b];
     const int k_hi = min(n, p0 + MP);
     const int k_lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
-    const int kt0 = k_lo >> 6, nt = ((k_hi + 63) >> 6) - kt0;
+    const int kt0 = k_lo / BN, nt = (k_hi + BN - 1) / BN - kt0;
     const int q_col = kvh * G * HD;                        // first column of the group's heads
     const int k_col = (p.n_heads + kvh) * HD;
     const int v_col = (p.n_heads + p.n_kv + kvh) * HD;
@@ -258,10 +268,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             mbar_init(&bars->k_empty[s], 1);
             mbar_init(&bars->v_full[s], 1);
             mbar_init(&bars->v_empty[s], 1);
+            mbar_init(&bars->s_full[s], 1);
+            mbar_init(&bars->p_full[s], 8);
         }
-        mbar_init(&bars->s_full, 1);
-        mbar_init(&bars->s_free, 4);
-        mbar_init(&bars->p_full, 4);
+        for (int q = 0; q < 4; ++q) mbar_init(&bars->pair[q], 2);
         mbar_init(&bars->pv_done, 1);
         mbar_init(&bars->o_done, 1);
         *failed = 0;
@@ -289,30 +299,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
                     tma_load_2d(Qs + c * (BM * 128) + half * (64 * 128), &map, &bars->q_full,
                                 q_col + head * HD + 64 * c, row0 + p0 + off);
                 }
-            // Keys run one tile ahead of values: a key tile is free again once its scores
-            // have been formed, a value tile only after the product that follows them.
-            auto load_k = [&](int t) -> bool {
-                const int s = t & 1;
-                if (t >= 2 && !mbar_wait(&bars->k_empty[s], ((t >> 1) - 1) & 1)) return false;
-                mbar_arrive_expect_tx(&bars->k_full[s], KV_BYTES);
+            // A key tile is free again once its scores have been formed, a value tile
+            // only after the product that follows them: keys run ahead of values.
+            auto load_tile = [&](unsigned char* tiles, uint64_t* full, uint64_t* empty, int col,
+                                 int t) -> bool {
+                const int s = t % ST;
+                if (t >= ST && !mbar_wait(&empty[s], ((t / ST) - 1) & 1)) return false;
+                mbar_arrive_expect_tx(&full[s], KV_BYTES);
                 for (int c = 0; c < CH; ++c)
-                    tma_load_2d(Ks + s * KV_BYTES + c * (BN * 128), &map, &bars->k_full[s],
-                                k_col + 64 * c, row0 + (kt0 + t) * 64);
+                    for (int half = 0; half < 2; ++half)
+                        tma_load_2d(tiles + s * KV_BYTES + c * CHUNK + half * (64 * 128), &map,
+                                    &full[s], col + 64 * c, row0 + (kt0 + t) * BN + 64 * half);
                 return true;
             };
-            auto load_v = [&](int t) -> bool {
-                const int s = t & 1;
-                if (t >= 2 && !mbar_wait(&bars->v_empty[s], ((t >> 1) - 1) & 1)) return false;
-                mbar_arrive_expect_tx(&bars->v_full[s], KV_BYTES);
-                for (int c = 0; c < CH; ++c)
-                    tma_load_2d(Vs + s * KV_BYTES + c * (BN * 128), &map, &bars->v_full[s],
-                                v_col + 64 * c, row0 + (kt0 + t) * 64);
-                return true;
-            };
-            bool fed = nt == 0 || load_k(0);
+            bool fed = nt == 0 || load_tile(Ks, bars->k_full, bars->k_empty, k_col, 0);
             for (int t = 0; t < nt && fed; ++t) {
-                if (t + 1 < nt) fed = load_k(t + 1);
-                fed = fed && load_v(t);
+                if (t + 1 < nt) fed = load_tile(Ks, bars->k_full, bars->k_empty, k_col, t + 1);
+                fed = fed && load_tile(Vs, bars->v_full, bars->v_empty, v_col, t);
             }
             if (!fed) *failed = 1;
         }
@@ -324,56 +327,57 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
                                           ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             bool ok = mbar_wait(&bars->q_full, 0);
             if (!ok) *failed = 2;
-            // S(t) = Q K(t)^T: HD / 16 steps of k
+            // S(t) = Q K(t)^T into score tile t & 1: HD / 16 steps of k
             auto issue_qk = [&](int t) {
-                const unsigned char* kt = Ks + (t & 1) * KV_BYTES;
+                const unsigned char* kt = Ks + (t % ST) * KV_BYTES;
 #pragma unroll
                 for (int j = 0; j < HD / 16; ++j) {
                     const uint64_t da = desc_k_major(Qs + (j >> 2) * (BM * 128)) + 2 * (j & 3);
-                    const uint64_t db = desc_k_major(kt + (j >> 2) * (BN * 128)) + 2 * (j & 3);
-                    umma_bf16(tmem, da, db, IDESC_QK, j > 0 ? 1u : 0u);
+                    const uint64_t db = desc_k_major(kt + (j >> 2) * CHUNK) + 2 * (j & 3);
+                    umma_bf16(tmem + 128 * (t & 1), da, db, IDESC_QK, j > 0 ? 1u : 0u);
                 }
-                umma_commit(&bars->k_empty[t & 1]);
-                umma_commit(&bars->s_full);
+                umma_commit(&bars->k_empty[t % ST]);
+                umma_commit(&bars->s_full[t & 1]);
             };
-            if (ok) {
-                if (!mbar_wait(&bars->k_full[0], 0)) { *failed = 3; ok = false; }
-            }
+            if (ok && !mbar_wait(&bars->k_full[0], 0)) { *failed = 3; ok = false; }
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 issue_qk(0);
             }
             for (int t = 0; t < nt && ok; ++t) {
                 if (t + 1 < nt) {
-                    // the next tile's scores as soon as this tile's have been read
-                    if (!mbar_wait(&bars->k_full[(t + 1) & 1], ((t + 1) >> 1) & 1) ||
-                        !mbar_wait(&bars->s_free, t & 1)) { *failed = 4; ok = false; break; }
+                    // the next tile's scores, formed while the softmax warps work on this tile's
+                    if (!mbar_wait(&bars->k_full[(t + 1) % ST], ((t + 1) / ST) & 1)) {
+                        *failed = 4; ok = false; break;
+                    }
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     issue_qk(t + 1);
                 }
-                if (!mbar_wait(&bars->p_full, t & 1) ||
-                    !mbar_wait(&bars->v_full[t & 1], (t >> 1) & 1)) { *failed = 5; ok = false; break; }
+                if (!mbar_wait(&bars->p_full[t & 1], (t >> 1) & 1) ||
+                    !mbar_wait(&bars->v_full[t % ST], (t / ST) & 1)) { *failed = 5; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                // O += P V(t): 4 steps of 16 keys; V rows are keys (MN-major operand)
-                const unsigned char* vt = Vs + (t & 1) * KV_BYTES;
+                // O += P(t) V(t): 8 steps of 16 keys; P from the score tile's first 64 columns
+                const unsigned char* vt = Vs + (t % ST) * KV_BYTES;
 #pragma unroll
                 for (int j = 0; j < BN / 16; ++j) {
-                    const uint64_t da = desc_k_major(Ps + (t & 1) * P_BYTES) + 2 * j;
-                    const uint64_t db = desc_mn_major(vt + j * (16 * 128), BN * 128);
-                    umma_bf16(tmem + O_COL, da, db, IDESC_PV, (t > 0 || j > 0) ? 1u : 0u);
+                    const uint64_t db = desc_mn_major(vt + j * (16 * 128), CHUNK);
+                    umma_bf16_ts(tmem + O_COL, tmem + 128 * (t & 1) + 8 * j, db, IDESC_PV,
+                                 (t > 0 || j > 0) ? 1u : 0u);
                 }
-                umma_commit(&bars->v_empty[t & 1]);
+                umma_commit(&bars->v_empty[t % ST]);
                 umma_commit(&bars->pv_done);
                 if (t == nt - 1) umma_commit(&bars->o_done);
             }
             if (!ok) {   // let nobody wait for what will not come
-                umma_commit(&bars->s_full);
+                umma_commit(&bars->s_full[0]);
+                umma_commit(&bars->s_full[1]);
                 umma_commit(&bars->pv_done);
                 umma_commit(&bars->o_done);
             }
         }
     } else {
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;                      // the tensor-memory lanes a warp may touch
+        const int half = (warp - 2) >> 2;                  // which 64 keys of a tile, which half of O
         const int row = 32 * quarter + lane;               // tensor-memory lane = query row
         const int head = kvh * G + row / MP;
         const int pos = p0 + row % MP;
@@ -386,28 +390,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
         const float c2 = p.softcap * LOG2E;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int t = 0; t < nt && ok; ++t) {
-            if (!mbar_wait(&bars->s_full, t & 1)) { if (lane == 0) *failed = 6; ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t raw[64];
-            tmem_ld32_issue(lane_addr, raw);
-            tmem_ld32_issue(lane_addr + 32, raw + 32);
-            tmem_ld_wait();
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        // the two threads of a row tell each other a number through shared memory
+        auto swap_with_partner = [&](int t, float mine, float& theirs) -> bool {
+            xch[((t & 1) * 2 + half) * BM + row] = mine;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->s_free);
-            // Which of the tile's keys the row sees: j in [j_lo, j_hi].  A warp whose rows
-            // all see the whole tile takes the path without the mask.
-            const int key0 = (kt0 + t) * 64;
+            if (lane == 0) mbar_arrive(&bars->pair[quarter]);
+            if (!mbar_wait(&bars->pair[quarter], t & 1)) return false;
+            theirs = xch[((t & 1) * 2 + (half ^ 1)) * BM + row];
+            return true;
+        };
+        for (int t = 0; t < nt && ok; ++t) {
+            if (!mbar_wait(&bars->s_full[t & 1], (t >> 1) & 1)) { if (lane == 0) *failed = 6; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t s_addr = lane_addr + 128 * (t & 1);
+            uint32_t raw[64];
+            tmem_ld32_issue(s_addr + 64 * half, raw);
+            tmem_ld32_issue(s_addr + 64 * half + 32, raw + 32);
+            tmem_ld_wait();
+            // Which of the thread's 64 keys the row sees: j in [j_lo, j_hi].  A warp whose
+            // rows all see all of them takes the path without the mask.
+            const int key0 = (kt0 + t) * BN + 64 * half;
             const int j_hi = min(pos, n - 1) - key0;
             const int j_lo = p.window > 0 ? pos - p.window + 1 - key0 : -(1 << 30);
             const bool whole = __all_sync(0xffffffffu, j_lo <= 0 && j_hi >= 63);
             // The row's maximum, taken on the raw products: scaling by a positive factor and
             // the cap are both increasing, so the largest product gives the largest score.
-            float mx_raw;
+            float mx_raw, other;
             if (whole) mx_raw = row_max<false>(raw, j_lo, j_hi);
             else mx_raw = row_max<true>(raw, j_lo, j_hi);
-            // scores are kept in units of log 2: probabilities are 2^(score - reference)
+            if (!swap_with_partner(t, mx_raw, other)) { if (lane == 0) *failed = 9; ok = false; break; }
+            mx_raw = fmaxf(mx_raw, other);
             float mx = mx_raw * c1;
             if (capped) mx = c2 * tanh_fast(mx);
             if (mx_raw == -INFINITY) mx = -INFINITY;
@@ -422,51 +434,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
                 m_ref = mx;
             }
             if (__any_sync(0xffffffffu, raise)) {
-                // O may be touched once the previous tile's P V has run
+                // O may be touched once the previous tile's P V has run; each thread of a
+                // row rescales its half of the columns
                 if (!mbar_wait(&bars->pv_done, (t - 1) & 1)) { if (lane == 0) *failed = 7; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 l *= factor;
 #pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < HD / 64; ++c) {
                     uint32_t o[32];
-                    tmem_ld32(lane_addr + O_COL + 32 * c, o);
+                    const uint32_t a = lane_addr + O_COL + (HD / 2) * half + 32 * c;
+                    tmem_ld32(a, o);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * factor);
-                    tmem_st32(lane_addr + O_COL + 32 * c, o);
+                    tmem_st32(a, o);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
             const float ref = m_ref == -INFINITY ? 0.f : m_ref;
-            // probabilities into the K-major, 128-byte-swizzled tile the MMA reads
-            // (this buffer's last reader, the product two tiles back, was issued before the
-            // scores of this tile, so it has run)
-            unsigned char* prow = Ps + (t & 1) * P_BYTES + row * 128;
             if (capped) {
-                if (whole) l += probabilities<true, false>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
-                else l += probabilities<true, true>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
+                if (whole) l += probabilities<true, false>(raw, c1, c2, ref, j_lo, j_hi);
+                else l += probabilities<true, true>(raw, c1, c2, ref, j_lo, j_hi);
             } else {
-                if (whole) l += probabilities<false, false>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
-                else l += probabilities<false, true>(raw, c1, c2, ref, j_lo, j_hi, prow, row);
+                if (whole) l += probabilities<false, false>(raw, c1, c2, ref, j_lo, j_hi);
+                else l += probabilities<false, true>(raw, c1, c2, ref, j_lo, j_hi);
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            // P over the first 64 columns of the score tile (both threads have read theirs)
+            tmem_st32(s_addr + 32 * half, reinterpret_cast<uint32_t(&)[32]>(raw));
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->p_full);
+            if (lane == 0) mbar_arrive(&bars->p_full[t & 1]);
         }
+        float l_other = 0.f;
         if (ok && nt > 0) {
             // (pv_done is not waited for tile by tile, so its phase cannot tell the last
             // product from the one before it)
             if (!mbar_wait(&bars->o_done, 0)) { if (lane == 0) *failed = 8; ok = false; }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (ok && !swap_with_partner(nt, l, l_other)) { if (lane == 0) *failed = 9; ok = false; }
         }
         if (ok) {
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / (l + l_other);
             const bool store = pos < n;
-            __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD;
+            __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD +
+                                 (HD / 2) * half;
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < HD / 64; ++c) {
                 uint32_t o[32];
-                tmem_ld32(lane_addr + O_COL + 32 * c, o);
+                tmem_ld32(lane_addr + O_COL + (HD / 2) * half + 32 * c, o);
                 if (store) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -532,8 +546,9 @@ SIB_EXPORT int sib_attention_prefill_tc_supports(int n_heads, int n_kv, int head
 template <int HD, int G>
 static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int max_len,
                      cudaStream_t s) {
-    const size_t smem = 1024 + (size_t)BM * HD * 2 + 4 * (size_t)BN * HD * 2 + 2 * BM * BN * 2 +
-                        sizeof(Bars) + 16;
+    constexpr int ST = HD == 256 ? 1 : 2;
+    const size_t smem = 1024 + (size_t)BM * HD * 2 + 2 * ST * (size_t)BN * HD * 2 + sizeof(Bars) +
+                        2 * 2 * BM * sizeof(float) + 16;
     auto kernel = attention_prefill_tc_kernel<HD, G>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
@@ -542,7 +557,7 @@ static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int ma
     }
     constexpr int MP = BM / G;
     dim3 grid((max_len + MP - 1) / MP, n_seqs, p.n_kv);
-    kernel<<<grid, 192, smem, s>>>(map, p);
+    kernel<<<grid, 320, smem, s>>>(map, p);
     return sib_check_launch("attention_prefill_tc");
 }
 
