@@ -251,18 +251,21 @@ def test_attention_prefill_kernel(nh, nkv, hd, window, cap):
         _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"prefill, sequence of {T}")
 
 
-@pytest.mark.parametrize("nh,nkv,hd,window,cap", [
-    (4, 2, 64, 0, 0.0), (8, 4, 256, 100, 50.0), (2, 2, 128, 70, 0.0), (8, 4, 256, 0, 0.0),
-    (3, 3, 64, 17, 20.0), (4, 2, 128, 0, 30.0)])
-def test_attention_prefill_tc_kernel(nh, nkv, hd, window, cap):
-    """The tcgen05 prompt kernel on packed prompts of unequal lengths."""
+@pytest.mark.parametrize("nh,nkv,hd,window,cap,boost", [
+    (4, 2, 64, 0, 0.0, 1.0), (8, 4, 256, 100, 50.0, 1.0), (2, 2, 128, 70, 0.0, 1.0),
+    (8, 4, 256, 0, 0.0, 1.0), (3, 3, 64, 17, 20.0, 1.0), (4, 2, 128, 0, 30.0, 1.0),
+    (8, 4, 256, 0, 50.0, 6.0), (4, 2, 128, 150, 10.0, 3.0)])
+def test_attention_prefill_tc_kernel(nh, nkv, hd, window, cap, boost):
+    """The tcgen05 prompt kernel on packed prompts of unequal lengths.  `boost` makes the
+    scores large against the cap, where the kernel takes the tanh from the
+    special-function unit instead of the short series it uses for small arguments."""
     n = _native()
     assert n.attention_prefill_tc_supports(nh, nkv, hd, (nh + 2 * nkv) * hd)
     assert not n.attention_prefill_tc_supports(8, 2, hd, 12 * hd)
     g = torch.Generator().manual_seed(15)
     lens = [200, 5, 64, 131, 300]
     dtype = torch.bfloat16
-    scale = 3.0 / math.sqrt(hd)
+    scale = 3.0 * boost / math.sqrt(hd)
     qs, refs = [], []
     for T in lens:
         q = torch.randn(T, nh, hd, generator=g).to(dtype)
