@@ -241,6 +241,283 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------
+// The same product for many activation rows, on pairs of SMs.
+//
+// A cluster of two blocks owns a tile of 256 activation rows x 256 weight rows and
+// walks the tiles pair_index, pair_index + pairs, ... (persistent).  The activation
+// rows are the M side here: each block of the pair holds its 128 rows of x and HALF
+// of the 256 weight rows per k-block in shared memory, and one thread of the first
+// block issues tcgen05.mma.cta_group::2 (M = 256, N = 256), which reads both blocks'
+// halves: every byte of x and W crosses from L2 once per pair, not once per SM.
+// Tensor memory holds two accumulators of 256 columns, so the epilogue warps drain
+// tile i (lane = activation row, 32 consecutive outputs per tcgen05.ld: 64-byte
+// stores) while the MMAs of tile i + 1 run.
+//
+//   warp 0      TMA loads of this block's operand halves into a ring of PAIR_STAGES;
+//               the transaction bytes of both blocks are counted on the first
+//               block's barrier (cp.async.bulk.tensor ... .cta_group::2)
+//   warp 1      allocates tensor memory (both blocks); in the first block one lane
+//               issues the MMAs; commits are multicast to both blocks' barriers
+//   warps 2-5   epilogue; the second block's warps report a drained accumulator to
+//               the first block's barrier
+// Every mbarrier wait is bounded; both blocks meet at a cluster barrier before they
+// free their tensor memory and leave.
+// ---------------------------------------------------------------------------
+static constexpr int PAIR_BN = 256;        // weight rows per tile (128 per block in shared memory)
+static constexpr int PAIR_STAGES = 6;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// the shared::cluster address of `p`'s counterpart in the pair's first block
+__device__ __forceinline__ uint32_t in_first_block(const void* p) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;\n" : "=r"(a) : "r"(smem_u32(p)));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the load lands in this block's shared memory; its bytes are counted on the barrier at
+// the same offset in the pair's first block
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                                 int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(in_first_block(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives, once the MMAs issued so far have run, on the barrier at this offset in both blocks
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;\n" ::"r"(smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+// arrive on the barrier at this offset in the pair's first block
+__device__ __forceinline__ void mbar_arrive_first_block(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(
+                     in_first_block(bar))
+                 : "memory");
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_run(OutT* dst, const float (&o)[32], int count);
+// `count` of 32 consecutive outputs (count < 32 at the edge of the matrix)
+template <>
+__device__ __forceinline__ void store_run<__nv_bfloat16>(__nv_bfloat16* dst, const float (&o)[32],
+                                                         int count) {
+    if (count == 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __nv_bfloat162 v = __floats2bfloat162_rn(o[8 * q + 2 * k], o[8 * q + 2 * k + 1]);
+                w[k] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < count) dst[j] = __float2bfloat16(o[j]);
+    }
+}
+template <>
+__device__ __forceinline__ void store_run<float>(float* dst, const float (&o)[32], int count) {
+    if (count == 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < count) dst[j] = o[j];
+    }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         GemmArgs p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr uint32_t A_BYTES = 128 * BK * 2, B_BYTES = (PAIR_BN / 2) * BK * 2;
+    constexpr uint32_t STAGE = A_BYTES + B_BYTES;
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + PAIR_STAGES * STAGE);   // used in the first block
+    uint64_t* empty = full + PAIR_STAGES;
+    uint64_t* acc_full = empty + PAIR_STAGES;        // [2]
+    uint64_t* acc_empty = acc_full + 2;              // [2], used in the first block
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    int* failed = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int tiles_m = (p.R + 255) / 256, tiles_n = (p.N + PAIR_BN - 1) / PAIR_BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);             // 4 epilogue warps of each block
+        }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();          // both blocks' barriers exist before anything arrives on them
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;     // k-blocks loaded so far
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
+                const int m0 = (tile % tiles_m) * 256 + 128 * (int)rank;
+                const int n0 = (tile / tiles_m) * PAIR_BN + (PAIR_BN / 2) * (int)rank;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    const uint32_t round = it / PAIR_STAGES;
+                    if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) { *failed = 1; ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * STAGE);
+                    unsigned char* a = tiles + s * STAGE;
+                    tma_load_2d_pair(a, &map_x, &full[s], kb * BK, m0);
+                    tma_load_2d_pair(a + A_BYTES, &map_w, &full[s], kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // f32 accumulate, bf16 x bf16, both operands K-major, N = 256, M = 256 over the pair
+            constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(PAIR_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            uint32_t it = 0, done = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += pairs, ++done) {
+                const uint32_t b = done & 1;
+                // the epilogue of the tile two back has drained this accumulator
+                if (done >= 2 && !mbar_wait(&acc_empty[b], ((done >> 1) - 1) & 1)) { *failed = 4; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    if (!mbar_wait(&full[s], (it / PAIR_STAGES) & 1)) { *failed = 2; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    unsigned char* a = tiles + s * STAGE;
+                    const uint64_t da = umma_desc(a), db = umma_desc(a + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(tmem + 256 * b, da + 2 * k, db + 2 * k, IDESC,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[b]);
+            }
+            if (!ok) {     // let nobody wait for what will not come
+                umma_commit_pair(&acc_full[0]);
+                umma_commit_pair(&acc_full[1]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        OutT* y = (OutT*)p.y;
+        uint32_t done = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += pairs, ++done) {
+            const uint32_t b = done & 1;
+            if (!mbar_wait(&acc_full[b], (done >> 1) & 1)) { if (lane == 0) *failed = 3; ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int r = (tile % tiles_m) * 256 + 128 * (int)rank + 32 * quarter + lane;   // activation row
+            const int n0 = (tile / tiles_m) * PAIR_BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PAIR_BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + 256 * b + (uint32_t)c0, v);
+                const int n = n0 + c0;
+                if (r >= p.R || n >= p.N) continue;
+                float o[32];
+                if (p.epilogue == GEMM_EPI_GEGLU) {
+                    // weight rows come as 8 gates then their 8 ups: 32 columns make 16 outputs
+#pragma unroll
+                    for (int g = 0; g < 2; ++g)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            o[8 * g + i] = gemm_gelu_tanh(__uint_as_float(v[16 * g + i])) *
+                                           __uint_as_float(v[16 * g + 8 + i]);
+                    OutT* dst = y + (size_t)r * p.y_stride + n / 2;
+                    const int count = min(32, p.N - n) / 2;
+                    if (count == 16 && ((uintptr_t)dst & 15) == 0 && sizeof(OutT) == 2) {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const __nv_bfloat162 t2 = __floats2bfloat162_rn(o[8 * q + 2 * k], o[8 * q + 2 * k + 1]);
+                                w[k] = *reinterpret_cast<const uint32_t*>(&t2);
+                            }
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + 8 * q) =
+                                make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < count) dst[j] = from_f32<OutT>(o[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        o[j] = __uint_as_float(v[j]);
+                        if (p.epilogue == GEMM_EPI_SOFTCAP) o[j] = p.cap * tanhf(o[j] / p.cap);
+                    }
+                    store_run<OutT>(y + (size_t)r * p.y_stride + n, o, min(32, p.N - n));
+                }
+            }
+            // this warp has read its part of the accumulator
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_first_block(&acc_empty[b]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();          // the other block no longer touches this block's memory or barriers
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512)
+                     : "memory");
+    }
+    if (threadIdx.x == 0 && *failed) atomicExch(p.error_flag, *failed);
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -298,7 +575,41 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
     return sib_check_launch("gemm_tcgen05");
 }
 
+template <typename OutT>
+static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmArgs& p, int sm_count,
+                       cudaStream_t s) {
+    const size_t smem = 1024 + (size_t)PAIR_STAGES * (128 * BK * 2 + (PAIR_BN / 2) * BK * 2) +
+                        (2 * PAIR_STAGES + 4) * 8 + 16;
+    auto kernel = gemm_tcgen05_pair_kernel<OutT>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+        sib_set_error("gemm_tcgen05: shared memory: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    const int n_tiles = ((p.R + 255) / 256) * ((p.N + PAIR_BN - 1) / PAIR_BN);
+    const int pairs = n_tiles < sm_count / 2 ? n_tiles : sm_count / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, mx, mw, p);
+    if (e != cudaSuccess) {
+        sib_set_error("gemm_tcgen05: launch of the paired kernel failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return sib_check_launch("gemm_tcgen05");
+}
+
 static int* g_error_flag[64] = {};
+static int g_sm_count[64] = {};
 
 // 0, or the code a block left when one of its waits ran out (1: a stage never
 // became free, 2: a load never arrived, 3: the accumulator never became ready).
@@ -316,9 +627,10 @@ SIB_EXPORT int sib_gemm_tcgen05_supports(int R, int N, int K, long long x_stride
     return R > 0 && N > 0 && K > 0 && K % 8 == 0 && x_stride % 8 == 0;
 }
 
-SIB_EXPORT int sib_gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, int R, int N,
-                                int K, long long x_stride, int y_stride, int epilogue, float cap,
-                                void* stream) {
+// variant 0: the kernel that suits the number of rows; 1: always the one-block kernel.
+static int gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, int R, int N, int K,
+                        long long x_stride, int y_stride, int epilogue, float cap, int variant,
+                        void* stream) {
     if (R == 0) return 0;
     SIB_REQUIRE(sib_gemm_tcgen05_supports(R, N, K, x_stride),
                 "gemm_tcgen05: R=%d N=%d K=%d x_stride=%lld; K and the row stride must be multiples "
@@ -337,8 +649,23 @@ SIB_EXPORT int sib_gemm_tcgen05(const void* W, const void* x, void* y, int out_d
         SIB_REQUIRE(e == cudaSuccess, "gemm_tcgen05: %s", cudaGetErrorString(e));
         cudaMemset(g_error_flag[dev], 0, sizeof(int));
     }
-    const int bn = R <= 32 ? 32 : R <= 64 ? 64 : R <= 128 ? 128 : 256;
+    if (!g_sm_count[dev]) {
+        e = cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+        SIB_REQUIRE(e == cudaSuccess && g_sm_count[dev] >= 2, "gemm_tcgen05: %s", cudaGetErrorString(e));
+    }
     CUtensorMap mw, mx;
+    if (R > 128 && variant != 1) {
+        // many rows: tiles of 256 x 256 on pairs of SMs
+        if (make_map(&mx, x, R, K, x_stride, 128)) return -1;
+        if (make_map(&mw, W, N, K, K, PAIR_BN / 2)) return -1;
+        GemmArgs pp{y, g_error_flag[dev], R, N, K, y_stride, epilogue, cap};
+        if (out_dtype == SIB_BF16)
+            return launch_pair<__nv_bfloat16>(mx, mw, pp, g_sm_count[dev], (cudaStream_t)stream);
+        if (out_dtype == SIB_F32)
+            return launch_pair<float>(mx, mw, pp, g_sm_count[dev], (cudaStream_t)stream);
+        SIB_REQUIRE(false, "gemm_tcgen05: unknown output type %d", out_dtype);
+    }
+    const int bn = R <= 32 ? 32 : R <= 64 ? 64 : R <= 128 ? 128 : 256;
     if (make_map(&mw, W, N, K, K, BM)) return -1;
     if (make_map(&mx, x, R, K, x_stride, bn)) return -1;
     GemmArgs p{y, g_error_flag[dev], R, N, K, y_stride, epilogue, cap};
@@ -354,4 +681,17 @@ SIB_EXPORT int sib_gemm_tcgen05(const void* W, const void* x, void* y, int out_d
     if (bn == 256) GO(256, 4);
 #undef GO
     SIB_REQUIRE(false, "gemm_tcgen05: unknown output type %d", out_dtype);
+}
+
+SIB_EXPORT int sib_gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, int R, int N,
+                                int K, long long x_stride, int y_stride, int epilogue, float cap,
+                                void* stream) {
+    return gemm_tcgen05(W, x, y, out_dtype, R, N, K, x_stride, y_stride, epilogue, cap, 0, stream);
+}
+
+// The one-block kernel whatever the number of rows (for comparison and tests).
+SIB_EXPORT int sib_gemm_tcgen05_one_block(const void* W, const void* x, void* y, int out_dtype, int R,
+                                          int N, int K, long long x_stride, int y_stride,
+                                          int epilogue, float cap, void* stream) {
+    return gemm_tcgen05(W, x, y, out_dtype, R, N, K, x_stride, y_stride, epilogue, cap, 1, stream);
 }

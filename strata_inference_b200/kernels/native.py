@@ -353,8 +353,9 @@ def gemm_tcgen05_supports(R: int, N: int, K: int, x_stride: int) -> bool:
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
-                 cap: float = 0.0) -> torch.Tensor:
-    """out = x . w^T for bfloat16 x and w on tcgen05 (see csrc/gemm_tcgen05.cu)."""
+                 cap: float = 0.0, one_block: bool = False) -> torch.Tensor:
+    """out = x . w^T for bfloat16 x and w on tcgen05 (see csrc/gemm_tcgen05.cu).  More than
+    128 rows go to the kernel that works on pairs of SMs unless ``one_block`` is set."""
     _want(x, torch.bfloat16, "x", contiguous=False)
     _want(w, torch.bfloat16, "w")
     _want(out, out.dtype, "out", contiguous=False)
@@ -363,10 +364,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
     n_out = N // 2 if epilogue == EPI_GEGLU else N
     if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("gemm_tcgen05: shapes do not fit")
-    _check(library().sib_gemm_tcgen05(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
-                                      c_int(N), c_int(K), c_longlong(x.stride(0)),
-                                      c_int(out.stride(0)), c_int(epilogue), c_float(cap),
-                                      _stream()))
+    entry = library().sib_gemm_tcgen05_one_block if one_block else library().sib_gemm_tcgen05
+    _check(entry(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R), c_int(N), c_int(K),
+                 c_longlong(x.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_float(cap),
+                 _stream()))
     return out
 
 

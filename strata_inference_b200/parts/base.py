@@ -63,6 +63,9 @@ class Runtime:
         # takes up to native.SKINNY_MAX_ROWS); measured on a B200 at Gemma2-2B sizes it
         # is ahead of the library product up to 16 rows and behind it from 32 on.
         self.skinny_max_rows = 16
+        # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
+        # 256 x 256 tiles) beats the library product followed by the activation kernel
+        self.gated_gemm_min_rows = 128
         self._scratch: Optional[torch.Tensor] = None
         self._tickets: Optional[torch.Tensor] = None
         self._retired: list = []       # outgrown buffers that captured graphs may still name
@@ -103,10 +106,11 @@ class Runtime:
             return native.skinny_linear(x, w, out, epilogue, cap)
         aligned = (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                    and x.data_ptr() % 16 == 0)
-        if (x.dtype == torch.bfloat16 and out_dtype == torch.float32 and aligned):
-            # many rows of 32-bit outputs (logits of whole prompts): the tcgen05 product
-            # writes them once, soft-capped in its epilogue, where the library product
-            # would write them and a second kernel read and write them again
+        fused_gate = epilogue == native.EPI_GEGLU and R > self.gated_gemm_min_rows
+        if x.dtype == torch.bfloat16 and aligned and (out_dtype == torch.float32 or fused_gate):
+            # the tcgen05 product where its epilogue saves a pass over the outputs: 32-bit
+            # logits of many rows, soft-capped as they are written; the gated activation of
+            # the feed-forward, which halves what is written and spares a second kernel
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             return native.gemm_tcgen05(x, w, out, epilogue, cap)
         if epilogue == native.EPI_GEGLU:

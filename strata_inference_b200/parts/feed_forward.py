@@ -56,8 +56,8 @@ class GatedMLP:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         rt = self.rt
         R = x.shape[0]
-        if (self.group == _GROUP and x.dtype == torch.bfloat16 and R <= rt.skinny_max_rows
-                and x.shape[1] % 8 == 0):
+        if (self.group == _GROUP and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                and (R <= rt.skinny_max_rows or R > rt.gated_gemm_min_rows)):
             t = rt.linear(x, self.w_gate_up, epilogue=native.EPI_GEGLU)
         else:
             gate_up = rt.linear(x, self.w_gate_up)

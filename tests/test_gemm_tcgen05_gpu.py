@@ -25,7 +25,9 @@ def _rel(got, ref):
 
 
 SHAPES = [(1, 128, 64), (8, 16, 8), (33, 200, 72), (64, 2304, 2048), (100, 300, 96),
-          (129, 1000, 200), (300, 520, 1000), (1024, 384, 2304)]
+          (129, 1000, 200), (300, 520, 1000), (1024, 384, 2304),
+          # more tiles than pairs of SMs: every pair walks several, through both accumulators
+          (2048, 9216, 512), (513, 5000, 136)]
 
 
 @pytest.mark.parametrize("R,N,K", SHAPES)
@@ -45,7 +47,7 @@ def test_gemm_tcgen05_plain_product(R, N, K):
     assert _rel(out16, ref) <= 1e-2
 
 
-@pytest.mark.parametrize("R,N,K", [(5, 64, 64), (70, 320, 96), (300, 2048, 256)])
+@pytest.mark.parametrize("R,N,K", [(5, 64, 64), (70, 320, 96), (300, 2048, 256), (700, 9232, 128)])
 def test_gemm_tcgen05_epilogues(R, N, K):
     n = _native()
     g = torch.Generator().manual_seed(N + K)
