@@ -34,6 +34,8 @@
 // Reference: src/backend/cuda/kernels.rs:3183-3430 (batched_causal_attention).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -118,6 +120,62 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
         "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// ---- the same on a pair of blocks (a cluster of two, tcgen05 cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// the shared::cluster address of `p`'s counterpart in the pair's first block
+__device__ __forceinline__ uint32_t in_first_block(const void* p) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;\n" : "=r"(a) : "r"(smem_u32(p)));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the load lands in this block's shared memory; its bytes are counted on the barrier at
+// the same offset in the pair's first block
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                                 int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];\n" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(in_first_block(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b,
+                                                  uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives, once the MMAs issued so far have run, on the barrier at this offset in both blocks
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;\n" ::"r"(smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_first_block(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(in_first_block(bar))
+                 : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
@@ -228,14 +286,24 @@ struct Bars {
 
 }  // namespace
 
-template <int HD, int G>
+// PAIR: two blocks (a cluster) take 256 query rows, two neighbouring runs of positions,
+// and share every key and value tile: each loads 64 of the tile's 128 keys and half of
+// the value columns, and one thread of the first block issues the MMAs for both
+// (cta_group::2, M = 256), so a tile crosses from L2 once per pair and the halved tiles
+// leave room for two of each in flight at head size 256.
+template <int HD, int G, bool PAIR>
 __global__ void __launch_bounds__(320)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
+    static_assert(!PAIR || HD >= 128, "half of the value columns must fill a 128-byte row");
     constexpr int MP = BM / G;                 // positions per block
     constexpr int CH = HD / 64;                // 64-wide column chunks of a head
-    constexpr int ST = HD == 256 ? 1 : 2;      // key tiles (and value tiles) in flight
-    constexpr uint32_t Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;
-    constexpr uint32_t CHUNK = BN * 128;       // one 64-column chunk of a key or value tile
+    constexpr int ST = (HD == 256 && !PAIR) ? 1 : 2;   // key tiles (and value tiles) in flight
+    constexpr int NB = PAIR ? 2 : 1;           // blocks that share the tiles
+    constexpr int K_ROWS = BN / NB;            // keys of a tile in this block's shared memory
+    constexpr int V_CH = CH / NB;              // 64-column chunks of the values here
+    constexpr uint32_t Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2 / NB;
+    constexpr uint32_t K_CHUNK = K_ROWS * 128; // one 64-column chunk of this block's keys
+    constexpr uint32_t V_CHUNK = BN * 128;     // one 64-column chunk of a value tile
     constexpr uint32_t TMEM_COLS = 512;
     constexpr uint32_t O_COL = 256;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -251,11 +319,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.y, kvh = blockIdx.z;
     const int n = p.seq_len[b];
-    const int p0 = (int)(gridDim.x - 1 - blockIdx.x) * MP;   // the longest tiles first
-    if (p0 >= n) return;
+    const int rank = PAIR ? (int)cluster_ctarank() : 0;
+    // the longest tiles first; first0: the first position of the block or of the pair
+    const int first0 = (int)(gridDim.x / NB - 1 - blockIdx.x / NB) * (NB * MP);
+    const int p0 = first0 + rank * MP;
+    if (first0 >= n) return;                               // (both blocks of a pair)
     const int row0 = p.seq_row0[b];
-    const int k_hi = min(n, p0 + MP);
-    const int k_lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
+    const int k_hi = min(n, first0 + NB * MP);
+    const int k_lo = p.window > 0 ? max(0, first0 - p.window + 1) : 0;
     const int kt0 = k_lo / BN, nt = (k_hi + BN - 1) / BN - kt0;
     const int q_col = kvh * G * HD;                        // first column of the group's heads
     const int k_col = (p.n_heads + kvh) * HD;
@@ -269,7 +340,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             mbar_init(&bars->v_full[s], 1);
             mbar_init(&bars->v_empty[s], 1);
             mbar_init(&bars->s_full[s], 1);
-            mbar_init(&bars->p_full[s], 8);
+            mbar_init(&bars->p_full[s], 8 * NB);       // the softmax warps of every block
         }
         for (int q = 0; q < 4; ++q) mbar_init(&bars->pair[q], 2);
         mbar_init(&bars->pv_done, 1);
@@ -278,53 +349,87 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
-                         smem_u32(tmem_slot)),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                             smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                             smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();     // both blocks' barriers exist before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    // a load whose bytes are counted on the (first block's) barrier; an arrival that
+    // announces the bytes of all blocks, by the first block only
+    auto load = [&](void* dst, uint64_t* bar, int c0, int c1) {
+        if (PAIR) tma_load_2d_pair(dst, &map, bar, c0, c1);
+        else tma_load_2d(dst, &map, bar, c0, c1);
+    };
+    auto expect = [&](uint64_t* bar, uint32_t bytes) {
+        if (rank == 0) mbar_arrive_expect_tx(bar, NB * bytes);
+    };
 
     if (warp == 0) {
         if (lane == 0) {
             // the query tile: per 64-column chunk two boxes of 64 rows
-            mbar_arrive_expect_tx(&bars->q_full, Q_BYTES);
+            expect(&bars->q_full, Q_BYTES);
             for (int c = 0; c < CH; ++c)
                 for (int half = 0; half < 2; ++half) {
                     const int head = (half * 64) / MP, off = (half * 64) % MP;
-                    tma_load_2d(Qs + c * (BM * 128) + half * (64 * 128), &map, &bars->q_full,
-                                q_col + head * HD + 64 * c, row0 + p0 + off);
+                    load(Qs + c * (BM * 128) + half * (64 * 128), &bars->q_full,
+                         q_col + head * HD + 64 * c, row0 + p0 + off);
                 }
             // A key tile is free again once its scores have been formed, a value tile
             // only after the product that follows them: keys run ahead of values.
-            auto load_tile = [&](unsigned char* tiles, uint64_t* full, uint64_t* empty, int col,
-                                 int t) -> bool {
+            // (of a pair, this block brings keys [64 rank, 64 rank + 64) of a tile, all columns,
+            // and all 128 keys' value columns [HD / 2 * rank, HD / 2 * rank + HD / 2))
+            auto load_k = [&](int t) -> bool {
                 const int s = t % ST;
-                if (t >= ST && !mbar_wait(&empty[s], ((t / ST) - 1) & 1)) return false;
-                mbar_arrive_expect_tx(&full[s], KV_BYTES);
+                if (t >= ST && !mbar_wait(&bars->k_empty[s], ((t / ST) - 1) & 1)) return false;
+                expect(&bars->k_full[s], KV_BYTES);
                 for (int c = 0; c < CH; ++c)
-                    for (int half = 0; half < 2; ++half)
-                        tma_load_2d(tiles + s * KV_BYTES + c * CHUNK + half * (64 * 128), &map,
-                                    &full[s], col + 64 * c, row0 + (kt0 + t) * BN + 64 * half);
+                    for (int r64 = 0; r64 < K_ROWS / 64; ++r64)
+                        load(Ks + s * KV_BYTES + c * K_CHUNK + r64 * (64 * 128), &bars->k_full[s],
+                             k_col + 64 * c, row0 + (kt0 + t) * BN + K_ROWS * rank + 64 * r64);
                 return true;
             };
-            bool fed = nt == 0 || load_tile(Ks, bars->k_full, bars->k_empty, k_col, 0);
+            auto load_v = [&](int t) -> bool {
+                const int s = t % ST;
+                if (t >= ST && !mbar_wait(&bars->v_empty[s], ((t / ST) - 1) & 1)) return false;
+                expect(&bars->v_full[s], KV_BYTES);
+                for (int c = 0; c < V_CH; ++c)
+                    for (int r64 = 0; r64 < BN / 64; ++r64)
+                        load(Vs + s * KV_BYTES + c * V_CHUNK + r64 * (64 * 128), &bars->v_full[s],
+                             v_col + (HD / NB) * rank + 64 * c, row0 + (kt0 + t) * BN + 64 * r64);
+                return true;
+            };
+            bool fed = nt == 0 || load_k(0);
             for (int t = 0; t < nt && fed; ++t) {
-                if (t + 1 < nt) fed = load_tile(Ks, bars->k_full, bars->k_empty, k_col, t + 1);
-                fed = fed && load_tile(Vs, bars->v_full, bars->v_empty, v_col, t);
+                if (t + 1 < nt) fed = load_k(t + 1);
+                fed = fed && load_v(t);
             }
             if (!fed) *failed = 1;
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
+            // M is 128 rows of one block or 256 rows over the pair
             constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) |
-                                          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                                          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(NB * BM >> 4) << 24);
             constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
-                                          ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                                          ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(NB * BM >> 4) << 24);
+            auto commit = [&](uint64_t* bar) {
+                if (PAIR) umma_commit_pair(bar);
+                else umma_commit(bar);
+            };
             bool ok = mbar_wait(&bars->q_full, 0);
             if (!ok) *failed = 2;
             // S(t) = Q K(t)^T into score tile t & 1: HD / 16 steps of k
@@ -333,11 +438,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
 #pragma unroll
                 for (int j = 0; j < HD / 16; ++j) {
                     const uint64_t da = desc_k_major(Qs + (j >> 2) * (BM * 128)) + 2 * (j & 3);
-                    const uint64_t db = desc_k_major(kt + (j >> 2) * CHUNK) + 2 * (j & 3);
-                    umma_bf16(tmem + 128 * (t & 1), da, db, IDESC_QK, j > 0 ? 1u : 0u);
+                    const uint64_t db = desc_k_major(kt + (j >> 2) * K_CHUNK) + 2 * (j & 3);
+                    if (PAIR) umma_bf16_pair(tmem + 128 * (t & 1), da, db, IDESC_QK, j > 0 ? 1u : 0u);
+                    else umma_bf16(tmem + 128 * (t & 1), da, db, IDESC_QK, j > 0 ? 1u : 0u);
                 }
-                umma_commit(&bars->k_empty[t % ST]);
-                umma_commit(&bars->s_full[t & 1]);
+                commit(&bars->k_empty[t % ST]);
+                commit(&bars->s_full[t & 1]);
             };
             if (ok && !mbar_wait(&bars->k_full[0], 0)) { *failed = 3; ok = false; }
             if (ok) {
@@ -360,19 +466,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
                 const unsigned char* vt = Vs + (t % ST) * KV_BYTES;
 #pragma unroll
                 for (int j = 0; j < BN / 16; ++j) {
-                    const uint64_t db = desc_mn_major(vt + j * (16 * 128), CHUNK);
-                    umma_bf16_ts(tmem + O_COL, tmem + 128 * (t & 1) + 8 * j, db, IDESC_PV,
-                                 (t > 0 || j > 0) ? 1u : 0u);
+                    const uint64_t db = desc_mn_major(vt + j * (16 * 128), V_CHUNK);
+                    const uint32_t acc = (t > 0 || j > 0) ? 1u : 0u;
+                    if (PAIR) umma_bf16_ts_pair(tmem + O_COL, tmem + 128 * (t & 1) + 8 * j, db, IDESC_PV, acc);
+                    else umma_bf16_ts(tmem + O_COL, tmem + 128 * (t & 1) + 8 * j, db, IDESC_PV, acc);
                 }
-                umma_commit(&bars->v_empty[t % ST]);
-                umma_commit(&bars->pv_done);
-                if (t == nt - 1) umma_commit(&bars->o_done);
+                commit(&bars->v_empty[t % ST]);
+                commit(&bars->pv_done);
+                if (t == nt - 1) commit(&bars->o_done);
             }
             if (!ok) {   // let nobody wait for what will not come
-                umma_commit(&bars->s_full[0]);
-                umma_commit(&bars->s_full[1]);
-                umma_commit(&bars->pv_done);
-                umma_commit(&bars->o_done);
+                commit(&bars->s_full[0]);
+                commit(&bars->s_full[1]);
+                commit(&bars->pv_done);
+                commit(&bars->o_done);
             }
         }
     } else {
@@ -462,7 +569,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->p_full[t & 1]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_first_block(&bars->p_full[t & 1]);
+                else mbar_arrive(&bars->p_full[t & 1]);
+            }
         }
         float l_other = 0.f;
         if (ok && nt > 0) {
@@ -497,10 +607,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();     // the other block no longer touches this block's memory or barriers
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem),
-                     "r"(TMEM_COLS)
-                     : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem),
+                         "r"(TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem),
+                         "r"(TMEM_COLS)
+                         : "memory");
     }
     if (threadIdx.x == 0 && *failed) atomicExch(p.error_flag, *failed);
 }
@@ -543,22 +659,48 @@ SIB_EXPORT int sib_attention_prefill_tc_supports(int n_heads, int n_kv, int head
            width % 8 == 0;
 }
 
-template <int HD, int G>
+template <int HD, int G, bool PAIR>
 static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int max_len,
                      cudaStream_t s) {
-    constexpr int ST = HD == 256 ? 1 : 2;
-    const size_t smem = 1024 + (size_t)BM * HD * 2 + 2 * ST * (size_t)BN * HD * 2 + sizeof(Bars) +
+    constexpr int ST = (HD == 256 && !PAIR) ? 1 : 2;
+    constexpr int NB = PAIR ? 2 : 1;
+    const size_t smem = 1024 + (size_t)BM * HD * 2 + 2 * ST * (size_t)BN * HD * 2 / NB + sizeof(Bars) +
                         2 * 2 * BM * sizeof(float) + 16;
-    auto kernel = attention_prefill_tc_kernel<HD, G>;
+    auto kernel = attention_prefill_tc_kernel<HD, G, PAIR>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
         sib_set_error("attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));
         return (int)e;
     }
     constexpr int MP = BM / G;
-    dim3 grid((max_len + MP - 1) / MP, n_seqs, p.n_kv);
-    kernel<<<grid, 320, smem, s>>>(map, p);
+    const int q_blocks = (max_len + MP - 1) / MP;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(NB * ((q_blocks + NB - 1) / NB), n_seqs, p.n_kv);
+    cfg.blockDim = dim3(320, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = NB;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = PAIR ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kernel, map, p);
+    if (e != cudaSuccess) {
+        sib_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     return sib_check_launch("attention_prefill_tc");
+}
+
+// SIB_PREFILL_PAIR=0: one block per 128 query rows also where pairs of blocks could share the tiles.
+static bool tc_pairs_allowed() {
+    static const bool allowed = [] {
+        const char* v = getenv("SIB_PREFILL_PAIR");
+        return !(v && v[0] == '0');
+    }();
+    return allowed;
 }
 
 // Attention of `n_seqs` packed prompts that all start at position 0; `total_rows`
@@ -603,13 +745,17 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
              scale, softcap};
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;
-#define BY_G(HD)                                                         \
-    do {                                                                 \
-        if (G == 1) return launch_tc<HD, 1>(map, p, n_seqs, max_len, s); \
-        return launch_tc<HD, 2>(map, p, n_seqs, max_len, s);             \
+#define BY_G(HD, PAIR)                                                         \
+    do {                                                                       \
+        if (G == 1) return launch_tc<HD, 1, PAIR>(map, p, n_seqs, max_len, s); \
+        return launch_tc<HD, 2, PAIR>(map, p, n_seqs, max_len, s);             \
     } while (0)
-    if (head_dim == 64) BY_G(64);
-    if (head_dim == 128) BY_G(128);
-    BY_G(256);
+    if (head_dim == 64) BY_G(64, false);
+    if (tc_pairs_allowed()) {
+        if (head_dim == 128) BY_G(128, true);
+        BY_G(256, true);
+    }
+    if (head_dim == 128) BY_G(128, false);
+    BY_G(256, false);
 #undef BY_G
 }

@@ -310,8 +310,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 }
 // arrive on the barrier at this offset in the pair's first block
 __device__ __forceinline__ void mbar_arrive_first_block(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(
-                     in_first_block(bar))
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(in_first_block(bar))
                  : "memory");
 }
 
