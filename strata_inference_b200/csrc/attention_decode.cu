@@ -84,18 +84,20 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
     extern __shared__ __align__(16) float part_dyn[];          // [warps][G][PW]
     float(*part_sm)[G][PW] = reinterpret_cast<float(*)[G][PW]>(part_dyn);
     __shared__ float w_sm[G][MAX_SPLITS];
+    __shared__ float l_sm[G][MAX_SPLITS];
     __shared__ float ml_sm[G][2];
     __shared__ int ticket_sm;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float(*s_sm)[8] = sm_all[warp][0];
     float(*p_sm)[8] = sm_all[warp][1];
     pdl_trigger();
-    pdl_wait();
     const int split = (int)(blockIdx.x % p.splits);
     const int kvh = (int)((blockIdx.x / p.splits) % p.n_kv);
     const int r = (int)(blockIdx.x / ((unsigned)p.splits * p.n_kv));
     const int g = lane >> 2, t = lane & 3;
 
+    // Where the row is and which pages it reads: written by the host before the step, not
+    // by the kernel before this one, so this chain of dependent loads need not wait for it.
     const int pos = p.row_pos[r];
     const int slot = p.seq_slot[p.row_seq[r]];
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
@@ -105,6 +107,11 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
     const int t0 = tile_lo + (split * nw + warp) * per;
     const int t1 = min(t0 + per, tile_hi + 1);
     const int* table = p.page_table + (size_t)slot * p.max_pages;
+    if (t0 < t1) {
+        const int cell0 = p.ring_tokens > 0 ? (t0 << 4) % p.ring_tokens : (t0 << 4);
+        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(table + cell0 / p.page_tokens));
+    }
+    pdl_wait();
 
     // query heads of this kv head as the B operand: lane (g, t) holds head g
     uint4 qf[KB];
@@ -281,23 +288,43 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
     for (int i = threadIdx.x; i < G * p.splits; i += blockDim.x) {
         const int h = i / p.splits, b = i % p.splits;
         const float mb = w_sm[h][b];
-        w_sm[h][b] = mb == -INFINITY ? 0.f : expf(mb - ml_sm[h][0]);
+        const float f = mb == -INFINITY ? 0.f : expf(mb - ml_sm[h][0]);
+        w_sm[h][b] = f;
+        l_sm[h][b] = f * __ldcg(unit_partial + (size_t)i * PW + 1);
     }
     __syncthreads();
+    if (threadIdx.x < G) {
+        const int h = threadIdx.x;
+        float sum = 0.f;
+        for (int b = 0; b < p.splits; ++b) sum += l_sm[h][b];        // in run order
+        ml_sm[h][1] = sum;
+    }
+    __syncthreads();
+    // the weighted sum of the runs' accumulators, 8 loads in flight per thread
     for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
         const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
-        const float* pp = unit_partial + (size_t)h * p.splits * PW;
+        const float* pp = unit_partial + (size_t)h * p.splits * PW + 2 + d;
         float2 a = make_float2(0.f, 0.f);
-        float sum = 0.f;
-#pragma unroll 4
-        for (int b = 0; b < p.splits; ++b) {
+        int b = 0;
+        for (; b + 8 <= p.splits; b += 8) {
+            float2 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = __ldcg(reinterpret_cast<const float2*>(pp + (size_t)(b + u) * PW));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float f = w_sm[h][b + u];
+                a.x += f * v[u].x;
+                a.y += f * v[u].y;
+            }
+        }
+        for (; b < p.splits; ++b) {
             const float f = w_sm[h][b];
-            const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + (size_t)b * PW + 2 + d));
-            sum += f * __ldcg(pp + (size_t)b * PW + 1);
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + (size_t)b * PW));
             a.x += f * v.x;
             a.y += f * v.y;
         }
-        const float inv = 1.0f / sum;
+        const float inv = 1.0f / ml_sm[h][1];
         *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
             __floats2bfloat162_rn(a.x * inv, a.y * inv);
     }

@@ -81,10 +81,11 @@ __global__ void rope_store_kernel(RopeStoreArgs p) {
 // The common case in 16-byte accesses: bfloat16, half-split pairs, the whole
 // head rotated.  One block per row; a thread takes 8 pairs (x[i..i+8) with
 // x[i+half..i+half+8)) of a q or k head, or 8 elements of a v head.
+// A row's units of work are dealt out over the threads of gridDim.y blocks.
 __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
     pdl_trigger();
-    pdl_wait();
     const int r = blockIdx.x;
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
     const int hd = p.head_dim, half = hd / 2;
     const int width = (p.n_heads + 2 * p.n_kv) * hd;
     __nv_bfloat16* row = (__nv_bfloat16*)p.qkv + (size_t)r * width;
@@ -104,9 +105,12 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
             cell_off = ((size_t)page * p.n_kv * p.page_tokens + cell % p.page_tokens) * hd;
         }
     }
+    // (positions, slots and page tables are written by the host before the step: only from
+    // here on does the kernel need what the kernel before it wrote)
+    pdl_wait();
     const size_t head_step = (size_t)p.page_tokens * hd;    // between kv heads of a page
     const int per_head = half / 8;
-    for (int u = threadIdx.x; u < (p.n_heads + p.n_kv) * per_head; u += blockDim.x) {
+    for (int u = first; u < (p.n_heads + p.n_kv) * per_head; u += step) {
         const int y = u / per_head, i0 = (u % per_head) * 8;
         __nv_bfloat16* x = row + (size_t)y * hd;
         const uint4 lo = *reinterpret_cast<const uint4*>(x + i0);
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
     if (keep) {
         const int per_v = hd / 8;
         const __nv_bfloat16* v = row + (size_t)(p.n_heads + p.n_kv) * hd;
-        for (int u = threadIdx.x; u < p.n_kv * per_v; u += blockDim.x) {
+        for (int u = first; u < p.n_kv * per_v; u += step) {
             const int y = u / per_v, i0 = (u % per_v) * 8;
             __nv_bfloat16* dst = (__nv_bfloat16*)p.v_pool + cell_off + (size_t)y * head_step;
             *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(v + (size_t)y * hd + i0);
@@ -172,7 +176,14 @@ SIB_EXPORT int sib_rope_store(void* qkv, int dtype, const int* row_pos, const in
                     n_heads, n_kv, head_dim, rot, style, max_pages, page_tokens, ring_tokens};
     if (dtype == SIB_BF16 && style == 0 && rot == head_dim && head_dim % 16 == 0 &&
         ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0) {
-        sib_launch_chained(rope_store_bf16_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, p);
+        // few rows (decoding): a row's heads spread over several small blocks, so that the
+        // sines and cosines of a row are not one block's serial work
+        const int units = (n_heads + n_kv) * (head_dim / 16);
+        if (rows < 64)
+            sib_launch_chained(rope_store_bf16_kernel, dim3(rows, (units + 31) / 32), dim3(32), 0,
+                               (cudaStream_t)stream, p);
+        else
+            sib_launch_chained(rope_store_bf16_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, p);
         return sib_check_launch("rope_store");
     }
     int threads = 32;
