@@ -439,3 +439,133 @@ def test_schedule_names_a_layer_twice_and_lends_a_cache(tmp_path, dtype):
         got.append(eng.step([(slot, [t])]))
     eng.end_sequence(slot)
     assert_logits_close(torch.cat(got), ref, dtype, "looped schedule with a lent cache")
+
+
+# ---------------------------------------------------------------- a toy feed-forward with routing
+
+class TopOneExperts:
+    """Each row goes to the expert its router scores highest and comes back scaled by that
+    expert's softmax weight: y = p_e * W2_e relu(W1_e x).  Router scores and the softmax are
+    32-bit.  Defined here; the framework only learns its name."""
+
+    @staticmethod
+    def tensors(params, hidden):
+        from strata_inference_b200.weights.loader import TensorDecl
+        E, I = params["experts"], params["expert_size"]
+        out = {"router.weight": TensorDecl((E, hidden))}
+        for e in range(E):
+            out[f"experts.{e}.w1.weight"] = TensorDecl((I, hidden))
+            out[f"experts.{e}.w2.weight"] = TensorDecl((hidden, I))
+        return out
+
+    def __init__(self, params, hidden, weights, rt):
+        self.rt = rt
+        self.E = params["experts"]
+        self.router = weights["router.weight"].to(device=rt.device, dtype=torch.float32)
+        self.w1 = [rt.cast_matrix(weights[f"experts.{e}.w1.weight"]) for e in range(self.E)]
+        self.w2 = [rt.cast_matrix(weights[f"experts.{e}.w2.weight"]) for e in range(self.E)]
+
+    def forward(self, x, ctx):
+        probs = torch.softmax(x.float() @ self.router.t(), dim=-1)
+        weight, choice = probs.max(dim=-1)
+        out = torch.zeros_like(x)
+        for e in range(self.E):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                t = torch.relu(self.rt.linear(x[rows].contiguous(), self.w1[e]))
+                y = self.rt.linear(t, self.w2[e]).float() * weight[rows, None]
+                out[rows] = y.to(x.dtype)
+        return out
+
+
+def _routed_spec(config):
+    """Layer 0: windowed attention and the dense gated feed-forward; layer 1: global attention
+    and the routed feed-forward above.  The parts of a layer are chosen layer by layer."""
+    from strata_inference_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = config["hidden_size"]
+    norm = PartSpec("rms_norm", {"eps": config["eps"], "unit_offset": False})
+    rope = PartSpec("rope_neox", {"theta": 300.0, "rotary_dim": config["head_dim"]})
+    dense = PartSpec("gated_mlp", {"intermediate_size": config["inter"],
+                                   "activation": "gelu_pytorch_tanh"})
+    routed = PartSpec("top_one_experts", {"experts": config["experts"],
+                                          "expert_size": config["expert_size"]})
+    layers = []
+    for i in range(2):
+        mixer = PartSpec("attention", {
+            "num_heads": config["heads"], "num_kv_heads": config["kv_heads"],
+            "head_dim": config["head_dim"], "score_scale": config["head_dim"] ** -0.5,
+            "logit_softcap": 0.0, "window": 6 if i == 0 else 0, "position": rope})
+        layers.append(LayerSpec(prefix=f"layers.{i}.", block="pre_norm", mixer=mixer,
+                                feed_forward=dense if i == 0 else routed,
+                                norms={"pre_mixer": norm, "pre_feed_forward": norm},
+                                names={"mixer": "attn.", "feed_forward": "ffn.",
+                                       "pre_mixer": "norm1.", "pre_feed_forward": "norm2."}))
+    return ModelSpec(architecture="ToyRouted", hidden_size=H, vocab_size=config["vocab"],
+                     max_positions=config["max_pos"], embedding=PartSpec("token_embedding", {}),
+                     layers=tuple(layers), schedule=(ScheduleEntry(0), ScheduleEntry(1)),
+                     final_norm=norm, head=PartSpec("lm_head", {"tied": True}),
+                     names={"embedding": "embed.", "final_norm": "norm.", "head": "head."})
+
+
+def _routed_plain(tokens, W, config):
+    """The same model, whole sequence, in 64-bit, from the plain implementation's parts."""
+    eps, nh, nkv, hd = config["eps"], config["heads"], config["kv_heads"], config["head_dim"]
+    T = len(tokens)
+    norm = lambda x, w: x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w  # noqa: E731
+    pos = torch.arange(T)
+    h = W["embed.weight"][torch.tensor(tokens)]
+    for i in range(2):
+        p = f"layers.{i}."
+        n = norm(h, W[p + "norm1.weight"])
+        q = plain.rope_neox((n @ W[p + "attn.q_proj.weight"].T).view(T, nh, hd), pos, 300.0)
+        k = plain.rope_neox((n @ W[p + "attn.k_proj.weight"].T).view(T, nkv, hd), pos, 300.0)
+        v = (n @ W[p + "attn.v_proj.weight"].T).view(T, nkv, hd)
+        a = plain.attention(q, k, v, hd ** -0.5, 0.0, 6 if i == 0 else 0)
+        h = h + a.reshape(T, nh * hd) @ W[p + "attn.o_proj.weight"].T
+        n = norm(h, W[p + "norm2.weight"])
+        if i == 0:
+            h = h + plain.geglu_ffn(n, W[p + "ffn.gate_proj.weight"], W[p + "ffn.up_proj.weight"],
+                                    W[p + "ffn.down_proj.weight"])
+        else:
+            probs = torch.softmax(n @ W[p + "ffn.router.weight"].T, dim=-1)
+            weight, choice = probs.max(dim=-1)
+            y = torch.zeros_like(n)
+            for r in range(T):
+                e = int(choice[r])
+                t = torch.relu(W[p + f"ffn.experts.{e}.w1.weight"] @ n[r])
+                y[r] = weight[r] * (W[p + f"ffn.experts.{e}.w2.weight"] @ t)
+            h = h + y
+    return norm(h, W["norm.weight"]) @ W["embed.weight"].T
+
+
+def test_toy_routed_feed_forward_beside_the_dense_one(tmp_path):
+    """A feed-forward with routing, defined in this file, in one layer and the framework's
+    dense one in the other: registered, built from a model folder and stepped (prompts of
+    unequal lengths, then single tokens) without a change to the framework."""
+    from strata_inference_b200 import Engine, register_architecture, write_random_model
+    from strata_inference_b200.parts import register_feed_forward
+    from safetensors.torch import load_file
+    register_feed_forward("top_one_experts", TopOneExperts)
+    register_architecture("ToyRouted", dict, _routed_spec)
+    config = {"architectures": ["ToyRouted"], "hidden_size": 48, "inter": 40, "vocab": 70,
+              "heads": 3, "kv_heads": 1, "head_dim": 16, "experts": 3, "expert_size": 24,
+              "eps": 1e-5, "max_pos": 64}
+    d = write_random_model(str(tmp_path / "routed"), config, seed=5, dtype=torch.float32,
+                           matrix_std=0.3, norm_std=0.5)
+    W = {k: v.double() for k, v in load_file(d + "/model.safetensors").items()}
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=256)
+    g = torch.Generator().manual_seed(2)
+    a = torch.randint(0, 70, (21,), generator=g).tolist()
+    b = torch.randint(0, 70, (8,), generator=g).tolist()
+    ref_a, ref_b = _routed_plain(a, W, config), _routed_plain(b, W, config)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    got = eng.step([(sa, a[:12]), (sb, b[:3])], want=[list(range(12)), list(range(3))])
+    _close(got, torch.cat([ref_a[:12], ref_b[:3]]), torch.float32, "routed prompts")
+    for t in range(3, 8):
+        got = eng.step([(sa, [a[9 + t]]), (sb, [b[t]])])
+        _close(got, torch.stack([ref_a[9 + t], ref_b[t]]), torch.float32, f"routed step {t}")
+    eng.end_sequence(sb)
+    got = eng.step([(sa, a[17:])], want=[list(range(4))])
+    _close(got, ref_a[17:], torch.float32, "routed tail")
+    eng.end_sequence(sa)
+    assert eng.cache.pages_in_use() == 0
