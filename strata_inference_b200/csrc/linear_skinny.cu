@@ -11,6 +11,13 @@
 // alternating 64-wide blocks of k of the same 16 (or 32) weight rows; their
 // partial sums are added in warp order through shared memory.
 //
+// The q|k|v product of attention can rotate q and k and write k and v into the paged
+// cache itself (RopeTail): a tile then takes 8 weight rows of a head's first half and
+// the 8 rows that produce their rotation partners (half a head further on), so that
+// both elements of a pair end up in one thread; no weight is moved for it, only the
+// two row pointers of a tile change.  Rotation and cache layout are those of
+// rope_cache.cu.
+//
 // Epilogues: none; soft cap (cap * tanh(y / cap)); gated tanh-GELU, for which
 // the weight rows come in groups of 16: 8 gate rows, then the 8 matching up
 // rows, and y gets N / 2 columns.
@@ -22,7 +29,21 @@
 
 namespace cg = cooperative_groups;
 
-enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2 };
+enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3 };
+
+// What the q|k|v product needs to rotate and store (see rope_cache.cu for the cache layout).
+struct RopeTail {
+    const int* row_pos;        // [rows] absolute position
+    const int* row_seq;        // [rows] index into the step's sequences
+    const int* seq_slot;       // [seqs]
+    const int* seq_end;        // [seqs] length after this step
+    const float* inv_freq;     // [head_dim / 2]
+    __nv_bfloat16* k_pool;     // null: q only, nothing is stored
+    __nv_bfloat16* v_pool;
+    const int* page_table;     // [slots, max_pages]
+    int n_heads, n_kv, head_dim;
+    int max_pages, page_tokens, ring_tokens;
+};
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -55,7 +76,7 @@ template <int NT, int MT, typename OutT, int EPI>
 __global__ void __launch_bounds__(256)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
                      OutT* __restrict__ y, int R, int N, int K, int x_stride, int y_stride,
-                     float cap, int ksplit) {
+                     float cap, int ksplit, RopeTail rope) {
     // [8 warps][MT][NT][32 lanes][4], then [ksplit - 1][MT][NT][32][4] for the other
     // blocks of the cluster (used in the cluster's first block only)
     extern __shared__ float red[];
@@ -65,6 +86,17 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (16 * MT);
+    // the tile's two runs of 8 weight rows: consecutive, or (q and k heads of the rotating
+    // product) half a head apart
+    int run_a = n0, run_b = n0 + 8;
+    if (EPI == EPI_ROPE) {
+        const int per_head = rope.head_dim / 16;
+        const int head = blockIdx.x / per_head, i = blockIdx.x % per_head;
+        if (head < rope.n_heads + rope.n_kv) {
+            run_a = head * rope.head_dim + 8 * i;
+            run_b = run_a + rope.head_dim / 2;
+        }
+    }
 
     float acc[MT][NT][4];
 #pragma unroll
@@ -77,8 +109,8 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     const __nv_bfloat16* wrow[MT][2];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-        wrow[m][0] = W + (size_t)min(n0 + 16 * m + g, N - 1) * K;
-        wrow[m][1] = W + (size_t)min(n0 + 16 * m + g + 8, N - 1) * K;
+        wrow[m][0] = W + (size_t)min(run_a + 16 * m + g, N - 1) * K;
+        wrow[m][1] = W + (size_t)min(run_b + 16 * m + g, N - 1) * K;
     }
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
@@ -171,7 +203,47 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         const int gg = l2 >> 2, tt = l2 & 3;
         const int n_lo = n0 + 16 * m + gg;          // s.x, s.y; n_lo + 8: s.z, s.w
         const int r0 = 8 * j + 2 * tt;              // s.x, s.z; r0 + 1: s.y, s.w
-        if (EPI == EPI_GEGLU) {
+        if (EPI == EPI_ROPE) {
+            // s.x, s.y: feature run_a + gg of rows r0, r0 + 1; s.z, s.w: feature run_b + gg
+            const int hd = rope.head_dim;
+            const int head = run_a / hd, dim = run_a % hd + gg;
+            const bool rotates = head < rope.n_heads + rope.n_kv;
+            const float in_a[2] = {s.x, s.y}, in_b[2] = {s.z, s.w};
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int r = r0 + e;
+                if (r >= R) continue;
+                const int pos = rope.row_pos[r];
+                float oa = in_a[e], ob = in_b[e];
+                if (rotates) {
+                    const float ang = (float)pos * rope.inv_freq[dim];
+                    const float c = cosf(ang), sn = sinf(ang);
+                    oa = in_a[e] * c - in_b[e] * sn;
+                    ob = in_a[e] * sn + in_b[e] * c;
+                }
+                y[(size_t)r * y_stride + run_a + gg] = from_f32<OutT>(oa);
+                y[(size_t)r * y_stride + run_b + gg] = from_f32<OutT>(ob);
+                if (head >= rope.n_heads && rope.k_pool) {
+                    const int b = rope.row_seq[r];
+                    int cell = pos;
+                    bool keep = true;
+                    if (rope.ring_tokens > 0) {
+                        keep = pos >= rope.seq_end[b] - rope.ring_tokens;
+                        cell = pos % rope.ring_tokens;
+                    }
+                    if (keep) {
+                        const int page = rope.page_table[(size_t)rope.seq_slot[b] * rope.max_pages +
+                                                         cell / rope.page_tokens];
+                        const bool is_k = head < rope.n_heads + rope.n_kv;
+                        const int kvh = head - rope.n_heads - (is_k ? 0 : rope.n_kv);
+                        __nv_bfloat16* dst = (is_k ? rope.k_pool : rope.v_pool) +
+                            (((size_t)page * rope.n_kv + kvh) * rope.page_tokens + cell % rope.page_tokens) * hd;
+                        dst[run_a % hd + gg] = __float2bfloat16(oa);
+                        dst[run_b % hd + gg] = __float2bfloat16(ob);
+                    }
+                }
+            }
+        } else if (EPI == EPI_GEGLU) {
             // rows gg (gate) and gg + 8 (up) of the 16-row group make column n_out
             const int n_out = (n0 + 16 * m) / 2 + gg;
             if (n_lo + 8 < N) {
@@ -196,7 +268,7 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
 
 template <int NT, int MT, typename OutT, int EPI>
 static int launch_skinny(const void* W, const void* x, void* y, int R, int N, int K, int x_stride,
-                         int y_stride, float cap, cudaStream_t s) {
+                         int y_stride, float cap, const RopeTail& rope, cudaStream_t s) {
     const int blocks = (N + 16 * MT - 1) / (16 * MT);
     // few weight rows: several blocks (a cluster) share a tile of rows and split k, so
     // that enough loads are in flight to fill the memory system
@@ -228,7 +300,7 @@ static int launch_skinny(const void* W, const void* x, void* y, int R, int N, in
     cfg.numAttrs = sib_chained_launches() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)W,
                                        (const __nv_bfloat16*)x, (OutT*)y, R, N, K, x_stride,
-                                       y_stride, cap, ksplit);
+                                       y_stride, cap, ksplit, rope);
     if (e != cudaSuccess) {
         sib_set_error("skinny_linear: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
@@ -238,11 +310,20 @@ static int launch_skinny(const void* W, const void* x, void* y, int R, int N, in
 
 template <typename OutT, int EPI>
 static int dispatch_skinny(const void* W, const void* x, void* y, int R, int N, int K,
-                           int x_stride, int y_stride, float cap, cudaStream_t s) {
-    if (R <= 8) return launch_skinny<1, 1, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
-    if (R <= 16) return launch_skinny<2, 1, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
-    if (R <= 32) return launch_skinny<4, 2, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
-    return launch_skinny<8, 2, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s);
+                           int x_stride, int y_stride, float cap, const RopeTail& rope,
+                           cudaStream_t s) {
+#define GO(NT, MT) \
+    return launch_skinny<NT, MT, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, rope, s)
+    if (R <= 8) GO(1, 1);
+    if (R <= 16) GO(2, 1);
+    if constexpr (EPI == EPI_ROPE) {
+        sib_set_error("skinny_linear: the rotating product takes at most 16 rows, not %d", R);
+        return -1;
+    } else {
+        if (R <= 32) GO(4, 2);
+        GO(8, 2);
+    }
+#undef GO
 }
 
 // The largest R this kernel takes.
@@ -261,7 +342,8 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
                 "skinny_linear: the gated epilogue needs N (%d) in whole groups of 16", N);
     SIB_REQUIRE(epilogue != EPI_SOFTCAP || cap > 0.f, "skinny_linear: soft cap must be positive");
     cudaStream_t s = (cudaStream_t)stream;
-#define GO(OUT, EPI) return dispatch_skinny<OUT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, s)
+#define GO(OUT, EPI) \
+    return dispatch_skinny<OUT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, RopeTail{}, s)
     if (out_dtype == SIB_BF16) {
         if (epilogue == EPI_NONE) GO(__nv_bfloat16, EPI_NONE);
         if (epilogue == EPI_GEGLU) GO(__nv_bfloat16, EPI_GEGLU);
@@ -273,4 +355,39 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
     }
 #undef GO
     SIB_REQUIRE(false, "skinny_linear: unknown output type %d or epilogue %d", out_dtype, epilogue);
+}
+
+
+// The q|k|v product of attention for at most 16 rows, followed in the same kernel by what
+// sib_rope_store does (half-split pairing over the whole head): y[R, (n_heads + 2 n_kv) *
+// head_dim] gets q and k rotated and v, and k and v also go into the paged cache.
+// n_kv == 0: W holds the q rows only and nothing is stored.
+SIB_EXPORT int sib_skinny_linear_rope(const void* W, const void* x, void* y, int R, int K,
+                                      int x_stride, int y_stride, const int* row_pos,
+                                      const int* row_seq, const int* seq_slot, const int* seq_end,
+                                      const float* inv_freq, void* k_pool, void* v_pool,
+                                      const int* page_table, int max_pages, int page_tokens,
+                                      int ring_tokens, int n_heads, int n_kv, int head_dim,
+                                      void* stream) {
+    if (R == 0) return 0;
+    SIB_REQUIRE(R > 0 && R <= 16, "skinny_linear_rope: %d rows; this product takes 1 to 16", R);
+    SIB_REQUIRE(n_heads > 0 && n_kv >= 0 && head_dim > 0 && head_dim % 16 == 0,
+                "skinny_linear_rope: heads=%d kv=%d head_dim=%d (a multiple of 16)", n_heads, n_kv,
+                head_dim);
+    SIB_REQUIRE(K > 0 && K % 8 == 0 && x_stride % 8 == 0 && ((uintptr_t)W % 16) == 0 &&
+                    ((uintptr_t)x % 16) == 0,
+                "skinny_linear_rope: K=%d and the operands must be aligned to 8 elements", K);
+    SIB_REQUIRE(row_pos && inv_freq, "skinny_linear_rope: positions and frequencies are needed");
+    SIB_REQUIRE(n_kv == 0 || (k_pool && v_pool && page_table && row_seq && seq_slot && seq_end &&
+                              page_tokens > 0 && max_pages > 0),
+                "skinny_linear_rope: incomplete cache description");
+    SIB_REQUIRE(ring_tokens >= 0 && (ring_tokens == 0 || ring_tokens % page_tokens == 0),
+                "skinny_linear_rope: ring of %d tokens is not whole pages of %d", ring_tokens,
+                page_tokens);
+    const int N = (n_heads + 2 * n_kv) * head_dim;
+    RopeTail rope{row_pos, row_seq, seq_slot, seq_end, inv_freq,
+                  n_kv ? (__nv_bfloat16*)k_pool : nullptr, (__nv_bfloat16*)v_pool, page_table,
+                  n_heads, n_kv, head_dim, max_pages, page_tokens, ring_tokens};
+    return dispatch_skinny<__nv_bfloat16, EPI_ROPE>(W, x, y, R, N, K, x_stride, y_stride, 0.f, rope,
+                                                    (cudaStream_t)stream);
 }

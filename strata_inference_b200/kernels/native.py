@@ -347,6 +347,41 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     return out
 
 
+def skinny_linear_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_pos, row_seq,
+                       seq_slot, seq_end, inv_freq: torch.Tensor,
+                       k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                       page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int,
+                       n_heads: int, n_kv: int, head_dim: int) -> torch.Tensor:
+    """The q|k|v product of at most 16 bfloat16 rows that also rotates q and k (half-split
+    pairs over the whole head) and writes k and v into the paged cache as well as into
+    ``out`` (see csrc/linear_skinny.cu, RopeTail).  ``n_kv == 0``: q rows only, nothing stored."""
+    _want(x, torch.bfloat16, "x", contiguous=False)
+    _want(w, torch.bfloat16, "w")
+    _want(out, torch.bfloat16, "out", contiguous=False)
+    _want(inv_freq, torch.float32, "inv_freq")
+    R, K = x.shape
+    N = (n_heads + 2 * n_kv) * head_dim
+    if tuple(w.shape) != (N, K) or tuple(out.shape) != (R, N) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("skinny_linear_rope: shapes do not fit the head counts")
+    if inv_freq.numel() * 2 != head_dim:
+        raise KernelError("skinny_linear_rope: one frequency per pair of the whole head")
+    max_pages = 0
+    if n_kv:
+        _want(k_pool, torch.bfloat16, "k_pool")
+        _want(v_pool, torch.bfloat16, "v_pool")
+        _want(page_table, torch.int32, "page_table")
+        max_pages = page_table.shape[1]
+        if tuple(k_pool.shape[1:]) != (n_kv, page_tokens, head_dim):
+            raise KernelError("skinny_linear_rope: pool layout must be [pages, kv_heads, page_tokens, head_dim]")
+    _check(library().sib_skinny_linear_rope(
+        _ptr(w), _ptr(x), _ptr(out), c_int(R), c_int(K), c_int(x.stride(0)), c_int(out.stride(0)),
+        _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(seq_end), _ptr(inv_freq),
+        _ptr(k_pool) if n_kv else c_void_p(0), _ptr(v_pool) if n_kv else c_void_p(0),
+        _ptr(page_table) if n_kv else c_void_p(0), c_int(max_pages), c_int(page_tokens),
+        c_int(ring_tokens), c_int(n_heads), c_int(n_kv), c_int(head_dim), _stream()))
+    return out
+
+
 def gemm_tcgen05_supports(R: int, N: int, K: int, x_stride: int) -> bool:
     return bool(library().sib_gemm_tcgen05_supports(c_int(R), c_int(N), c_int(K),
                                                     c_longlong(x_stride)))

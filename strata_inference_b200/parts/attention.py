@@ -106,7 +106,6 @@ class Attention:
         rt, nh, hd = self.rt, self.nh, self.hd
         R = x.shape[0]
         nkv = self.nkv if owns_cache else 0
-        qkv = rt.linear(x, self.w_qkv if owns_cache else self.w_q)
         view = ctx.kv(cache_entry)
         fresh = ctx.all_from_start and owns_cache
         if not fresh and not ctx.all_from_start and view.ring_tokens > 0 and \
@@ -119,17 +118,33 @@ class Attention:
             raise ValueError("a run that borrows a windowed cache cannot take prompts longer "
                              "than what that cache keeps")
 
-        if hasattr(self.position, "rotary"):
-            inv_freq, rot, style = self.position.rotary()
+        w_in = self.w_qkv if owns_cache else self.w_q
+        rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
+        if (rotary is not None and rotary[1] == hd and rotary[2] == native.ROPE_HALF_SPLIT
+                and x.dtype == torch.bfloat16 and rt.fuse_rotation and 0 < R <= rt.skinny_max_rows
+                and self.hidden % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0):
+            # few rows: the product rotates q and k and writes k and v into the cache itself
+            qkv = torch.empty((R, w_in.shape[0]), dtype=x.dtype, device=x.device)
+            native.skinny_linear_rope(x, w_in, qkv, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
+                                      ctx.seq_end, rotary[0], view.k if owns_cache else None,
+                                      view.v if owns_cache else None,
+                                      view.page_table if owns_cache else None, view.page_tokens,
+                                      view.ring_tokens, nh, nkv, hd)
         else:
-            q_view = qkv[:, : nh * hd].view(R, nh, hd)
-            k_view = qkv[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd) if nkv else None
-            self.position.apply(q_view, k_view, ctx)
-            inv_freq, rot, style = None, 0, native.ROPE_HALF_SPLIT
-        native.rope_store(qkv, ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end, inv_freq, rot,
-                          style, view.k if owns_cache else None, view.v if owns_cache else None,
-                          view.page_table if owns_cache else None, view.page_tokens,
-                          view.ring_tokens, nh, nkv, hd)
+            qkv = rt.linear(x, w_in)
+            if rotary is not None:
+                inv_freq, rot, style = rotary
+            else:
+                q_view = qkv[:, : nh * hd].view(R, nh, hd)
+                k_view = qkv[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd) if nkv else None
+                self.position.apply(q_view, k_view, ctx)
+                inv_freq, rot, style = None, 0, native.ROPE_HALF_SPLIT
+            native.rope_store(qkv, ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end, inv_freq,
+                              rot, style, view.k if owns_cache else None,
+                              view.v if owns_cache else None,
+                              view.page_table if owns_cache else None, view.page_tokens,
+                              view.ring_tokens, nh, nkv, hd)
 
         out = torch.empty((R, nh * hd), dtype=qkv.dtype, device=qkv.device)
         width = qkv.shape[1]

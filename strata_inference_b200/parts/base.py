@@ -36,6 +36,7 @@ Interfaces (duck-typed; the toy parts of the tests implement exactly these):
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -63,6 +64,8 @@ class Runtime:
         # takes up to native.SKINNY_MAX_ROWS); measured on a B200 at Gemma2-2B sizes it
         # is ahead of the library product up to 16 rows and behind it from 32 on.
         self.skinny_max_rows = 16
+        # SIB_FUSE_ROTATION=0: rotation and cache write always run as a kernel of their own
+        self.fuse_rotation = os.environ.get("SIB_FUSE_ROTATION", "1") != "0"
         # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
         # 256 x 256 tiles) beats the library product followed by the activation kernel
         self.gated_gemm_min_rows = 128

@@ -336,6 +336,53 @@ def test_rope_store(dtype, style, hd, rot):
         _close(vp[pg, :, cell % page].cpu(), v_ref[r], dtype, f"v cell of row {r}")
 
 
+@pytest.mark.parametrize("hd,nh,nkv,K", [(32, 3, 2, 72), (256, 8, 4, 256), (64, 2, 1, 40), (16, 4, 0, 64)])
+def test_skinny_linear_that_rotates_and_stores(hd, nh, nkv, K):
+    """The q|k|v product of a few rows with rotation and cache write in its epilogue: the rows
+    of two sequences, one of them in a ring; nkv = 0 projects q only and stores nothing."""
+    n = _native()
+    g = torch.Generator().manual_seed(40 + hd)
+    theta = 500.0
+    positions = [0, 1, 2, 3, 4, 17, 18, 19, 20]
+    R = len(positions)
+    N = (nh + 2 * nkv) * hd
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    page, ring = 4, 8
+    kp = torch.zeros(9, max(nkv, 1), page, hd, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    table = torch.tensor([[3, 5], [0, 0], [7, 2]], dtype=torch.int32, device=DEV)
+    inv_freq = torch.pow(torch.tensor(theta), (-1.0 / hd) * torch.arange(hd // 2).float() * 2)
+    out = torch.full((R, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
+    n.skinny_linear_rope(x.to(DEV), w.to(DEV), out, i32(positions), i32([0] * 5 + [1] * 4),
+                         i32([2, 0]), i32([5, 21]), inv_freq.to(DEV), kp if nkv else None,
+                         vp if nkv else None, table if nkv else None, page, ring, nh, nkv, hd)
+    y = x.double() @ w.double().T
+
+    def rot_ref(v):  # v [R, heads, hd]
+        ang = torch.tensor(positions).double()[:, None] * inv_freq.double()[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+    q_ref = rot_ref(y[:, :nh * hd].view(R, nh, hd))
+    got = out.double().cpu()
+    _close(got[:, :nh * hd].view(R, nh, hd), q_ref, torch.bfloat16, "q rotated")
+    if not nkv:
+        return
+    k_ref = rot_ref(y[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd))
+    v_ref = y[:, (nh + nkv) * hd:].view(R, nkv, hd)
+    _close(got[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd), k_ref, torch.bfloat16, "k rotated")
+    _close(got[:, (nh + nkv) * hd:].view(R, nkv, hd), v_ref, torch.bfloat16, "v")
+    tab = table.cpu()
+    for r, pos in enumerate(positions):
+        slot = 2 if r < 5 else 0
+        cell = pos % ring
+        pg = int(tab[slot, cell // page])
+        _close(kp[pg, :, cell % page].cpu(), k_ref[r], torch.bfloat16, f"k cell of row {r}")
+        _close(vp[pg, :, cell % page].cpu(), v_ref[r], torch.bfloat16, f"v cell of row {r}")
+
+
 def test_rope_store_ring_keeps_only_the_last_positions():
     """A prompt longer than the ring: only its last ring_tokens positions are written."""
     n = _native()
