@@ -273,10 +273,22 @@ struct TcArgs {
     const int* seq_row0;
     const int* seq_len;
     int* error_flag;
+    float* part;             // partial results of split blocks (see SPLIT below), or null
+    int* tickets;            // 8 per block of query rows, zero between launches
+    int split_tiles;         // blocks with at least this many key tiles are split (0: none)
     int n_heads, n_kv;
     int window;
     float scale, softcap;
 };
+
+// SPLIT.  When the grid is small against the device, a block (or pair) of query rows with
+// many key tiles is run twice, by blockIdx.z / n_kv = 0 and 1, each over half of the
+// tiles.  Both write max, sum and accumulator of their rows to `part`, warp by warp,
+// then draw a ticket of that warp's rows; the warp that draws the second ticket adds the
+// other's partial result to its own and stores the output.
+// Floats of `part` for one block of 128 query rows and one half:
+template <int HD>
+__host__ __device__ constexpr size_t part_floats() { return (size_t)BM * (HD + 2); }
 
 // Barriers of one block.
 struct Bars {
@@ -316,8 +328,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch + 2 * 2 * BM);
     int* failed = reinterpret_cast<int*>(tmem_slot + 1);
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y, kvh = blockIdx.z;
+    const int b = blockIdx.y, kvh = blockIdx.z % p.n_kv, part = blockIdx.z / p.n_kv;
     const int n = p.seq_len[b];
     const int rank = PAIR ? (int)cluster_ctarank() : 0;
     // the longest tiles first; first0: the first position of the block or of the pair
@@ -327,7 +340,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
     const int row0 = p.seq_row0[b];
     const int k_hi = min(n, first0 + NB * MP);
     const int k_lo = p.window > 0 ? max(0, first0 - p.window + 1) : 0;
-    const int kt0 = k_lo / BN, nt = (k_hi + BN - 1) / BN - kt0;
+    int kt0 = k_lo / BN, nt = (k_hi + BN - 1) / BN - kt0;
+    // a long run of key tiles is shared with the block that has the other blockIdx.z / n_kv
+    const bool is_split = p.split_tiles > 0 && nt >= p.split_tiles;
+    if (part == 1 && !is_split) return;                    // (both blocks of a pair)
+    if (is_split) {
+        const int first_half = (nt + 1) / 2;
+        if (part == 1) kt0 += first_half;
+        nt = part == 0 ? first_half : nt - first_half;
+    }
     const int q_col = kvh * G * HD;                        // first column of the group's heads
     const int k_col = (p.n_heads + kvh) * HD;
     const int v_col = (p.n_heads + p.n_kv + kvh) * HD;
@@ -380,6 +401,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
 
     if (warp == 0) {
         if (lane == 0) {
+            // Barriers, tensor memory and the roles above needed nothing from the kernel that
+            // wrote q, k and v; the loads do.  (Every other thread of the block only ever
+            // acts on what these loads bring.)
+            pdl_wait();
             // the query tile: per 64-column chunk two boxes of 64 rows
             expect(&bars->q_full, Q_BYTES);
             for (int c = 0; c < CH; ++c)
@@ -582,15 +607,63 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             if (ok && !swap_with_partner(nt, l, l_other)) { if (lane == 0) *failed = 9; ok = false; }
         }
+        // With a split: this warp's rows to `part`, a ticket, and the second to come goes on.
+        float w_mine = 1.f, w_theirs = 0.f;
+        const float* theirs = nullptr;       // the other half's accumulator columns of this thread
+        float l_all = l + l_other;
+        if (ok && is_split) {
+            // the block's place among all blocks of query rows, and its two partial results
+            const size_t unit = ((size_t)b * p.n_kv + kvh) * gridDim.x + blockIdx.x;
+            float* mine = p.part + (unit * 2 + part) * part_floats<HD>();
+            theirs = p.part + (unit * 2 + (part ^ 1)) * part_floats<HD>();
+            // layout: [HD columns][128 rows], then [128 rows][max, sum]
+            if (half == 0) {
+                mine[(size_t)HD * BM + 2 * row] = m_ref;
+                mine[(size_t)HD * BM + 2 * row + 1] = l_all;
+            }
+#pragma unroll 1
+            for (int c = 0; c < HD / 64; ++c) {
+                uint32_t o[32];
+                const int col0 = (HD / 2) * half + 32 * c;
+                tmem_ld32(lane_addr + O_COL + col0, o);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mine[(size_t)(col0 + j) * BM + row] = __uint_as_float(o[j]);
+            }
+            __threadfence();
+            __syncwarp();
+            int ticket = 0;
+            int* counter = p.tickets + unit * 8 + (warp - 2);
+            if (lane == 0) ticket = atomicAdd(counter, 1);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket == 0) {
+                ok = false;                   // the other half finishes these rows
+            } else {
+                __threadfence();
+                if (lane == 0) *counter = 0;
+                const float m_b = __ldcg(theirs + (size_t)HD * BM + 2 * row);
+                const float l_b = __ldcg(theirs + (size_t)HD * BM + 2 * row + 1);
+                const float top = fmaxf(m_ref, m_b);
+                w_mine = m_ref == -INFINITY ? 0.f : exp2_fast(m_ref - top);
+                w_theirs = m_b == -INFINITY ? 0.f : exp2_fast(m_b - top);
+                l_all = w_mine * l_all + w_theirs * l_b;
+            }
+        }
         if (ok) {
-            const float inv = 1.0f / (l + l_other);
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             const bool store = pos < n;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD +
                                  (HD / 2) * half;
 #pragma unroll 1
             for (int c = 0; c < HD / 64; ++c) {
                 uint32_t o[32];
-                tmem_ld32(lane_addr + O_COL + (HD / 2) * half + 32 * c, o);
+                const int col0 = (HD / 2) * half + 32 * c;
+                tmem_ld32(lane_addr + O_COL + col0, o);
+                if (theirs != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        o[j] = __float_as_uint(w_mine * __uint_as_float(o[j]) +
+                                               w_theirs * __ldcg(theirs + (size_t)(col0 + j) * BM + row));
+                }
                 if (store) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -675,17 +748,27 @@ static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int ma
     constexpr int MP = BM / G;
     const int q_blocks = (max_len + MP - 1) / MP;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(NB * ((q_blocks + NB - 1) / NB), n_seqs, p.n_kv);
+    cfg.gridDim = dim3(NB * ((q_blocks + NB - 1) / NB), n_seqs, p.n_kv * (p.split_tiles > 0 ? 2 : 1));
     cfg.blockDim = dim3(320, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = NB;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    // chained to the kernel before it (see common.cuh), and in clusters of two for pairs
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (sib_chained_launches()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (PAIR) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = NB;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = PAIR ? 1 : 0;
+    cfg.numAttrs = n_attr;
     e = cudaLaunchKernelEx(&cfg, kernel, map, p);
     if (e != cudaSuccess) {
         sib_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
@@ -705,10 +788,44 @@ static bool tc_pairs_allowed() {
 
 // Attention of `n_seqs` packed prompts that all start at position 0; `total_rows`
 // is the number of rows of the packed buffer.
+// Whether a launch of this shape would split its long blocks of query rows (see SPLIT at the
+// top): it does when its blocks would fill at most half of the device.  Returns
+// the number of key tiles from which a block is split (0: no split) and what the launch then
+// needs: bytes of scratch memory and ticket counters (int, zero between launches).
+SIB_EXPORT int sib_attention_prefill_tc_split(int n_seqs, int max_len, int n_heads, int n_kv,
+                                              int head_dim, long long* scratch_bytes,
+                                              int* n_tickets) {
+    if (scratch_bytes) *scratch_bytes = 0;
+    if (n_tickets) *n_tickets = 0;
+    if (n_kv <= 0 || n_heads % n_kv || n_seqs <= 0 || max_len <= 0) return 0;
+    static const bool allowed = [] {
+        const char* v = getenv("SIB_PREFILL_SPLIT");
+        return !(v && v[0] == '0');
+    }();
+    if (!allowed) return 0;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return 0;
+    const int G = n_heads / n_kv, MP = BM / G;
+    const bool pair = head_dim >= 128 && tc_pairs_allowed();
+    const int nb = pair ? 2 : 1;
+    const long long q_blocks = nb * (((max_len + MP - 1) / MP + nb - 1) / nb);
+    const long long blocks = q_blocks * n_seqs * n_kv;
+    // (measured: a split that pushes the launch into a second wave of blocks loses more than
+    // it gains, since every block pays about 9 us of start-up before its first tile)
+    if (2 * blocks > sms) return 0;
+    if (scratch_bytes) *scratch_bytes = blocks * 2 * (long long)BM * (head_dim + 2) * sizeof(float);
+    if (n_tickets) *n_tickets = (int)(blocks * 8);
+    return 6;
+}
+
 SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_rows, void* out,
                                         const int* seq_row0, const int* seq_len, int n_seqs,
                                         int max_len, int n_heads, int n_kv, int head_dim,
-                                        float scale, float softcap, int window, void* stream) {
+                                        float scale, float softcap, int window, void* scratch,
+                                        long long scratch_bytes, int* tickets, int n_tickets,
+                                        void* stream) {
     if (n_seqs == 0 || max_len == 0) return 0;
     SIB_REQUIRE(sib_attention_prefill_tc_supports(n_heads, n_kv, head_dim, width),
                 "attention_prefill_tc: heads=%d kv_heads=%d head_dim=%d is not a shape this kernel "
@@ -741,8 +858,16 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     SIB_REQUIRE(r == CUDA_SUCCESS, "attention_prefill_tc: cuTensorMapEncodeTiled failed with code %d",
                 (int)r);
-    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, g_tc_error_flag[dev], n_heads, n_kv, window,
-             scale, softcap};
+    // long blocks are split if the caller brought the memory for it
+    long long need_bytes = 0;
+    int need_tickets = 0;
+    int split_tiles = sib_attention_prefill_tc_split(n_seqs, max_len, n_heads, n_kv, head_dim,
+                                                     &need_bytes, &need_tickets);
+    if (scratch == nullptr || tickets == nullptr || scratch_bytes < need_bytes ||
+        n_tickets < need_tickets || ((uintptr_t)scratch % 16) != 0)
+        split_tiles = 0;
+    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, g_tc_error_flag[dev], (float*)scratch, tickets,
+             split_tiles, n_heads, n_kv, window, scale, softcap};
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;
 #define BY_G(HD, PAIR)                                                         \

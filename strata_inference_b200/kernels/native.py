@@ -304,18 +304,38 @@ def attention_prefill_tc_supports(n_heads: int, n_kv: int, head_dim: int, width:
                                                             c_int(head_dim), c_int(width)))
 
 
+def attention_prefill_tc_split(n_seqs: int, max_len: int, n_heads: int, n_kv: int,
+                               head_dim: int):
+    """(bytes of scratch memory, ticket counters) that a launch of this shape needs to split
+    its long blocks of query rows; (0, 0) if it would not split."""
+    nbytes, n_tickets = c_longlong(0), c_int(0)
+    from ctypes import byref
+    library().sib_attention_prefill_tc_split(c_int(n_seqs), c_int(max_len), c_int(n_heads),
+                                             c_int(n_kv), c_int(head_dim), byref(nbytes),
+                                             byref(n_tickets))
+    return int(nbytes.value), int(n_tickets.value)
+
+
 def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                          max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
-                         softcap: float, window: int) -> torch.Tensor:
-    """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu)."""
+                         softcap: float, window: int, scratch: Optional[torch.Tensor] = None,
+                         tickets: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu).  With ``scratch``
+    and ``tickets`` (int32, zero before the first call; every call leaves them zero) of the
+    sizes ``attention_prefill_tc_split`` gives, a launch that cannot fill the device runs its
+    long blocks of query rows as two halves."""
     _want(qkv, torch.bfloat16, "qkv")
     _want(out, torch.bfloat16, "out")
     if out.shape[0] != qkv.shape[0] or out.shape[1] != n_heads * head_dim:
         raise KernelError("attention_prefill_tc: out must be [rows, heads * head_dim]")
+    if tickets is not None:
+        _want(tickets, torch.int32, "tickets")
     _check(library().sib_attention_prefill_tc(
         _ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _ptr(out), _ptr(seq_row0),
         _ptr(seq_len), c_int(n_seqs), c_int(max_len), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-        c_float(scale), c_float(softcap), c_int(window), _stream()))
+        c_float(scale), c_float(softcap), c_int(window), _ptr(scratch),
+        c_longlong(scratch.numel() * scratch.element_size() if scratch is not None else 0),
+        _ptr(tickets), c_int(tickets.numel() if tickets is not None else 0), _stream()))
     return out
 
 

@@ -150,9 +150,13 @@ class Attention:
         width = qkv.shape[1]
         if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
                 native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
+            # a launch too small for the device splits its long blocks, given the memory
+            need, n_tickets = native.attention_prefill_tc_split(ctx.n_seqs, ctx.max_count, nh,
+                                                               self.nkv, hd)
             native.attention_prefill_tc(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
                                         ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,
-                                        self.window)
+                                        self.window, rt.scratch(need) if need else None,
+                                        rt.tickets(n_tickets) if need else None)
         elif fresh and qkv.dtype == torch.bfloat16 and \
                 native.attention_prefill_supports(nh, self.nkv, hd):
             native.attention_prefill(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,

@@ -286,6 +286,40 @@ def test_attention_prefill_tc_kernel(nh, nkv, hd, window, cap, boost):
         _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"tcgen05 prefill, sequence of {T}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,cap", [
+    (4, 2, 256, 0, 50.0), (2, 2, 128, 0, 0.0), (4, 2, 128, 900, 30.0), (2, 1, 64, 0, 0.0)])
+def test_attention_prefill_tc_kernel_splits_long_blocks(nh, nkv, hd, window, cap):
+    """Few blocks of query rows: those with many key tiles are run as two halves whose
+    partial results the later one joins; twice in a row through the same tickets."""
+    n = _native()
+    g = torch.Generator().manual_seed(16)
+    lens = [1100, 70]                      # few enough blocks to fill half of the device at most
+    dtype = torch.bfloat16
+    scale = 3.0 / math.sqrt(hd)
+    qs, refs = [], []
+    for T in lens:
+        q = torch.randn(T, nh, hd, generator=g).to(dtype)
+        k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        refs.append(plain.attention(q.double(), k.double(), v.double(), scale, cap, window))
+        qs.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    packed = torch.cat(qs, dim=0).contiguous().to(DEV)
+    row0 = [0, lens[0]]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    need, n_tickets = n.attention_prefill_tc_split(len(lens), max(lens), nh, nkv, hd)
+    assert need > 0 and n_tickets > 0, "a launch this small splits"
+    scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+    tickets = torch.zeros(n_tickets, dtype=torch.int32, device=DEV)
+    for call in range(2):
+        out = torch.full((sum(lens), nh * hd), float("nan"), dtype=dtype, device=DEV)
+        n.attention_prefill_tc(packed, out, i32(row0), i32(lens), len(lens), max(lens), nh, nkv, hd,
+                               scale, cap, window, scratch, tickets)
+        assert n.attention_prefill_tc_error() == 0
+        assert int(tickets.abs().sum()) == 0, "the tickets are put back"
+        for r0, T, ref in zip(row0, lens, refs):
+            _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"split prefill, sequence of {T}, call {call}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
 @pytest.mark.parametrize("hd,rot", [(48, 32), (64, 64), (16, 16)])
