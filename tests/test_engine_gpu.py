@@ -146,6 +146,53 @@ def test_first_tokens(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16)])
+def test_prompts_continued_in_pieces(model_dirs, name, page, dtype):
+    """Two requests fed in pieces of unequal sizes (several new positions of a sequence in one
+    step, below and above the number of rows the weight-streaming kernels take): the logits
+    of every position are those of the whole prompt."""
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, page)
+    top = cfg["max_position_embeddings"]
+    a, b = random_prompts(cfg, [top - 2, top // 2], seed=6)
+    ref_a = plain_logits(a, model_dirs[name, dtype], cfg)
+    ref_b = plain_logits(b, model_dirs[name, dtype], cfg)
+    # a sequence may add at most (ring - window + 1) positions a step once it has begun
+    most = eng.cache.max_step_tokens()
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    pa = pb = 0
+    pieces = [(5, 3), (1, 2), (7, 1), (3, 6), (2, 2), (9, 4), (20, 1), (4, 3)]
+    k = 0
+    got_a, got_b = [], []
+    while pa < len(a) or pb < len(b):
+        na, nb = pieces[k % len(pieces)]
+        k += 1
+        if pa > 0:
+            na = min(na, most)
+        if pb > 0:
+            nb = min(nb, most)
+        na, nb = min(na, len(a) - pa), min(nb, len(b) - pb)
+        entries, want = [], []
+        if na:
+            entries.append((sa, a[pa:pa + na]))
+            want.append(list(range(na)))
+        if nb:
+            entries.append((sb, b[pb:pb + nb]))
+            want.append(list(range(nb)))
+        out = eng.step(entries, want=want)          # both begin in the first step, then both go on
+        if na:
+            got_a.append(out[:na])
+        if nb:
+            got_b.append(out[na:na + nb])
+        pa, pb = pa + na, pb + nb
+    eng.end_sequence(sa)
+    eng.end_sequence(sb)
+    assert_logits_close(torch.cat(got_a), ref_a, dtype, f"{name} request a in pieces")
+    assert_logits_close(torch.cat(got_b), ref_b, dtype, f"{name} request b in pieces")
+    assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_far_key_and_window_edge(tmp_path, dtype):
     """One early key made to stand out: a global layer must find it among all
     keys, a sliding layer must lose it exactly when it leaves the window."""
