@@ -86,3 +86,30 @@ def test_two_layers_of_real_sizes(model, dtype):
     for i in live:
         eng.end_sequence(slots[i])
     assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_of_4096_at_real_sizes(tmp_path, dtype):
+    """Two layers at Gemma2-2B sizes with the real window of 4096: a 4 100-token prompt (the
+    paired tcgen05 prompt kernel with a window; the sliding layer's ring of 4 160 positions
+    is written around once), then 150 single-token steps that take the ring over its end.
+    The plain implementation runs on the GPU here (its code is the same; 4 250 x 4 250 scores
+    per head are too slow on the host)."""
+    from strata_inference_b200 import Engine
+    from strata_inference_b200.weights.random_init import write_random_model
+    cfg = dict(CFG_2B, vocab_size=32000, sliding_window=4096, max_position_embeddings=8192)
+    d = str(tmp_path / "gemma2_window")
+    write_random_model(d, cfg, seed=3, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1)
+    toks = random_prompts(cfg, [4250], seed=4)[0]
+    with torch.no_grad(), torch.device("cuda"):
+        W = {k: v.float().cuda() for k, v in plain_weights(d).items()}
+        ref = plain.forward(toks, W, cfg, dtype=torch.float32).cpu()
+    del W
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=8192)
+    s = eng.new_sequence()
+    outs = [eng.step([(s, toks[:4100])], want=[[4098, 4099]])]
+    for t in toks[4100:]:
+        outs.append(eng.step([(s, [t])]))
+    eng.end_sequence(s)
+    err = _rel(torch.cat(outs), ref[4098:])
+    assert err <= REL_TOL[dtype], f"window of 4096, {dtype}: {err:.2e}"
