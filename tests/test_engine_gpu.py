@@ -254,3 +254,39 @@ def test_step_errors(model_dirs):
         eng.end_sequence(s2)
     with pytest.raises(CacheError):
         eng.step([(s2, [1])])
+
+
+# Sizes at the edges of what the fast kernels take: a width that is no multiple of 8 (no
+# 16-byte rows), an intermediate size that is no multiple of 8 (gate and up rows cannot be
+# interleaved), three heads to a kv head, head sizes 80 and 112, an odd vocabulary.
+ODD = {
+    "narrow rows": dict(hidden_size=100, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                        intermediate_size=100, vocab_size=257),
+    "three to a group": dict(hidden_size=72, num_attention_heads=6, num_key_value_heads=2,
+                             head_dim=80, intermediate_size=88, vocab_size=301),
+    "seven heads": dict(hidden_size=88, num_attention_heads=7, num_key_value_heads=7, head_dim=112,
+                        intermediate_size=136, vocab_size=130),
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", sorted(ODD))
+def test_sizes_the_fast_kernels_refuse_take_the_general_ones(tmp_path, which, dtype):
+    from strata_inference_b200 import Engine
+    cfg = dict(CONFIGS["A"], **ODD[which], max_position_embeddings=96, sliding_window=20,
+               query_pre_attn_scalar=ODD[which]["head_dim"])
+    d = make_model_dir(str(tmp_path / "odd"), cfg, seed=31, sharpen=SHARPEN[dtype])
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=512, page_tokens=16)
+    a, b = random_prompts(cfg, [70, 33], seed=7)
+    ref_a, ref_b = plain_logits(a, d, cfg), plain_logits(b, d, cfg)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    got = eng.step([(sa, a[:40]), (sb, b[:9])], want=[list(range(40)), list(range(9))])
+    assert_logits_close(got, torch.cat([ref_a[:40], ref_b[:9]]), dtype, f"{which}: prompts")
+    for t in range(24):
+        got = eng.step([(sa, [a[40 + t]]), (sb, [b[9 + t]])])
+        assert_logits_close(got, torch.stack([ref_a[40 + t], ref_b[9 + t]]), dtype,
+                            f"{which}: step {t}")
+    eng.end_sequence(sb)
+    got = eng.step([(sa, a[64:])], want=[list(range(6))])
+    assert_logits_close(got, ref_a[64:], dtype, f"{which}: tail")
+    eng.end_sequence(sa)
