@@ -20,15 +20,22 @@ from ..kernels import native
 from ..parts.base import StepContext
 
 
+_STAGES = 4      # steps a caller may be ahead of the device
+
+
 class DecodeGraph:
     def __init__(self, engine, n_seqs: int, temperature: float, top_k: int, top_p: float):
         self.engine = engine
         self.B = B = n_seqs
         self.temperature, self.top_k, self.top_p = temperature, top_k, top_p
-        self.host = torch.zeros(8 * B, dtype=torch.int32).pin_memory()
+        # Pinned staging buffers for the metadata, used in turn: a caller may issue steps
+        # without waiting for them, and a buffer must not be rewritten before its copy ran.
+        self.hosts = [torch.zeros(8 * B, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
+        self.copied = [None] * _STAGES
         ar = torch.arange(B, dtype=torch.int32)
-        for field in (2, 6, 7):          # row_seq, seq_row0, wanted rows: 0..B-1
-            self.host[field * B:(field + 1) * B] = ar
+        for host in self.hosts:
+            for field in (2, 6, 7):      # row_seq, seq_row0, wanted rows: 0..B-1
+                host[field * B:(field + 1) * B] = ar
         self.meta = torch.zeros(8 * B, dtype=torch.int32, device=engine.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[torch.Tensor] = None
@@ -66,7 +73,10 @@ class DecodeGraph:
         slots = [int(s) for s in slots]
         eng.cache.reserve([(s, 1) for s in slots])
         starts = [eng.cache.length(s) for s in slots]
-        h = self.host
+        stage = self.calls % _STAGES
+        if self.copied[stage] is not None:
+            self.copied[stage].synchronize()     # (long done unless the caller runs far ahead)
+        h = self.hosts[stage]
         h[0:B] = torch.tensor([int(t) for t in tokens], dtype=torch.int32)
         st = torch.tensor(starts, dtype=torch.int32)
         h[B:2 * B] = st
@@ -74,6 +84,9 @@ class DecodeGraph:
         h[4 * B:5 * B] = st
         h[5 * B:6 * B] = st + 1
         self.meta.copy_(h, non_blocking=True)
+        if self.copied[stage] is None:
+            self.copied[stage] = torch.cuda.Event()
+        self.copied[stage].record()
         eng.cache.sync_tables()
         if self.graph is not None and use_graph:
             self.graph.replay()

@@ -78,9 +78,12 @@ class Runtime:
         return w.to(device=self.device, dtype=self.dtype).contiguous()
 
     def scratch(self, n_bytes: int) -> torch.Tensor:
-        """A persistent scratch buffer of at least ``n_bytes`` (grows, never shrinks)."""
+        """A persistent scratch buffer of at least ``n_bytes``.  It grows by doubling; a buffer
+        that was outgrown is kept, because a captured graph may still write into it."""
         if self._scratch is None or self._scratch.numel() < n_bytes:
-            self._scratch = torch.empty(max(n_bytes, 1 << 20), dtype=torch.uint8,
+            have = self._scratch.numel() if self._scratch is not None else 0
+            self._retired.append(self._scratch)
+            self._scratch = torch.empty(max(n_bytes, 2 * have, 1 << 20), dtype=torch.uint8,
                                         device=self.device)
         return self._scratch
 

@@ -290,3 +290,31 @@ def test_sizes_the_fast_kernels_refuse_take_the_general_ones(tmp_path, which, dt
     got = eng.step([(sa, a[64:])], want=[list(range(6))])
     assert_logits_close(got, ref_a[64:], dtype, f"{which}: tail")
     eng.end_sequence(sa)
+
+
+def test_steps_issued_without_waiting_and_a_scratch_buffer_that_grows(model_dirs):
+    """Single-token steps issued back to back, their results read only at the end: every step
+    sees its own positions (the metadata's staging buffers are not rewritten before they were
+    copied).  And the scratch buffer that a captured step writes into is not given back when a
+    later step needs a larger one: memory allocated afterwards stays untouched by replays."""
+    name, dtype = "A", "bfloat16"
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, 16)
+    toks = random_prompts(cfg, [100], seed=8)[0]
+    ref = plain_logits(toks, model_dirs[name, dtype], cfg)
+    slot = eng.new_sequence()
+    eng.step([(slot, toks[:60])])
+    for t in toks[60:64]:                       # eager step, capture, two replays
+        eng.decode_step([slot], [t])
+    small = eng.rt.scratch(1)
+    eng.rt.scratch(4 * small.numel())           # a later step needs more
+    assert eng.rt.scratch(1).data_ptr() != small.data_ptr()
+    del small
+    victims = [torch.zeros(1 << 18, dtype=torch.uint8, device=eng.device) for _ in range(8)]
+    got = []
+    for t in toks[64:96]:
+        eng.decode_step([slot], [t])
+        got.append(eng.last_logits.clone())     # no wait for the device in this loop
+    eng.end_sequence(slot)
+    assert all(int(v.sum()) == 0 for v in victims), "a replay wrote into memory that is not its own"
+    assert_logits_close(torch.cat(got), ref[64:96], dtype, "steps issued without waiting")
