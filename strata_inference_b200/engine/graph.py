@@ -12,6 +12,7 @@ launches.
 
 from __future__ import annotations
 
+import gc
 from typing import Optional, Sequence
 
 import torch
@@ -100,9 +101,21 @@ class DecodeGraph:
                 # the step uses).  The capture records the same launches for the
                 # steps to come and runs nothing; its output buffers are the ones
                 # later replays fill.
+                # Nothing but the step's own launches may touch CUDA while it is recorded.  The
+                # garbage collector could: when it frees a pinned buffer of an engine that
+                # is gone, the host allocator asks CUDA about that buffer's events, which
+                # invalidates a capture in progress.  So it collects before and stays off
+                # until the capture has ended.
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    self.logits, self.out = self._forward(slots, starts)
+                collecting = gc.isenabled()
+                gc.collect()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                        self.logits, self.out = self._forward(slots, starts)
+                finally:
+                    if collecting:
+                        gc.enable()
                 self.graph = g
         self.calls += 1
         for s in slots:

@@ -91,7 +91,9 @@ def test_bfloat16_generation_runs_and_is_deterministic(model_dirs):
     eng = GenerationEngine.from_dir(model_dirs["C"], dtype="bfloat16", max_tokens=1024)
     a = eng.generate(prompts, GenerationConfig(max_tokens=40))
     b = eng.generate(prompts, GenerationConfig(max_tokens=40))
-    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    for r, (x, y) in enumerate(zip(a, b)):
+        first = next((i for i, (u, v) in enumerate(zip(x.token_ids, y.token_ids)) if u != v), None)
+        assert x.token_ids == y.token_ids, f"request {r}: the two runs differ from token {first} on"
     assert all(len(o.token_ids) == 40 for o in a)
 
 
