@@ -318,3 +318,32 @@ def test_steps_issued_without_waiting_and_a_scratch_buffer_that_grows(model_dirs
     eng.end_sequence(slot)
     assert all(int(v.sum()) == 0 for v in victims), "a replay wrote into memory that is not its own"
     assert_logits_close(torch.cat(got), ref[64:96], dtype, "steps issued without waiting")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_batch_of_twenty(model_dirs, name, dtype):
+    """More sequences than the weight-streaming kernels take rows: the single-token steps of
+    20 sequences go through the library products, the rotation kernel and the cache
+    attention with 20 rows; through `step` and through the captured `decode_step`."""
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, 16, max_tokens=4096)
+    lens = [5 + (7 * i) % 26 for i in range(20)]
+    reqs = random_prompts(cfg, [n + 8 for n in lens], seed=9)
+    refs = [plain_logits(t, model_dirs[name, dtype], cfg) for t in reqs]
+    slots = [eng.new_sequence() for _ in reqs]
+    got = eng.step([(s, r[:n]) for s, r, n in zip(slots, reqs, lens)])
+    assert_logits_close(got, torch.stack([f[n - 1] for f, n in zip(refs, lens)]), dtype,
+                        f"{name}: 20 prompts")
+    for k in range(8):
+        toks = [r[n + k] for r, n in zip(reqs, lens)]
+        if k < 4:
+            got = eng.step([(s, [t]) for s, t in zip(slots, toks)])
+        else:
+            eng.decode_step(slots, toks)
+            got = eng.last_logits
+        assert_logits_close(got, torch.stack([f[n + k] for f, n in zip(refs, lens)]), dtype,
+                            f"{name}: 20 sequences, step {k}")
+    for s in slots:
+        eng.end_sequence(s)
+    assert eng.cache.pages_in_use() == 0
