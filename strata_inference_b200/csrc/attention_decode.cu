@@ -340,6 +340,37 @@ SIB_EXPORT int sib_attention_decode_supports(int n_heads, int n_kv, int head_dim
     return g_ok && hd_ok && page_tokens % 16 == 0;
 }
 
+// How many warps of this kernel the current device holds at a time for the shape (blocks of
+// 4 warps that fit on an SM, by the kernel's registers and shared memory, times the SMs):
+// what a caller sizes its split of the keys by.  0 if the shape is not one this kernel takes.
+SIB_EXPORT int sib_attention_decode_resident_warps(int n_heads, int n_kv, int head_dim) {
+    if (!sib_attention_decode_supports(n_heads, n_kv, head_dim, 16)) return 0;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return 0;
+    const int G = n_heads / n_kv;
+    int per_sm = 0;
+    cudaError_t e = cudaErrorInvalidValue;
+#define ASK(HD, GG)                                                                         \
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, GG>, 128, \
+                                                      (size_t)4 * GG * (HD + 2) * sizeof(float))
+#define BY_G(HD)                    \
+    do {                            \
+        if (G == 1) ASK(HD, 1);     \
+        else if (G == 2) ASK(HD, 2); \
+        else if (G == 4) ASK(HD, 4); \
+        else ASK(HD, 8);            \
+    } while (0)
+    if (head_dim == 64) BY_G(64);
+    else if (head_dim == 128) BY_G(128);
+    else BY_G(256);
+#undef BY_G
+#undef ASK
+    if (e != cudaSuccess || per_sm <= 0) return 0;
+    return per_sm * 4 * sms;
+}
+
 SIB_EXPORT int sib_attention_decode(
     const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
     int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,

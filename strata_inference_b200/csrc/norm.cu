@@ -74,33 +74,20 @@ __global__ void add_rms_norm_kernel(const T* __restrict__ a, const float* __rest
 }
 
 // The same for bfloat16 activations and a hidden size in whole groups of 8: every
-// access is 16 bytes wide (8 activations, 4 stream or gain values).  The kernel is used
-// for few rows, where its time is memory round trips one after another, so everything it
-// will need is asked for at once: the row of a and the row of h go to shared memory
-// together, the gains are pulled towards L1 (they do not depend on the kernel before:
-// that happens ahead of the dependency wait).
+// access is 16 bytes wide (8 activations, 4 stream or gain values).
 __global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
                                          const float* __restrict__ post_gain, float post_eps,
                                          float* __restrict__ h, const float* __restrict__ pre_gain,
                                          float pre_eps, __nv_bfloat16* __restrict__ out, int hidden) {
-    extern __shared__ float row[];             // [hidden] of a, then [hidden] of h
-    float* hrow = row + hidden;
+    extern __shared__ float row[];
     __shared__ float scratch[33];
     pdl_trigger();
-    const int groups = hidden / 8;
-    for (int v = threadIdx.x; v < groups; v += blockDim.x) {       // a 128-byte line holds 4 groups
-        if ((v & 3) == 0) {
-            if (post_gain) asm volatile("prefetch.global.L1 [%0];\n" ::"l"(post_gain + 8 * v));
-            if (pre_gain) asm volatile("prefetch.global.L1 [%0];\n" ::"l"(pre_gain + 8 * v));
-        }
-    }
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * hidden;
+    const int groups = hidden / 8;
     float ss = 0.f;
     for (int v = threadIdx.x; v < groups; v += blockDim.x) {
         const uint4 raw = *reinterpret_cast<const uint4*>(a + base + 8 * v);
-        const float4 h0 = *reinterpret_cast<const float4*>(h + base + 8 * v);
-        const float4 h1 = *reinterpret_cast<const float4*>(h + base + 8 * v + 4);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -109,8 +96,6 @@ __global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
             row[8 * v + 2 * k + 1] = hi;
             ss += lo * lo + hi * hi;
         }
-        *reinterpret_cast<float4*>(hrow + 8 * v) = h0;
-        *reinterpret_cast<float4*>(hrow + 8 * v + 4) = h1;
     }
     float inv = 1.f;
     if (post_gain) {
@@ -121,7 +106,7 @@ __global__ void add_rms_norm_bf16_kernel(const __nv_bfloat16* __restrict__ a,
     }
     float ss2 = 0.f;
     for (int v = threadIdx.x; v < 2 * groups; v += blockDim.x) {   // float4 at a time
-        float4 hv = *reinterpret_cast<const float4*>(hrow + 4 * v);
+        float4 hv = *reinterpret_cast<const float4*>(h + base + 4 * v);
         float4 av = *reinterpret_cast<const float4*>(row + 4 * v);
         if (post_gain) {
             const float4 gv = *reinterpret_cast<const float4*>(post_gain + 4 * v);
@@ -287,8 +272,8 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
                 "add_rms_norm: hidden=%d needs %zu bytes of shared memory; at most %d are supported",
                 hidden, smem, kMaxRowBytes);
     const int threads = norm_threads(hidden);
-    if (dtype == SIB_BF16 && hidden % 8 == 0 && 2 * smem <= (size_t)kMaxRowBytes &&
-        ((uintptr_t)a % 16) == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+    if (dtype == SIB_BF16 && hidden % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+        ((uintptr_t)h % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
         ((uintptr_t)post_gain % 16) == 0 && ((uintptr_t)pre_gain % 16) == 0) {
         // many rows: a warp per row keeps the device full without block barriers; few rows
         // (decoding): a block per row has the shorter latency
@@ -303,10 +288,10 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
             }
 #undef NORM_CASE
         }
-        int rc = allow_row(add_rms_norm_bf16_kernel, 2 * smem);       // a row of a and a row of h
+        int rc = allow_row(add_rms_norm_bf16_kernel, smem);
         if (rc) return rc;
         sib_launch_chained(add_rms_norm_bf16_kernel, dim3(n_rows),
-                           dim3(threads < 256 ? threads : 256), 2 * smem, (cudaStream_t)stream,
+                           dim3(threads < 256 ? threads : 256), smem, (cudaStream_t)stream,
                            (const __nv_bfloat16*)a, post_gain, post_eps, h, pre_gain, pre_eps,
                            (__nv_bfloat16*)out, hidden);
         return sib_check_launch("add_rms_norm");

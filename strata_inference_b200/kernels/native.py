@@ -251,6 +251,13 @@ def attention_decode_supports(n_heads: int, n_kv: int, head_dim: int, page_token
                                                         c_int(head_dim), c_int(page_tokens)))
 
 
+def attention_decode_resident_warps(n_heads: int, n_kv: int, head_dim: int) -> int:
+    """Warps of the decode attention kernel that the current device holds at a time for this
+    shape (0: not a shape the kernel takes)."""
+    return int(library().sib_attention_decode_resident_warps(c_int(n_heads), c_int(n_kv),
+                                                             c_int(head_dim)))
+
+
 def attention_decode(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                      page_table: torch.Tensor, page_tokens: int, ring_tokens: int, row_pos,
                      row_seq, seq_slot, out: torch.Tensor, scratch: Optional[torch.Tensor],

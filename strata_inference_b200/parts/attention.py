@@ -29,9 +29,8 @@ from ..kernels import native
 from ..weights.loader import TensorDecl
 from .registry import part_class, register_mixer
 
+# warps of the general attention kernel a split of the keys aims at (16 per SM of a B200)
 _TARGET_WARPS = 148 * 16
-# the decode kernel keeps 12 warps resident per SM (its registers decide)
-_RESIDENT_WARPS_DECODE = 148 * 12
 # SIB_PREFILL_TCGEN05=0 selects the mma.sync prompt kernel instead of the tcgen05 one
 _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 
@@ -72,6 +71,7 @@ class Attention:
             [weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0))
         self.w_q = self.w_qkv[: self.nh * self.hd]
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        self._resident_warps: Optional[int] = None
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
@@ -93,8 +93,10 @@ class Attention:
         once (a second, partly filled wave of blocks costs more than it brings)
         and be about as many warps as that allows; a warp takes no fewer than 32
         keys."""
+        if self._resident_warps is None:     # what the device holds of this kernel at a time
+            self._resident_warps = native.attention_decode_resident_warps(self.nh, self.nkv, self.hd)
         units = max(1, ctx.n_rows * self.nkv)
-        most = max(1, min(_RESIDENT_WARPS_DECODE // units, -(-self._longest(ctx, capacity) // 32)))
+        most = max(1, min(self._resident_warps // units, -(-self._longest(ctx, capacity) // 32)))
         for warps in (4, 2):     # wider blocks leave fewer partial results to join
             runs = min(most // warps, 128)
             if runs >= 1 and runs * warps >= 0.9 * most:
