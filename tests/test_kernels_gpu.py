@@ -2,6 +2,7 @@
 operation in 32-bit/64-bit, at sizes other than the engine tests use."""
 
 import math
+import os
 
 import pytest
 import torch
@@ -307,6 +308,8 @@ def test_attention_prefill_tc_kernel_splits_long_blocks(nh, nkv, hd, window, cap
     row0 = [0, lens[0]]
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
     need, n_tickets = n.attention_prefill_tc_split(len(lens), max(lens), nh, nkv, hd)
+    if os.environ.get("SIB_PREFILL_SPLIT") == "0":
+        pytest.skip("the split is switched off")
     assert need > 0 and n_tickets > 0, "a launch this small splits"
     scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
     tickets = torch.zeros(n_tickets, dtype=torch.int32, device=DEV)
