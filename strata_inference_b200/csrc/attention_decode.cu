@@ -461,16 +461,15 @@ static int no_alloc_scratch_address(float** address) {
     return 0;
 }
 
-// The ticket counters come first, one per (row, kv head) and never more than one per
-// (row, head), rounded up to 64 entries; the partial results follow.
-static long long no_alloc_ticket_floats(int rows, int n_heads) {
-    return ((long long)rows * n_heads + 63) / 64 * 64;
-}
+// The ticket counters have a region of their own at the front of the array, of a fixed
+// size, so that no call's partial results can land where another call's counters live.
+static_assert(NO_ALLOC_TICKET_SLOTS % 64 == 0 && NO_ALLOC_TICKET_SLOTS < NO_ALLOC_SCRATCH_FLOATS,
+              "the ticket region is a whole number of 256-byte lines inside the array");
 
 SIB_EXPORT long long sib_attention_decode_no_alloc_floats(int rows, int n_heads, int head_dim,
                                                           int splits) {
     if (splits <= 1) return 0;
-    return no_alloc_ticket_floats(rows, n_heads) + (long long)rows * n_heads * splits * (head_dim + 2);
+    return (long long)NO_ALLOC_TICKET_SLOTS + (long long)rows * n_heads * splits * (head_dim + 2);
 }
 
 SIB_EXPORT int sib_attention_decode_no_alloc(
@@ -478,20 +477,36 @@ SIB_EXPORT int sib_attention_decode_no_alloc(
     int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
     const int* seq_slot, void* out, int rows, int n_heads, int n_kv, int head_dim, float scale,
     float softcap, int window, int splits, void* stream) {
-    SIB_REQUIRE(rows >= 0 && n_heads > 0 && head_dim > 0 && splits >= 1,
-                "attention_decode_no_alloc: rows=%d heads=%d head_dim=%d splits=%d", rows, n_heads,
-                head_dim, splits);
+    SIB_REQUIRE(rows >= 0 && n_heads > 0 && n_kv > 0 && head_dim > 0 && splits >= 1,
+                "attention_decode_no_alloc: rows=%d heads=%d kv_heads=%d head_dim=%d splits=%d",
+                rows, n_heads, n_kv, head_dim, splits);
     const long long need = sib_attention_decode_no_alloc_floats(rows, n_heads, head_dim, splits);
     SIB_REQUIRE(need <= (long long)NO_ALLOC_SCRATCH_FLOATS,
                 "attention_decode_no_alloc: %d rows x %d heads x %d splits x (%d + 2) floats of "
                 "partial results and the ticket counters come to %lld floats, the built-in array "
                 "holds %u; use fewer splits or rows, or sib_attention_decode with memory of your own",
                 rows, n_heads, splits, head_dim, need, NO_ALLOC_SCRATCH_FLOATS);
+    SIB_REQUIRE(splits <= 1 || (long long)rows * n_kv <= (long long)NO_ALLOC_TICKET_SLOTS,
+                "attention_decode_no_alloc: %d rows x %d kv heads need %lld ticket counters, the "
+                "built-in array holds %u; use fewer rows, or sib_attention_decode with memory of "
+                "your own", rows, n_kv, (long long)rows * n_kv, NO_ALLOC_TICKET_SLOTS);
     float* scratch = nullptr;
     const int rc = no_alloc_scratch_address(&scratch);   // the first call on a device sets it up
     if (rc) return rc;
+    if (splits > 1) {
+        // The counters this launch uses start at zero whatever an earlier launch left there
+        // (one that failed midway does not put its counters back).  A memset on the call's
+        // stream allocates nothing.
+        cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)rows * n_kv * sizeof(int),
+                                        (cudaStream_t)stream);
+        if (e != cudaSuccess) {
+            sib_set_error("attention_decode_no_alloc: clearing the ticket counters failed: %s",
+                          cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
     return sib_attention_decode(q, q_stride, k_pool, v_pool, page_table, max_pages, page_tokens,
                                 ring_tokens, row_pos, row_seq, seq_slot, out,
-                                scratch + no_alloc_ticket_floats(rows, n_heads), (int*)scratch, rows,
+                                scratch + NO_ALLOC_TICKET_SLOTS, (int*)scratch, rows,
                                 n_heads, n_kv, head_dim, scale, softcap, window, splits, 4, stream);
 }

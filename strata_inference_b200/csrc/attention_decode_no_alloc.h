@@ -16,31 +16,33 @@
 // Every GPU on which this library is loaded holds it from load until the process
 // exits, whether or not this entry point is ever called.
 //
-// Limits.  With splits > 1 a call uses rows * n_heads * splits * (head_dim + 2)
-// floats for partial results and, in front of them, rows * n_heads ticket
-// counters rounded up to 64 (sib_attention_decode_no_alloc_floats gives the sum);
-// that must not exceed NO_ALLOC_SCRATCH_FLOATS.  A larger request is refused with
-// an error (sib_last_error() says how many floats were asked for), nothing is
-// launched.  With splits == 1 the array is not used.
+// Limits.  The first NO_ALLOC_TICKET_SLOTS words of the array are ticket counters, one
+// per (row, kv head) of a call; the partial results follow, rows * n_heads * splits *
+// (head_dim + 2) floats with splits > 1 (sib_attention_decode_no_alloc_floats gives the
+// sum).  A call whose rows * n_kv exceeds NO_ALLOC_TICKET_SLOTS, or whose sum exceeds
+// NO_ALLOC_SCRATCH_FLOATS, is refused with an error (sib_last_error() says how much was
+// asked for) and nothing is launched.  With splits == 1 the array is not used.
 //
 // Behaviour.  Arguments, result and arithmetic are those of sib_attention_decode
 // without its `partial` and `tickets` arguments.  It calls no cudaMalloc, no cudaFree and no
 // allocating library routine.  The first call on a device looks up the array's
 // device address (cudaGetSymbolAddress, with that device current) and keeps it;
 // make that first call on each device before any stream capture begins.  All
-// calls share the one array.  The partial results need no initial value: every
-// element that is read was written earlier in the same launch.  The ticket
-// counters have to be zero when a launch begins; they are, because the array is
-// zero when the library is loaded and the block that draws the last ticket of a
-// (row, kv head) puts that counter back.  Two calls that overlap on the GPU
-// (different streams, or several host threads) write over each other's partial
-// results and tickets: run calls that use splits > 1 one after another on a
-// device.
+// calls share the one array, which keeps what the last call left in it.  The partial
+// results need no initial value: every element that is read was written earlier in the
+// same launch.  The ticket counters a launch uses have to be zero when it begins: each
+// call clears them on its stream (a memset, no allocation) before it launches, so a
+// launch that failed midway and left its counters non-zero does not spoil the next.
+// The counters and the partial results never share an address, whatever the shapes of
+// successive calls.  Two calls that overlap on the GPU (different streams, or several
+// host threads) write over each other's partial results and tickets: run calls that
+// use splits > 1 one after another on a device.
 #pragma once
 
 #include "common.cuh"
 
 #define NO_ALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u)
+#define NO_ALLOC_TICKET_SLOTS 4096u
 
 SIB_EXPORT int sib_attention_decode_no_alloc(
     const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
