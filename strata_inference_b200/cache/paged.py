@@ -10,8 +10,9 @@ and fixed-size per-sequence state.
   own pool of pages and its own page table; a sequence's pages are taken
   from the pool as it grows.  A group whose layers see all keys keeps every
   position; a group with a window keeps a ring of the last
-  ``ring_tokens`` positions (position p lives in cell p % ring_tokens), one
-  page more than the window so that a step may add several positions.
+  ``ring_tokens`` positions (position p lives in cell p % ring_tokens): the
+  window plus room for the longest step that continues a sequence
+  (``max_continuation`` positions; by default one page more than the window).
 * *State* is a fixed-size tensor per slot and schedule entry for mixers
   that carry a recurrent state instead of keys; it is zeroed when the slot
   is acquired.  (The attention mixer needs none.)
@@ -46,8 +47,13 @@ class KVNeed:
     """Per-position keys and values: what an attention-like mixer declares."""
 
     n_kv_heads: int
-    head_dim: int
-    window: int = 0  # 0: every earlier position stays visible
+    head_dim: int            # width of a key
+    window: int = 0          # 0: every earlier position stays visible
+    value_dim: int = 0       # width of a value; 0: the same as a key
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -98,12 +104,19 @@ class KVGroup:
     """Storage of the layers (schedule entries) that share one :class:`KVNeed`."""
 
     def __init__(self, need: KVNeed, entries: List[int], n_pages: int, max_slots: int,
-                 max_seq_len: int, page_tokens: int, dtype: torch.dtype, device: torch.device):
+                 max_seq_len: int, page_tokens: int, dtype: torch.dtype, device: torch.device,
+                 max_continuation: Optional[int] = None):
         self.need = need
         self.entries = list(entries)
         self.page_tokens = page_tokens
         full_pages = -(-max_seq_len // page_tokens)
-        ring_pages = -(-need.window // page_tokens) + 1 if need.window > 0 else full_pages
+        if need.window <= 0:
+            ring_pages = full_pages
+        elif max_continuation is None:
+            ring_pages = -(-need.window // page_tokens) + 1
+        else:
+            # a step of c positions writes c - 1 cells ahead of what its first row still sees
+            ring_pages = -(-(need.window + max(1, max_continuation) - 1) // page_tokens)
         if ring_pages >= full_pages:
             self.ring_tokens = 0          # never wraps
             self.pages_per_seq = full_pages
@@ -112,11 +125,11 @@ class KVGroup:
             self.pages_per_seq = ring_pages
         self.n_pages = min(n_pages, max_slots * self.pages_per_seq)
         self.pool = PagePool(self.n_pages)
-        shape = (len(entries), self.n_pages, need.n_kv_heads, page_tokens, need.head_dim)
+        shape = (len(entries), self.n_pages, need.n_kv_heads, page_tokens)
         # zeroed once: kernels that work on whole tiles of positions may load a
         # cell that is masked out, and its bits must at least be a number
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.k = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape + (need.v_dim,), dtype=dtype, device=device)
         self.table_host = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32)
         self.table = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32, device=device)
         self.pages: List[List[int]] = [[] for _ in range(max_slots)]
@@ -126,21 +139,24 @@ class KVGroup:
         """Pages a sequence of ``length`` positions holds in this group."""
         return min(-(-length // self.page_tokens), self.pages_per_seq)
 
-    def max_step_tokens(self) -> int:
-        """The most positions one continuation step may add to a sequence
-        without overwriting a key that a row of the same step still sees."""
+    def max_step_tokens(self, start: Optional[int] = None) -> int:
+        """The most positions one step may add to a sequence without overwriting a key
+        that a row of the same step still sees: the ring's room beyond the window, which
+        holds wherever the sequence stands; a sequence that holds ``start`` positions may
+        also add whatever does not wrap around the ring."""
         if self.ring_tokens == 0:
             return 1 << 30
-        return self.ring_tokens - self.need.window + 1
+        room = self.ring_tokens - self.need.window + 1
+        return room if start is None else max(self.ring_tokens - start, room)
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class SequenceCache:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], max_tokens: int, max_seq_len: int,
                  dtype: torch.dtype, device, page_tokens: int = 64,
-                 max_slots: Optional[int] = None):
+                 max_slots: Optional[int] = None, max_continuation: Optional[int] = None):
         if page_tokens <= 0 or max_tokens <= 0 or max_seq_len <= 0:
             raise CacheError("page_tokens, max_tokens and max_seq_len must be positive")
         device = torch.device(device)
@@ -157,7 +173,7 @@ class SequenceCache:
                 by_need.setdefault(need.kv, []).append(entry)
         self.groups: List[KVGroup] = [
             KVGroup(kv, entries, self.total_pages, self.max_slots, max_seq_len, page_tokens,
-                    dtype, device) for kv, entries in by_need.items()]
+                    dtype, device, max_continuation) for kv, entries in by_need.items()]
         self._where: Dict[int, Tuple[int, int]] = {}
         for gi, g in enumerate(self.groups):
             for li, entry in enumerate(g.entries):
@@ -243,6 +259,17 @@ class SequenceCache:
         self._check_slot(slot)
         self.lengths[slot] += n
 
+    def trim(self, slot: int) -> None:
+        """Give back the pages ``slot`` holds beyond what its length needs (what a step
+        reserved and then did not use because it failed)."""
+        self._check_slot(slot)
+        for g in self.groups:
+            keep = g.pages_for(self.lengths[slot])
+            extra = g.pages[slot][keep:]
+            if extra:
+                g.pool.give_back(extra)
+                del g.pages[slot][keep:]
+
     def sync_tables(self) -> None:
         """Bring the device copies of changed page tables up to date."""
         for g in self.groups:
@@ -250,8 +277,9 @@ class SequenceCache:
                 g.table.copy_(g.table_host, non_blocking=True)
                 g.dirty = False
 
-    def max_step_tokens(self) -> int:
-        return min([g.max_step_tokens() for g in self.groups] or [1 << 30])
+    def max_step_tokens(self, start: Optional[int] = None) -> int:
+        """The most positions a step may add to a sequence (that holds ``start`` positions)."""
+        return min([g.max_step_tokens(start) for g in self.groups] or [1 << 30])
 
     # ---- views --------------------------------------------------------
     def kv_view(self, entry: int) -> "KVView":
@@ -277,7 +305,7 @@ class KVView:
     """What a mixer sees of one schedule entry's keys and values."""
 
     k: torch.Tensor            # [pages, kv_heads, page_tokens, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor            # [pages, kv_heads, page_tokens, value_dim]
     page_table: torch.Tensor   # [slots, pages_per_seq] int32, on the device
     page_tokens: int
     ring_tokens: int           # 0: position p lives in cell p

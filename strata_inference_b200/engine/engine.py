@@ -23,8 +23,8 @@ from ..config.registry import read_config_json, spec_from_config
 from ..config.spec import ModelSpec
 from ..kernels import native
 from ..parts.base import Runtime, StepContext
-from ..weights.loader import load_weights
-from .model import DecoderModel, expected_tensors
+from ..weights.arena import DictSource, FileSource, RandomSource
+from .model import DecoderModel, expected_tensors, place_weights
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
            "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
@@ -43,22 +43,32 @@ def parse_dtype(dtype) -> torch.dtype:
 
 
 class Engine:
-    def __init__(self, spec: ModelSpec, weights: Mapping[str, torch.Tensor], dtype="bfloat16",
+    """``weights``: a source of the model's stored tensors (``FileSource``,
+    ``RandomSource``, ``DictSource``) or a plain ``{name: tensor}`` mapping of them."""
+
+    def __init__(self, spec: ModelSpec, weights, dtype="bfloat16",
                  max_tokens: int = 8192, max_seq_len: Optional[int] = None,
-                 page_tokens: int = 64, max_slots: Optional[int] = None, device="cuda:0"):
+                 page_tokens: int = 64, max_slots: Optional[int] = None, device="cuda:0",
+                 max_continuation: Optional[int] = None, where: str = "weights"):
         self.spec = spec
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
+        native.require_device(self.device)
         torch.cuda.set_device(self.device)
         self.rt = Runtime(self.device, self.dtype)
-        self.model = DecoderModel(spec, weights, self.rt)
+        spec.validate()
+        source = weights if hasattr(weights, "write") else DictSource(weights)
+        self.model = DecoderModel(spec, place_weights(spec, source, self.dtype, self.device, where),
+                                  self.rt)
         self.max_seq_len = min(max_seq_len or spec.max_positions, spec.max_positions)
         self.cache = SequenceCache(self.model.cache_needs(), max_tokens, self.max_seq_len,
-                                   self.dtype, self.device, page_tokens, max_slots)
+                                   self.dtype, self.device, page_tokens, max_slots,
+                                   max_continuation)
         self.vocab_size = spec.vocab_size
         # one xorshift64 state per slot, for the sampling kernel
         self.rng_state = torch.ones(self.cache.max_slots, dtype=torch.int64, device=self.device)
         self._graphs: Dict[Tuple, "DecodeGraph"] = {}
+        self.max_graphs = 8     # captured steps kept (by batch size and sampling options)
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
 
     # ---- construction ----------------------------------------------------
@@ -66,22 +76,25 @@ class Engine:
     def from_dir(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
         """Load ``config.json`` and the safetensors of ``model_dir``; the model is
         chosen by the architecture named in config.json."""
+        from ..weights.safetensors_io import ModelFiles
         config = read_config_json(model_dir)
         _, spec = spec_from_config(config)
-        device = torch.device(kw.get("device", "cuda:0"))
-        native.require_device(device)
-        weights = load_weights(model_dir, expected_tensors(spec), device)
-        return cls(spec, weights, dtype, **kw)
+        native.require_device(torch.device(kw.get("device", "cuda:0")))
+        return cls(spec, FileSource(ModelFiles(model_dir)), dtype, where=model_dir, **kw)
 
     @classmethod
-    def from_random(cls, config: Mapping, seed: int, dtype="bfloat16", **kw) -> "Engine":
-        """Random weights drawn on the device (no files): for benchmarks of large shapes."""
-        from ..weights.random_init import random_tensors
+    def from_random(cls, config: Mapping, seed: int, dtype="bfloat16", matrix_std: float = None,
+                    norm_std: float = None, **kw) -> "Engine":
+        """Seeded random weights drawn on the device straight into the weight buffer (no
+        files, no host copy): the model ``write_random_model(dir, config, seed, dtype)``
+        writes, tensor for tensor and bit for bit."""
+        from ..weights import random_init
         _, spec = spec_from_config(config)
-        device = torch.device(kw.get("device", "cuda:0"))
-        native.require_device(device)
-        weights = random_tensors(expected_tensors(spec), seed, parse_dtype(dtype), device)
-        return cls(spec, weights, dtype, **kw)
+        native.require_device(torch.device(kw.get("device", "cuda:0")))
+        source = RandomSource(expected_tensors(spec), seed, parse_dtype(dtype),
+                              random_init.MATRIX_STD if matrix_std is None else matrix_std,
+                              random_init.NORM_STD if norm_std is None else norm_std)
+        return cls(spec, source, dtype, **kw)
 
     # ---- sequences -------------------------------------------------------
     def new_sequence(self) -> int:
@@ -110,48 +123,34 @@ class Engine:
                 if not 0 <= int(t) < V:
                     raise StepError(f"input token ID {t} exceeds vocab_size {V}")
         starts = [self.cache.length(s) for s in slots]
-        all_from_start = all(st == 0 for st in starts)
-        if not all_from_start and max(counts) > self.cache.max_step_tokens():
-            raise StepError(f"a step that continues sequences may add at most "
-                            f"{self.cache.max_step_tokens()} positions to each; "
-                            f"got {max(counts)}")
+        if any(st > 0 for st in starts):
+            # (a step of prompts only attends over its own rows and may be of any length)
+            for slot, st, n in zip(slots, starts, counts):
+                most = self.cache.max_step_tokens(st)
+                if n > most:
+                    raise StepError(
+                        f"slot {slot}: a step that continues sequences may add at most {most} "
+                        f"positions to a sequence of {st} (the windowed layers keep "
+                        f"the window and room for {self.cache.max_step_tokens()} more; "
+                        f"'max_continuation' sizes that room); got {n}")
         if want is None:
             want = [[c - 1] for c in counts]
         if len(want) != len(entries):
             raise StepError("'want' needs one list per sequence")
-        self.cache.reserve(list(zip(slots, counts)))
-
-        R, B = sum(counts), len(entries)
-        row0, acc = [], 0
-        for c in counts:
-            row0.append(acc)
-            acc += c
-        tokens, row_pos, row_seq, want_rows = [], [], [], []
-        for b, (_, toks) in enumerate(entries):
-            tokens.extend(int(t) for t in toks)
-            row_pos.extend(range(starts[b], starts[b] + counts[b]))
-            row_seq.extend([b] * counts[b])
+        want_rows, row0 = [], 0
+        for b, c in enumerate(counts):
             for w in want[b]:
-                if not 0 <= int(w) < counts[b]:
-                    raise StepError(f"wanted place {w} is outside the {counts[b]} tokens "
+                if not 0 <= int(w) < c:
+                    raise StepError(f"wanted place {w} is outside the {c} tokens "
                                     f"of its sequence")
-                want_rows.append(row0[b] + int(w))
-        ends = [s + c for s, c in zip(starts, counts)]
-        flat = tokens + row_pos + row_seq + slots + starts + ends + row0 + want_rows
+                want_rows.append(row0 + int(w))
+            row0 += c
+        self.cache.reserve(list(zip(slots, counts)))
+        seqs = list(zip(slots, starts, counts))
+        flat = StepContext.pack(seqs, [t for _, toks in entries for t in toks], want_rows)
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
         meta = host.to(self.device, non_blocking=True)
-        o = [0]
-
-        def take(n):
-            v = meta[o[0]:o[0] + n]
-            o[0] += n
-            return v
-        ctx = StepContext(
-            n_rows=R, n_seqs=B, tokens=take(R), row_pos=take(R), row_seq=take(R),
-            seq_slot=take(B), seq_start=take(B), seq_end=take(B), seq_row0=take(B),
-            starts=starts, counts=counts, slots=slots, all_from_start=all_from_start,
-            max_count=max(counts), max_end=max(ends), cache=self.cache, runtime=self.rt)
-        return ctx, take(len(want_rows))
+        return StepContext(meta, seqs, len(want_rows), self.cache, self.rt)
 
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
@@ -163,10 +162,15 @@ class Engine:
         last).  Returns ``[n_wanted, vocab]`` 32-bit logits on the device, in the
         order of the entries and of ``want`` (``None`` if nothing is wanted).
         """
-        ctx, want_rows = self._context(entries, want)
-        self.cache.sync_tables()
-        h = self.model.hidden_states(ctx)
-        logits = self.model.logits(h, want_rows) if want_rows.numel() else None
+        ctx = self._context(entries, want)
+        try:
+            self.cache.sync_tables()
+            h = self.model.hidden_states(ctx)
+            logits = self.model.logits(h, ctx.want_rows) if ctx.want_rows.numel() else None
+        except BaseException:
+            for slot in ctx.slots:      # hand back the pages reserved for the failed step
+                self.cache.trim(slot)
+            raise
         for slot, n in zip(ctx.slots, ctx.counts):
             self.cache.advance(slot, n)
         return logits
@@ -197,9 +201,14 @@ class Engine:
         tokens as an int32 tensor on the device."""
         from .graph import DecodeGraph
         key = (len(slots), float(temperature), int(top_k), float(top_p))
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
-            g = self._graphs[key] = DecodeGraph(self, *key)
+            g = DecodeGraph(self, *key)
+            while len(self._graphs) >= self.max_graphs:
+                # the least recently used one goes, with its buffers (each holds a
+                # [sequences, vocab] 32-bit logits buffer beside its activations)
+                self._graphs.pop(next(iter(self._graphs)))
+        self._graphs[key] = g       # most recently used last
         out = g.run(slots, tokens, use_graph)
         self.last_logits = g.last_logits
         return out

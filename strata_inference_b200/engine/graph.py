@@ -29,15 +29,13 @@ class DecodeGraph:
         self.engine = engine
         self.B = B = n_seqs
         self.temperature, self.top_k, self.top_p = temperature, top_k, top_p
-        # Pinned staging buffers for the metadata, used in turn: a caller may issue steps
-        # without waiting for them, and a buffer must not be rewritten before its copy ran.
-        self.hosts = [torch.zeros(8 * B, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
+        # Pinned staging buffers for the step's integers, used in turn: a caller may issue
+        # steps without waiting for them, and a buffer must not be rewritten before its
+        # copy ran.
+        size = StepContext.packed_size(B, B, B)
+        self.hosts = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
         self.copied = [None] * _STAGES
-        ar = torch.arange(B, dtype=torch.int32)
-        for host in self.hosts:
-            for field in (2, 6, 7):      # row_seq, seq_row0, wanted rows: 0..B-1
-                host[field * B:(field + 1) * B] = ar
-        self.meta = torch.zeros(8 * B, dtype=torch.int32, device=engine.device)
+        self.meta = torch.zeros(size, dtype=torch.int32, device=engine.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[torch.Tensor] = None
         self.logits: Optional[torch.Tensor] = None
@@ -45,22 +43,14 @@ class DecodeGraph:
         self.calls = 0
         self.launches_per_step = 0
 
-    def _field(self, i: int) -> torch.Tensor:
-        return self.meta[i * self.B:(i + 1) * self.B]
-
-    def _forward(self, slots, starts):
+    def _forward(self, seqs, capture: bool):
         eng, B = self.engine, self.B
-        ctx = StepContext(
-            n_rows=B, n_seqs=B, tokens=self._field(0), row_pos=self._field(1),
-            row_seq=self._field(2), seq_slot=self._field(3), seq_start=self._field(4),
-            seq_end=self._field(5), seq_row0=self._field(6), starts=list(starts),
-            counts=[1] * B, slots=list(slots), all_from_start=False, max_count=1,
-            max_end=max(starts) + 1, cache=eng.cache, runtime=eng.rt, graph_capture=True)
+        ctx = StepContext(self.meta, seqs, B, eng.cache, eng.rt, graph_capture=capture)
         h = eng.model.hidden_states(ctx)
-        logits = eng.model.logits(h, self._field(7))
+        logits = eng.model.logits(h, ctx.want_rows)
         out = torch.empty(B, dtype=torch.int32, device=eng.device)
         native.sample_rows(logits, self.temperature, self.top_k, self.top_p, eng.rng_state, out,
-                           self._field(3))
+                           ctx.seq_slot)
         return logits, out
 
     def run(self, slots: Sequence[int], tokens: Sequence[int], use_graph: bool = True):
@@ -73,17 +63,24 @@ class DecodeGraph:
                 raise ValueError(f"input token ID {t} exceeds vocab_size {V}")
         slots = [int(s) for s in slots]
         eng.cache.reserve([(s, 1) for s in slots])
-        starts = [eng.cache.length(s) for s in slots]
+        try:
+            result = self._run(slots, tokens, use_graph)
+        except BaseException:
+            for s in slots:
+                eng.cache.trim(s)
+            raise
+        for s in slots:
+            eng.cache.advance(s, 1)
+        return result
+
+    def _run(self, slots, tokens, use_graph: bool):
+        eng, B = self.engine, self.B
+        seqs = [(s, eng.cache.length(s), 1) for s in slots]
         stage = self.calls % _STAGES
         if self.copied[stage] is not None:
             self.copied[stage].synchronize()     # (long done unless the caller runs far ahead)
         h = self.hosts[stage]
-        h[0:B] = torch.tensor([int(t) for t in tokens], dtype=torch.int32)
-        st = torch.tensor(starts, dtype=torch.int32)
-        h[B:2 * B] = st
-        h[3 * B:4 * B] = torch.tensor(slots, dtype=torch.int32)
-        h[4 * B:5 * B] = st
-        h[5 * B:6 * B] = st + 1
+        h.copy_(torch.tensor(StepContext.pack(seqs, tokens, range(B)), dtype=torch.int32))
         self.meta.copy_(h, non_blocking=True)
         if self.copied[stage] is None:
             self.copied[stage] = torch.cuda.Event()
@@ -94,7 +91,9 @@ class DecodeGraph:
             result, self.last_logits = self.out, self.logits
         else:
             before = native.launch_count()
-            self.last_logits, result = self._forward(slots, starts)
+            # (a step that will be captured runs eagerly under the same rules first, so
+            # that a part that cannot be captured fails here, before any recording)
+            self.last_logits, result = self._forward(seqs, capture=use_graph)
             self.launches_per_step = native.launch_count() - before
             if use_graph and self.calls >= 1:
                 # The eager run above was this step (and warmed up every library
@@ -112,12 +111,10 @@ class DecodeGraph:
                 gc.disable()
                 try:
                     with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                        self.logits, self.out = self._forward(slots, starts)
+                        self.logits, self.out = self._forward(seqs, capture=True)
                 finally:
                     if collecting:
                         gc.enable()
                 self.graph = g
         self.calls += 1
-        for s in slots:
-            eng.cache.advance(s, 1)
         return result

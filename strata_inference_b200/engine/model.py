@@ -7,14 +7,15 @@ function with per-architecture branches (src/model/layer.rs:1255-1392).
 
 from __future__ import annotations
 
-from typing import Dict, List, Mapping, Optional
+from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
 from ..cache.paged import CacheNeed
 from ..config.spec import ModelSpec, PartSpec
 from ..parts import registry as parts
-from ..weights.loader import TensorDecl
+from ..weights.arena import DictSource, Resident, WeightArena, resident_of
+from ..weights.loader import TensorDecl, check_table
 
 
 def _sub(weights: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
@@ -48,11 +49,65 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorDecl]:
     return out
 
 
+def _sites(spec: ModelSpec):
+    """(prefix, part class, arguments of its tensors()/resident()) of every part that
+    has tensors, in the order the model is built."""
+    H, V = spec.hidden_size, spec.vocab_size
+    yield (spec.names["embedding"], parts.part_class("embedding", spec.embedding.kind),
+           (spec.embedding.params, H, V))
+    for layer in spec.layers:
+        yield (layer.prefix + layer.names["mixer"], parts.part_class("mixer", layer.mixer.kind),
+               (layer.mixer.params, H))
+        yield (layer.prefix + layer.names["feed_forward"],
+               parts.part_class("feed_forward", layer.feed_forward.kind),
+               (layer.feed_forward.params, H))
+        for site, norm in layer.norms.items():
+            yield (layer.prefix + layer.names[site], parts.part_class("norm", norm.kind),
+                   (norm.params, H))
+    yield (spec.names["final_norm"], parts.part_class("norm", spec.final_norm.kind),
+           (spec.final_norm.params, H))
+    yield (spec.names["head"], parts.part_class("head", spec.head.kind), (spec.head.params, H, V))
+
+
+def resident_plan(spec: ModelSpec) -> Dict[str, Tuple[Resident, str]]:
+    """Every tensor the model keeps on the device, by full name, with the prefix of
+    the stored tensors it is put together from."""
+    plan: Dict[str, Tuple[Resident, str]] = {}
+    for prefix, cls, args in _sites(spec):
+        for name, res in resident_of(cls, cls.tensors(*args), *args).items():
+            plan[prefix + name] = (res, prefix)
+    return plan
+
+
+def place_weights(spec: ModelSpec, source, compute_dtype: torch.dtype, device,
+                  where: str = "weights") -> WeightArena:
+    """Check ``source``'s tensors against the model's and put them on the device: one
+    allocation, every resident tensor written straight to its place."""
+    table = source.table()
+    if table:
+        check_table(where, table, expected_tensors(spec))
+    arena = WeightArena(resident_plan(spec), compute_dtype, device,
+                        {n: dt for n, (_, dt) in table.items()})
+    return arena.fill(source)
+
+
 class DecoderModel:
-    def __init__(self, spec: ModelSpec, weights: Mapping[str, torch.Tensor], rt):
+    """``weights``: the resident tensors by full name (a :class:`WeightArena`'s
+    ``tensors``)."""
+
+    @classmethod
+    def from_stored(cls, spec: ModelSpec, stored: Mapping[str, torch.Tensor], rt) -> "DecoderModel":
+        """Build from stored tensors held in memory."""
+        spec.validate()
+        return cls(spec, place_weights(spec, DictSource(stored), rt.dtype, rt.device), rt)
+
+    def __init__(self, spec: ModelSpec, weights, rt):
         spec.validate()
         self.spec = spec
         self.rt = rt
+        self.arena = weights if isinstance(weights, WeightArena) else None
+        if self.arena is not None:
+            weights = self.arena.tensors
         H, V = spec.hidden_size, spec.vocab_size
         self.embedding = parts.part_class("embedding", spec.embedding.kind)(
             spec.embedding.params, H, V, _sub(weights, spec.names["embedding"]), rt)
@@ -83,7 +138,7 @@ class DecoderModel:
     def hidden_states(self, ctx) -> torch.Tensor:
         """Run every schedule entry over the step's rows; returns the 32-bit
         residual stream [rows, hidden]."""
-        h = self.embedding.forward(ctx.tokens)
+        h = self.embedding.forward(ctx)
         schedule = self.spec.schedule
         normed = None
         for pos, e in enumerate(schedule):
@@ -99,24 +154,16 @@ class DecoderModel:
         return self.head.forward(y)
 
     def weight_bytes(self) -> int:
-        """Bytes of every distinct weight tensor a step reads."""
+        """Bytes of the weights a step reads (every resident tensor once)."""
+        if self.arena is not None:
+            return self.arena.nbytes
         seen, total = set(), 0
-
-        def visit(obj):
-            nonlocal total
-            for v in vars(obj).values():
+        for part in [self.embedding, self.final_norm, self.head] + [
+                p for b in self.blocks for p in vars(b).values()]:
+            for v in vars(part).values() if hasattr(part, "__dict__") else ():
                 if isinstance(v, torch.Tensor) and v.is_cuda:
                     key = v.untyped_storage().data_ptr()
                     if key not in seen:
                         seen.add(key)
                         total += v.untyped_storage().nbytes()
-                elif hasattr(v, "__dict__") and not isinstance(v, (type, torch.device)) \
-                        and v is not self.rt and id(v) not in seen:
-                    seen.add(id(v))
-                    visit(v)
-        visit(self.embedding)
-        for b in self.blocks:
-            visit(b)
-        visit(self.final_norm)
-        visit(self.head)
         return total

@@ -118,6 +118,23 @@ def embed_rows(tokens: torch.Tensor, table: torch.Tensor, scale: float,
     return out
 
 
+def randn_fill(dst: torch.Tensor, rows: int, cols: int, group: int, group_stride: int, key: int,
+               offset: float, std: float, stored_dtype: torch.dtype) -> None:
+    """Seeded normal values for a stored tensor of [rows, cols], written to ``dst``: a view
+    [runs, rows a run, cols] into the weight buffer whose runs may lie apart (see
+    csrc/randn_fill.cu).  ``key`` is the tensor's 64-bit key."""
+    if not dst.is_cuda or dst.stride(2) != 1 or dst.stride(1) != cols:
+        raise KernelError("randn_fill: destination runs must be rows of `cols` contiguous elements")
+    runs, per_run, _ = dst.shape
+    if runs * per_run != rows or (runs > 1 and (per_run != group or dst.stride(0) != group_stride * cols)):
+        raise KernelError("randn_fill: the destination view does not fit the run layout")
+    _check(library().sib_randn_fill(
+        _ptr(dst), _code(dst.dtype), c_longlong(rows), c_longlong(cols),
+        c_longlong(group if runs > 1 else 0), c_longlong(group_stride if runs > 1 else 0),
+        ctypes.c_ulonglong(key), c_float(offset), c_float(std),
+        c_int(BF16 if stored_dtype == torch.bfloat16 else F32), _stream()))
+
+
 def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.Tensor:
     """out[r, i] = gelu_tanh(gate(r, i)) * up(r, i); gate_up rows are [gates | ups]
     (group 0) or groups of ``group`` gates followed by their ups."""

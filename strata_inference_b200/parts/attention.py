@@ -26,11 +26,12 @@ import torch
 from ..cache.paged import CacheNeed, KVNeed
 from ..config.spec import ConfigError, PartSpec
 from ..kernels import native
+from ..weights.arena import Piece, Resident, resident_of
 from ..weights.loader import TensorDecl
 from .registry import part_class, register_mixer
 
-# warps of the general attention kernel a split of the keys aims at (16 per SM of a B200)
-_TARGET_WARPS = 148 * 16
+# warps per SM of the general attention kernel that a split of the keys aims at
+_WARPS_PER_SM = 16
 # SIB_PREFILL_TCGEN05=0 selects the mma.sync prompt kernel instead of the tcgen05 one
 _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 
@@ -50,6 +51,24 @@ class Attention:
             out["position." + name] = decl
         return out
 
+    @staticmethod
+    def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
+        """q, k and v are kept as ONE matrix (one product makes all three)."""
+        nh, nkv, hd = params["num_heads"], params["num_kv_heads"], params["head_dim"]
+        out = {
+            "qkv_proj.weight": Resident(((nh + 2 * nkv) * hd, hidden), pieces=(
+                Piece("q_proj.weight", 0), Piece("k_proj.weight", nh * hd),
+                Piece("v_proj.weight", (nh + nkv) * hd))),
+            "o_proj.weight": Resident((hidden, nh * hd), pieces=(Piece("o_proj.weight"),)),
+        }
+        pos: PartSpec = params["position"]
+        cls = part_class("position", pos.kind)
+        for name, res in resident_of(cls, cls.tensors(pos.params, hd), pos.params, hd).items():
+            out["position." + name] = Resident(res.shape, res.dtype, tuple(
+                Piece("position." + q.source, q.row_offset, q.group, q.group_stride)
+                for q in res.pieces), res.offset)
+        return out
+
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
         self.rt = rt
         self.hidden = hidden
@@ -67,11 +86,11 @@ class Attention:
         pos: PartSpec = params["position"]
         pos_w = {k[len("position."):]: v for k, v in weights.items() if k.startswith("position.")}
         self.position = part_class("position", pos.kind)(pos.params, self.hd, pos_w, rt)
-        self.w_qkv = rt.cast_matrix(torch.cat(
-            [weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0))
+        self.w_qkv = rt.cast_matrix(weights["qkv_proj.weight"])
         self.w_q = self.w_qkv[: self.nh * self.hd]
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
         self._resident_warps: Optional[int] = None
+        self._target_warps = _WARPS_PER_SM * rt.sm_count
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
@@ -84,7 +103,7 @@ class Attention:
     def _splits(self, ctx, capacity: int) -> int:
         """How many runs of keys the general kernel cuts a (row, head) into, one
         warp each: as many as fill the device once, none shorter than 32 keys."""
-        want = max(1, _TARGET_WARPS // max(1, ctx.n_rows * self.nh))
+        want = max(1, self._target_warps // max(1, ctx.n_rows * self.nh))
         return max(1, min(want, -(-self._longest(ctx, capacity) // 32), 128))
 
     def _decode_shape(self, ctx, capacity: int):
@@ -110,15 +129,16 @@ class Attention:
         nkv = self.nkv if owns_cache else 0
         view = ctx.kv(cache_entry)
         fresh = ctx.all_from_start and owns_cache
-        if not fresh and not ctx.all_from_start and view.ring_tokens > 0 and \
-                ctx.max_count > view.ring_tokens - self.window + 1:
-            raise ValueError(f"a step that continues sequences may add at most "
-                             f"{view.ring_tokens - self.window + 1} positions to a sequence "
-                             f"whose layers keep a window of {self.window}; got {ctx.max_count}")
-        if not fresh and ctx.all_from_start and view.ring_tokens > 0 and \
-                ctx.max_end > view.ring_tokens:
-            raise ValueError("a run that borrows a windowed cache cannot take prompts longer "
-                             "than what that cache keeps")
+        if not fresh and view.ring_tokens > 0 and not ctx.graph_capture:
+            # rows that attend over a ring must not overwrite a key that an earlier row of
+            # the same step still sees (a captured step adds one position: always fine)
+            room = view.ring_tokens - self.window + 1
+            for start, n in zip(ctx.starts, ctx.counts):
+                if n > room and start + n > view.ring_tokens:
+                    raise ValueError(
+                        f"a step may add at most {max(room, view.ring_tokens - start)} positions "
+                        f"to a sequence of {start} whose layers keep a window of {self.window} "
+                        f"in a ring of {view.ring_tokens}; got {n}")
 
         w_in = self.w_qkv if owns_cache else self.w_q
         rotary = self.position.rotary() if hasattr(self.position, "rotary") else None

@@ -27,23 +27,33 @@ Interfaces (duck-typed; the toy parts of the tests implement exactly these):
     ``tensors(params, head_dim)`` (usually none); either ``rotary()`` returning
     ``(inv_freq, rotary_dim, style)`` for the fused rotate-and-store kernel, or
     ``apply(q, k, ctx)`` rotating ``[rows, heads, head_dim]`` views in place.
+``Embedding``
+    ``tensors(params, hidden, vocab)``, ``forward(ctx) -> h``: the step's rows of the
+    32-bit residual stream from ``ctx.tokens`` (and ``ctx.row_pos`` if it adds positions).
 ``Block``
     ``forward(h, normed, ctx, entry, cache_entry, owns_cache, next_norm)``:
     ``h`` is the 32-bit residual stream, updated in place; ``normed`` is
     ``first_norm(h)`` if the previous block already made it; the block returns
     ``next_norm(h)`` when it can fuse that, else ``None``.
+
+Tensors.  ``tensors(...)`` declares what a model folder stores for the part.  A part may
+also declare ``resident(...)`` (same arguments): what it keeps on the device and how that
+is put together from the stored tensors (weights/arena.py); its constructor then gets the
+resident tensors, already in place in the model's one weight buffer.  Without
+``resident`` it gets every stored tensor under its stored name, in its stored type.
+``build_part`` builds one part alone from stored tensors.
 """
 
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..cache.paged import KVView, SequenceCache
 from ..kernels import native
+from ..weights.arena import DictSource, WeightArena, resident_of
 
 
 class Runtime:
@@ -56,6 +66,7 @@ class Runtime:
         self.dtype = dtype
         native.require_device(self.device)
         native.library()
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # true 32-bit products: no reduced-precision matrix mode anywhere
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
@@ -132,32 +143,116 @@ class Runtime:
         return y
 
 
-@dataclass
-class StepContext:
-    """One step's rows: which sequence and position each row is, on the
-    device for the kernels and on the host for launch decisions."""
+class CapturedStepError(RuntimeError):
+    """A part read a host-side value of a step that is being captured into a CUDA graph."""
 
-    n_rows: int
-    n_seqs: int
-    tokens: torch.Tensor      # [rows] int32
-    row_pos: torch.Tensor     # [rows] absolute position of the row
-    row_seq: torch.Tensor     # [rows] index of the row's sequence in this step
-    seq_slot: torch.Tensor    # [seqs] cache slot
-    seq_start: torch.Tensor   # [seqs] length before the step
-    seq_end: torch.Tensor     # [seqs] length after the step
-    seq_row0: torch.Tensor    # [seqs] packed index of the sequence's first row
-    starts: List[int]         # host copies
-    counts: List[int]
-    slots: List[int]
-    all_from_start: bool      # every sequence begins at position 0 in this step
-    max_count: int
-    max_end: int
-    cache: SequenceCache
-    runtime: Runtime
-    graph_capture: bool = False   # the step is being captured into a CUDA graph: launch shapes must not depend on lengths
+
+class StepContext:
+    """One step's rows: which sequence and position each row is, on the device for the
+    kernels and on the host for launch decisions.
+
+    There is one way to make one: ``pack`` lays a step's integers out as
+    ``[tokens R | row_pos R | row_seq R | seq_slot B | seq_start B | seq_end B |
+    seq_row0 B | wanted rows n]`` (R rows, B sequences), the caller brings that array to
+    the device, and the constructor cuts the views.  The engine's step, the captured
+    single-token step and the tests all go through it.
+
+    A *captured* step (``graph_capture=True``) is recorded once and replayed for other
+    sequences, positions and slots: only the device tensors are refreshed before a replay.
+    What is the same in every replay stays readable on the host (``n_rows``, ``n_seqs``,
+    ``counts``, ``max_count``, ``all_from_start``); reading ``starts``, ``slots`` or
+    ``max_end`` raises :class:`CapturedStepError`, because a value read while recording
+    would be frozen into the graph.  A part that is to run in captured steps indexes its
+    cache or state with the device tensors (``seq_slot``, ``row_pos``, ...) only.
+    """
+
+    @staticmethod
+    def pack(seqs: Sequence[Tuple[int, int, int]], tokens: Optional[Sequence[int]],
+             want_rows: Sequence[int] = ()) -> List[int]:
+        """The step's integers for sequences ``[(slot, start, count)]``; ``tokens`` are the
+        R token ids in packed order (None: zeros)."""
+        row_pos: List[int] = []
+        row_seq: List[int] = []
+        row0: List[int] = []
+        acc = 0
+        for b, (_, start, n) in enumerate(seqs):
+            row_pos.extend(range(start, start + n))
+            row_seq.extend([b] * n)
+            row0.append(acc)
+            acc += n
+        toks = [0] * acc if tokens is None else [int(t) for t in tokens]
+        if len(toks) != acc:
+            raise ValueError(f"{len(toks)} tokens for {acc} rows")
+        return (toks + row_pos + row_seq + [int(s) for s, _, _ in seqs]
+                + [int(st) for _, st, _ in seqs] + [int(st + n) for _, st, n in seqs]
+                + row0 + [int(w) for w in want_rows])
+
+    @staticmethod
+    def packed_size(n_rows: int, n_seqs: int, n_want: int) -> int:
+        return 3 * n_rows + 4 * n_seqs + n_want
+
+    def __init__(self, meta: torch.Tensor, seqs: Sequence[Tuple[int, int, int]], n_want: int,
+                 cache: SequenceCache, runtime: Runtime, graph_capture: bool = False):
+        self.n_seqs = B = len(seqs)
+        self.counts = [int(n) for _, _, n in seqs]
+        self.n_rows = R = sum(self.counts)
+        if meta.numel() < self.packed_size(R, B, n_want):
+            raise ValueError("the packed step is shorter than its rows and sequences need")
+        at = [0]
+
+        def take(n: int) -> torch.Tensor:
+            v = meta[at[0]:at[0] + n]
+            at[0] += n
+            return v
+        self.tokens = take(R)        # [rows] int32
+        self.row_pos = take(R)       # [rows] absolute position of the row
+        self.row_seq = take(R)       # [rows] index of the row's sequence in this step
+        self.seq_slot = take(B)      # [seqs] cache slot
+        self.seq_start = take(B)     # [seqs] length before the step
+        self.seq_end = take(B)       # [seqs] length after the step
+        self.seq_row0 = take(B)      # [seqs] packed index of the sequence's first row
+        self.want_rows = take(n_want)
+        self.max_count = max(self.counts)
+        self.graph_capture = graph_capture
+        self.all_from_start = (not graph_capture) and all(st == 0 for _, st, _ in seqs)
+        self._starts = [int(st) for _, st, _ in seqs]
+        self._slots = [int(s) for s, _, _ in seqs]
+        self._max_end = max(st + n for _, st, n in seqs)
+        self.cache = cache
+        self.runtime = runtime
+
+    def _host(self, name: str, value):
+        if self.graph_capture:
+            raise CapturedStepError(
+                f"'{name}' was read on the host while the step is captured into a CUDA graph; "
+                f"a replay runs other sequences, so captured steps may use the device "
+                f"tensors of the context only")
+        return value
+
+    @property
+    def starts(self) -> List[int]:
+        return self._host("starts", self._starts)
+
+    @property
+    def slots(self) -> List[int]:
+        return self._host("slots", self._slots)
+
+    @property
+    def max_end(self) -> int:
+        return self._host("max_end", self._max_end)
 
     def kv(self, entry: int) -> KVView:
         return self.cache.kv_view(entry)
 
     def state(self, entry: int) -> torch.Tensor:
         return self.cache.state_view(entry)
+
+
+def build_part(part_class, args: Tuple, stored, rt: Runtime, *extra):
+    """One part alone, from its stored tensors: ``part_class(*args, tensors, rt, *extra)``
+    with the part's resident tensors put together as the model's loader does it."""
+    plan = {name: (res, "") for name, res in
+            resident_of(part_class, part_class.tensors(*args), *args).items()}
+    arena = WeightArena(plan, rt.dtype, rt.device, {n: t.dtype for n, t in stored.items()})
+    arena.fill(DictSource(stored))
+    return part_class(*args, arena.tensors, rt, *extra)

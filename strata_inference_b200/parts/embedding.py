@@ -16,6 +16,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..kernels import native
+from ..weights.arena import Piece, Resident
 from ..weights.loader import TensorDecl
 from .registry import register_embedding, register_head
 
@@ -25,6 +26,10 @@ class TokenEmbedding:
     def tensors(params: Mapping, hidden: int, vocab: int) -> Dict[str, TensorDecl]:
         return {"weight": TensorDecl((vocab, hidden))}
 
+    @staticmethod
+    def resident(params: Mapping, hidden: int, vocab: int) -> Dict[str, Resident]:
+        return {"weight": Resident((vocab, hidden), pieces=(Piece("weight"),))}
+
     def __init__(self, params: Mapping, hidden: int, vocab: int,
                  weights: Mapping[str, torch.Tensor], rt):
         self.rt = rt
@@ -33,7 +38,10 @@ class TokenEmbedding:
         self.scale = float(params.get("scale", 1.0))
         self.table = rt.cast_matrix(weights["weight"])
 
-    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx) -> torch.Tensor:
+        """The step's rows of the 32-bit residual stream.  An embedding gets the whole
+        step context: one that adds learned positions reads ``ctx.row_pos`` too."""
+        tokens = ctx.tokens
         h = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=tokens.device)
         return native.embed_rows(tokens, self.table, self.scale, h)
 
@@ -41,9 +49,15 @@ class TokenEmbedding:
 class LMHead:
     @staticmethod
     def tensors(params: Mapping, hidden: int, vocab: int) -> Dict[str, TensorDecl]:
+        # a tied head uses the embedding's table; a file that stores the head's matrix
+        # all the same is accepted and that tensor is not read
+        return {"weight": TensorDecl((vocab, hidden), optional=bool(params.get("tied", True)))}
+
+    @staticmethod
+    def resident(params: Mapping, hidden: int, vocab: int) -> Dict[str, Resident]:
         if params.get("tied", True):
             return {}
-        return {"weight": TensorDecl((vocab, hidden))}
+        return {"weight": Resident((vocab, hidden), pieces=(Piece("weight"),))}
 
     def __init__(self, params: Mapping, hidden: int, vocab: int,
                  weights: Mapping[str, torch.Tensor], rt, embedding: Optional[TokenEmbedding]):

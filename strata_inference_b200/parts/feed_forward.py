@@ -17,6 +17,7 @@ import torch
 
 from ..config.spec import ConfigError
 from ..kernels import native
+from ..weights.arena import Piece, Resident
 from ..weights.loader import TensorDecl
 from .registry import register_feed_forward
 
@@ -34,6 +35,21 @@ class GatedMLP:
             "down_proj.weight": TensorDecl((hidden, inter)),
         }
 
+    @staticmethod
+    def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
+        """Gate and up as ONE matrix: runs of 8 gate rows followed by the 8 matching up
+        rows when the intermediate size is a multiple of 8, else all gates, then all ups."""
+        inter = int(params["intermediate_size"])
+        if inter % _GROUP == 0:
+            pieces = (Piece("gate_proj.weight", 0, _GROUP, 2 * _GROUP),
+                      Piece("up_proj.weight", _GROUP, _GROUP, 2 * _GROUP))
+        else:
+            pieces = (Piece("gate_proj.weight", 0), Piece("up_proj.weight", inter))
+        return {
+            "gate_up_proj.weight": Resident((2 * inter, hidden), pieces=pieces),
+            "down_proj.weight": Resident((hidden, inter), pieces=(Piece("down_proj.weight"),)),
+        }
+
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
         self.rt = rt
         self.inter = int(params["intermediate_size"])
@@ -41,16 +57,8 @@ class GatedMLP:
         if act not in _ACTIVATIONS:
             raise ConfigError(f"gated_mlp: activation {act!r} is not supported; "
                               f"known: {', '.join(_ACTIVATIONS)}")
-        gate, up = weights["gate_proj.weight"], weights["up_proj.weight"]
-        if self.inter % _GROUP == 0:
-            self.group = _GROUP
-            g = gate.view(self.inter // _GROUP, _GROUP, hidden)
-            u = up.view(self.inter // _GROUP, _GROUP, hidden)
-            fused = torch.cat([g, u], dim=1).reshape(2 * self.inter, hidden)
-        else:
-            self.group = 0
-            fused = torch.cat([gate, up], dim=0)
-        self.w_gate_up = rt.cast_matrix(fused)
+        self.group = _GROUP if self.inter % _GROUP == 0 else 0
+        self.w_gate_up = rt.cast_matrix(weights["gate_up_proj.weight"])
         self.w_down = rt.cast_matrix(weights["down_proj.weight"])
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:

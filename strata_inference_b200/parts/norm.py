@@ -4,7 +4,7 @@
 that store the weight as a deviation from one) instead of gain = weight
 (the reference's convention, src/backend/cpu.rs:797-810, whose input files
 already hold the effective gain).  The gain is formed once, in 32-bit, when
-the part is built.
+the weights are placed on the device.
 """
 
 from __future__ import annotations
@@ -14,6 +14,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..kernels import native
+from ..weights.arena import Piece, Resident
 from ..weights.loader import TensorDecl
 from .registry import register_norm
 
@@ -25,12 +26,16 @@ class RMSNorm:
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
         return {"weight": TensorDecl((hidden,), init="norm")}
 
+    @staticmethod
+    def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
+        return {"gain": Resident((hidden,), torch.float32, (Piece("weight"),),
+                                 1.0 if params.get("unit_offset", False) else 0.0)}
+
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
         self.eps = float(params["eps"])
         self.hidden = hidden
         self.rt = rt
-        w = weights["weight"].to(device=rt.device, dtype=torch.float32)
-        self.gain = (1.0 + w if params.get("unit_offset", False) else w.clone()).contiguous()
+        self.gain = weights["gain"]
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -145,3 +145,37 @@ def test_random_traffic_loses_nothing():
     for s in list(live):
         c.release(s)
     assert c.pages_in_use() == 0 and c.n_free_slots == c.max_slots
+
+
+def test_the_rings_room_for_a_continuing_step_is_a_parameter():
+    c = _cache(max_continuation=20)
+    ring = [g for g in c.groups if g.need.window][0]
+    assert ring.ring_tokens == 28 and ring.pages_per_seq == 7      # window 8 + 19 cells, whole pages
+    assert c.max_step_tokens() == 21
+    # a sequence that has not reached the ring's end may add whatever does not wrap
+    assert c.max_step_tokens(0) == 28 and c.max_step_tokens(3) == 25 and c.max_step_tokens(27) == 21
+    # values narrower than keys get storage of their own width
+    c = _cache(needs=(CacheNeed(kv=KVNeed(2, 16, 0, value_dim=4)),))
+    assert c.groups[0].k.shape[-1] == 16 and c.groups[0].v.shape[-1] == 4
+    assert c.kv_view(0).v.shape == (64, 2, 4, 4)
+
+
+def test_trim_gives_back_what_a_failed_step_reserved():
+    c = _cache()
+    s, t = c.acquire(), c.acquire()
+    c.reserve([(s, 6)])
+    c.advance(s, 6)
+    held = c.pages_in_use()
+    c.reserve([(s, 9), (t, 30)])          # a step that then fails: lengths do not move
+    assert c.pages_in_use() > held
+    c.trim(s)
+    c.trim(t)
+    assert c.pages_in_use() == held and c.length(s) == 6 and c.length(t) == 0
+    c.trim(s)                               # nothing left to give: no page is freed twice
+    c.reserve([(s, 9)])
+    c.advance(s, 9)
+    c.release(s)
+    c.release(t)
+    assert c.pages_in_use() == 0
+    for g in c.groups:
+        assert g.pool.n_free == g.n_pages

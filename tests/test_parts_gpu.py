@@ -28,24 +28,16 @@ def _close(got, ref, dtype, what):
     assert err <= tol * scale, f"{what}: {err:.3e} vs {tol:.0e} x {scale:.3e}"
 
 
-def _ctx(rt, cache, seqs):
-    """A StepContext for sequences [(slot, start, count)]."""
+def _ctx(rt, cache, seqs, tokens=None):
+    """A StepContext for sequences [(slot, start, count)], made the way the engine makes its own."""
     from strata_inference_b200.parts.base import StepContext
-    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
-    row_pos, row_seq, row0, acc = [], [], [], 0
-    for b, (_, start, n) in enumerate(seqs):
-        row_pos += list(range(start, start + n))
-        row_seq += [b] * n
-        row0.append(acc)
-        acc += n
-    return StepContext(
-        n_rows=acc, n_seqs=len(seqs), tokens=i32([0] * acc), row_pos=i32(row_pos),
-        row_seq=i32(row_seq), seq_slot=i32([s for s, _, _ in seqs]),
-        seq_start=i32([st for _, st, _ in seqs]), seq_end=i32([st + n for _, st, n in seqs]),
-        seq_row0=i32(row0), starts=[st for _, st, _ in seqs], counts=[n for _, _, n in seqs],
-        slots=[s for s, _, _ in seqs], all_from_start=all(st == 0 for _, st, _ in seqs),
-        max_count=max(n for _, _, n in seqs), max_end=max(st + n for _, st, n in seqs),
-        cache=cache, runtime=rt)
+    meta = torch.tensor(StepContext.pack(seqs, tokens), dtype=torch.int32, device=DEV)
+    return StepContext(meta, seqs, 0, cache, rt)
+
+
+def _build(part_class, args, stored, rt, *extra):
+    from strata_inference_b200.parts.base import build_part
+    return build_part(part_class, args, stored, rt, *extra)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -56,7 +48,7 @@ def test_norm_part(dtype):
     w = (torch.randn(200, generator=g) * 0.2).to(torch.bfloat16)
     x = torch.randn(7, 200, generator=g)
     for offset in (True, False):
-        part = RMSNorm({"eps": 1e-4, "unit_offset": offset}, 200, {"weight": w}, rt)
+        part = _build(RMSNorm, ({"eps": 1e-4, "unit_offset": offset}, 200), {"weight": w}, rt)
         got = part.forward(x.to(DEV))
         ref = plain.rms_norm(x.double(), w.double() if offset else w.double() - 1.0, 1e-4)
         _close(got, ref, dtype, f"rms_norm part, unit_offset={offset}")
@@ -71,8 +63,8 @@ def test_gated_mlp_part(dtype):
         ws = {n: (torch.randn(s, generator=g) * 0.2).to(torch.bfloat16) for n, s in (
             ("gate_proj.weight", (inter, hidden)), ("up_proj.weight", (inter, hidden)),
             ("down_proj.weight", (hidden, inter)))}
-        part = GatedMLP({"intermediate_size": inter, "activation": "gelu_pytorch_tanh"},
-                        hidden, ws, rt)
+        part = _build(GatedMLP, ({"intermediate_size": inter, "activation": "gelu_pytorch_tanh"},
+                                 hidden), ws, rt)
         x = torch.randn(rows, hidden, generator=g).to(dtype)
         got = part.forward(x.to(DEV), None)
         ref = plain.geglu_ffn(x.double(), ws["gate_proj.weight"].double(),
@@ -98,7 +90,7 @@ def _attention_setup(dtype, window, cfg_name="B"):
               "score_scale": cfg["query_pre_attn_scalar"] ** -0.5,
               "logit_softcap": cfg["attn_logit_softcapping"] or 0.0, "window": window,
               "position": PartSpec("rope_neox", {"theta": cfg["rope_theta"], "rotary_dim": hd})}
-    part = Attention(params, H, ws, rt)
+    part = _build(Attention, (params, H), ws, rt)
     cache = SequenceCache([part.cache_need()], 512, 128, dtype, DEV, page_tokens=8)
     pw = {"self_attn." + k: v for k, v in ws.items()}
     return cfg, rt, part, cache, pw, g
@@ -165,15 +157,15 @@ def test_embedding_and_head_parts(dtype):
     g = torch.Generator().manual_seed(3)
     V, H = 300, 80
     table = (torch.randn(V, H, generator=g) * 0.1).to(torch.bfloat16)
-    emb = TokenEmbedding({"scale": math.sqrt(H)}, H, V, {"weight": table}, rt)
+    emb = _build(TokenEmbedding, ({"scale": math.sqrt(H)}, H, V), {"weight": table}, rt)
     toks = torch.randint(0, V, (11,), generator=g, dtype=torch.int32)
-    h = emb.forward(toks.to(DEV))
+    h = emb.forward(_ctx(rt, None, [(0, 0, 11)], toks.tolist()))
     _close(h, plain.embed(toks.tolist(), table.double(), H, torch.float64), torch.float32,
            "embedding")
     for rows in (3, 100):
         y = torch.randn(rows, H, generator=g).to(dtype)
         for cap in (0.0, 2.0):
-            head = LMHead({"tied": True, "logit_softcap": cap}, H, V, {}, rt, emb)
+            head = _build(LMHead, ({"tied": True, "logit_softcap": cap}, H, V), {}, rt, emb)
             got = head.forward(y.to(DEV))
             ref = y.double() @ table.double().T
             if cap:
@@ -193,7 +185,7 @@ def test_block_part(dtype):
     _, spec = spec_from_config(cfg)
     ws = random_tensors(expected_tensors(spec), 5, torch.bfloat16, "cpu", 0.1, 0.3)
     rt = _rt(dtype)
-    model = DecoderModel(spec, ws, rt)
+    model = DecoderModel.from_stored(spec, ws, rt)
     cache = SequenceCache(model.cache_needs(), 512, 256, dtype, DEV, page_tokens=16)
     T = 50
     h0 = torch.randn(T, cfg["hidden_size"], generator=torch.Generator().manual_seed(6))
@@ -342,9 +334,9 @@ def test_toy_position_encoding_through_apply(dtype):
           "v_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.1,
           "o_proj.weight": torch.randn(H, nh * hd, generator=g) * 0.1}
     ws = {k: v.to(torch.bfloat16) for k, v in ws.items()}
-    part = Attention({"num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "score_scale": 0.3,
-                      "logit_softcap": 0.0, "window": 0,
-                      "position": PartSpec("damped", {"slope": slope})}, H, ws, rt)
+    part = _build(Attention, ({"num_heads": nh, "num_kv_heads": nkv, "head_dim": hd,
+                               "score_scale": 0.3, "logit_softcap": 0.0, "window": 0,
+                               "position": PartSpec("damped", {"slope": slope})}, H), ws, rt)
     cache = SequenceCache([part.cache_need()], 256, 64, dtype, DEV, page_tokens=16)
     T, cut = 40, 25
     x = torch.randn(T, H, generator=g).to(dtype)

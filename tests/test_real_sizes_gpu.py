@@ -42,7 +42,8 @@ def model(request, tmp_path_factory):
     from strata_inference_b200.weights.random_init import write_random_model
     cfg = CONFIGS[request.param]
     d = str(tmp_path_factory.mktemp("gemma2_%s_sizes" % request.param))
-    write_random_model(d, cfg, seed=17, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1)
+    write_random_model(d, cfg, seed=17, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1,
+                       device="cuda:0")
     W = {k: v.float() for k, v in plain_weights(d).items()}
     reqs = random_prompts(cfg, [200, 37, 150], seed=18)
     refs = [plain.forward(t, W, cfg, dtype=torch.float32) for t in reqs]
@@ -99,7 +100,8 @@ def test_window_of_4096_at_real_sizes(tmp_path, dtype):
     from strata_inference_b200.weights.random_init import write_random_model
     cfg = dict(CFG_2B, vocab_size=32000, sliding_window=4096, max_position_embeddings=8192)
     d = str(tmp_path / "gemma2_window")
-    write_random_model(d, cfg, seed=3, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1)
+    write_random_model(d, cfg, seed=3, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1,
+                       device="cuda:0")
     toks = random_prompts(cfg, [4250], seed=4)[0]
     with torch.no_grad(), torch.device("cuda"):
         W = {k: v.float().cuda() for k, v in plain_weights(d).items()}
