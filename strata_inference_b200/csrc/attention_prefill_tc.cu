@@ -714,17 +714,6 @@ static EncodeTiledFn tc_encode_fn() {
     return fn;
 }
 
-static int* g_tc_error_flag[64] = {};
-
-SIB_EXPORT int sib_attention_prefill_tc_error(int clear) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_tc_error_flag[dev]) return 0;
-    int v = 0;
-    cudaMemcpy(&v, g_tc_error_flag[dev], sizeof(int), cudaMemcpyDeviceToHost);
-    if (clear && v) cudaMemset(g_tc_error_flag[dev], 0, sizeof(int));
-    return v;
-}
-
 SIB_EXPORT int sib_attention_prefill_tc_supports(int n_heads, int n_kv, int head_dim, int width) {
     if (n_kv <= 0 || n_heads % n_kv) return 0;
     const int G = n_heads / n_kv;
@@ -841,11 +830,8 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     SIB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, "attention_prefill_tc: no current device");
-    if (!g_tc_error_flag[dev]) {
-        e = cudaMalloc(&g_tc_error_flag[dev], sizeof(int));
-        SIB_REQUIRE(e == cudaSuccess, "attention_prefill_tc: %s", cudaGetErrorString(e));
-        cudaMemset(g_tc_error_flag[dev], 0, sizeof(int));
-    }
+    int* error_flag = sib_error_word(SIB_ERR_ATTENTION_PREFILL_TC);
+    if (!error_flag) return -1;
     EncodeTiledFn enc = tc_encode_fn();
     SIB_REQUIRE(enc != nullptr, "attention_prefill_tc: cuTensorMapEncodeTiled is not available");
     CUtensorMap map;
@@ -866,7 +852,7 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
     if (scratch == nullptr || tickets == nullptr || scratch_bytes < need_bytes ||
         n_tickets < need_tickets || ((uintptr_t)scratch % 16) != 0)
         split_tiles = 0;
-    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, g_tc_error_flag[dev], (float*)scratch, tickets,
+    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, error_flag, (float*)scratch, tickets,
              split_tiles, n_heads, n_kv, window, scale, softcap};
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;

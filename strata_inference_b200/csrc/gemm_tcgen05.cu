@@ -607,20 +607,7 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const GemmA
     return sib_check_launch("gemm_tcgen05");
 }
 
-static int* g_error_flag[64] = {};
 static int g_sm_count[64] = {};
-
-// 0, or the code a block left when one of its waits ran out (1: a stage never
-// became free, 2: a load never arrived, 3: the accumulator never became ready).
-// Reads the flag with a synchronous copy; meant for tests and after a failure.
-SIB_EXPORT int sib_gemm_tcgen05_error(int clear) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_error_flag[dev]) return 0;
-    int v = 0;
-    cudaMemcpy(&v, g_error_flag[dev], sizeof(int), cudaMemcpyDeviceToHost);
-    if (clear && v) cudaMemset(g_error_flag[dev], 0, sizeof(int));
-    return v;
-}
 
 SIB_EXPORT int sib_gemm_tcgen05_supports(int R, int N, int K, long long x_stride) {
     return R > 0 && N > 0 && K > 0 && K % 8 == 0 && x_stride % 8 == 0;
@@ -642,12 +629,8 @@ static int gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, in
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     SIB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, "gemm_tcgen05: no current device");
-    if (!g_error_flag[dev]) {
-        // one int per device for the bounded waits' verdict; allocated at the first call
-        e = cudaMalloc(&g_error_flag[dev], sizeof(int));
-        SIB_REQUIRE(e == cudaSuccess, "gemm_tcgen05: %s", cudaGetErrorString(e));
-        cudaMemset(g_error_flag[dev], 0, sizeof(int));
-    }
+    int* error_flag = sib_error_word(SIB_ERR_GEMM_TCGEN05);   // the bounded waits' verdict
+    if (!error_flag) return -1;
     if (!g_sm_count[dev]) {
         e = cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
         SIB_REQUIRE(e == cudaSuccess && g_sm_count[dev] >= 2, "gemm_tcgen05: %s", cudaGetErrorString(e));
@@ -657,7 +640,7 @@ static int gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, in
         // many rows: tiles of 256 x 256 on pairs of SMs
         if (make_map(&mx, x, R, K, x_stride, 128)) return -1;
         if (make_map(&mw, W, N, K, K, PAIR_BN / 2)) return -1;
-        GemmArgs pp{y, g_error_flag[dev], R, N, K, y_stride, epilogue, cap};
+        GemmArgs pp{y, error_flag, R, N, K, y_stride, epilogue, cap};
         if (out_dtype == SIB_BF16)
             return launch_pair<__nv_bfloat16>(mx, mw, pp, g_sm_count[dev], (cudaStream_t)stream);
         if (out_dtype == SIB_F32)
@@ -667,7 +650,7 @@ static int gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, in
     const int bn = R <= 32 ? 32 : R <= 64 ? 64 : R <= 128 ? 128 : 256;
     if (make_map(&mw, W, N, K, K, BM)) return -1;
     if (make_map(&mx, x, R, K, x_stride, bn)) return -1;
-    GemmArgs p{y, g_error_flag[dev], R, N, K, y_stride, epilogue, cap};
+    GemmArgs p{y, error_flag, R, N, K, y_stride, epilogue, cap};
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(BN, ST)                                                              \
     do {                                                                        \

@@ -41,3 +41,92 @@ SIB_EXPORT int sib_compiled_arch() {
     return 0;
 #endif
 }
+
+// ---------------------------------------------------------------------------
+// The per-device table of error words (common.cuh).
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+static int* g_error_words[64] = {};
+static std::mutex g_error_mutex;
+static const char* const kErrorWordNames[SIB_ERROR_WORDS] = {
+    "gemm_tcgen05", "attention_prefill_tc", "", "", "", "", "", ""};
+
+static int* error_table() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        sib_set_error("no current CUDA device for the table of error words");
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> guard(g_error_mutex);
+    if (!g_error_words[dev]) {
+        int* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, SIB_ERROR_WORDS * sizeof(int));
+        if (e != cudaSuccess) {
+            sib_set_error("table of error words: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cudaMemset(p, 0, SIB_ERROR_WORDS * sizeof(int));
+        g_error_words[dev] = p;
+    }
+    return g_error_words[dev];
+}
+
+int* sib_error_word(int word) {
+    int* t = (word >= 0 && word < SIB_ERROR_WORDS) ? error_table() : nullptr;
+    return t ? t + word : nullptr;
+}
+
+SIB_EXPORT int sib_error_words() { return SIB_ERROR_WORDS; }
+
+SIB_EXPORT const char* sib_error_word_name(int word) {
+    return (word >= 0 && word < SIB_ERROR_WORDS) ? kErrorWordNames[word] : "";
+}
+
+// Copy the table to `host` (SIB_ERROR_WORDS ints, pinned for the copy to be asynchronous)
+// on `stream`: the words are valid once the stream has reached this point.
+SIB_EXPORT int sib_kernel_errors_fetch(int* host, void* stream) {
+    int* t = error_table();
+    if (!t) return -1;
+    cudaError_t e = cudaMemcpyAsync(host, t, SIB_ERROR_WORDS * sizeof(int), cudaMemcpyDeviceToHost,
+                                    (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        sib_set_error("fetching the error words: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// Set one word (0 clears it).  The kernels set their words themselves; the host sets one
+// to clear it after a report, and tests set one to stand for a failure.
+SIB_EXPORT int sib_kernel_error_set(int word, int code, void* stream) {
+    int* w = sib_error_word(word);
+    if (!w) return -1;
+    // (a 4-byte pattern needs the 32-bit memset of the driver API; codes fit a byte)
+    SIB_REQUIRE(code >= 0 && code < 256, "error codes are 0..255, got %d", code);
+    cudaError_t e = cudaMemsetAsync(w, 0, sizeof(int), (cudaStream_t)stream);
+    if (e == cudaSuccess && code) e = cudaMemsetAsync(w, code, 1, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        sib_set_error("setting an error word: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// One word, read with a synchronous copy (tests, and after a failure).
+static int error_word_now(int word, int clear) {
+    int* w = sib_error_word(word);
+    if (!w) return 0;
+    int v = 0;
+    cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost);
+    if (clear && v) cudaMemset(w, 0, sizeof(int));
+    return v;
+}
+
+// 0, or the code a block of gemm_tcgen05 left when one of its waits ran out (1: a stage
+// never became free, 2: a load never arrived, 3: the accumulator never became ready).
+SIB_EXPORT int sib_gemm_tcgen05_error(int clear) { return error_word_now(SIB_ERR_GEMM_TCGEN05, clear); }
+
+SIB_EXPORT int sib_attention_prefill_tc_error(int clear) {
+    return error_word_now(SIB_ERR_ATTENTION_PREFILL_TC, clear);
+}

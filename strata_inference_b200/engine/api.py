@@ -65,12 +65,12 @@ class EngineStepper:
         self.engine.last_logits = logits
         toks = self.engine.sample(logits, slots, sampling.temperature, sampling.top_k,
                                   sampling.top_p)
-        return toks.tolist()
+        return self.engine.read_back(toks)
 
     def decode(self, slots, tokens, sampling: SamplingConfig) -> List[int]:
         out = self.engine.decode_step(slots, tokens, sampling.temperature, sampling.top_k,
                                       sampling.top_p, use_graph=self.use_graph)
-        return out.tolist()
+        return self.engine.read_back(out)
 
 
 class GenerationEngine:

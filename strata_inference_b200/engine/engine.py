@@ -67,6 +67,7 @@ class Engine:
         self.vocab_size = spec.vocab_size
         # one xorshift64 state per slot, for the sampling kernel
         self.rng_state = torch.ones(self.cache.max_slots, dtype=torch.int64, device=self.device)
+        self.kernel_watch = native.KernelWatch()
         self._graphs: Dict[Tuple, "DecodeGraph"] = {}
         self.max_graphs = 8     # captured steps kept (by batch size and sampling options)
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
@@ -211,6 +212,15 @@ class Engine:
         self._graphs[key] = g       # most recently used last
         out = g.run(slots, tokens, use_graph)
         self.last_logits = g.last_logits
+        return out
+
+    def read_back(self, t: torch.Tensor):
+        """``t`` on the host (a list for integer tensors, else a tensor), and a check that
+        no kernel of the steps so far gave up on a bounded wait: the error words ride on
+        the same stream and the same synchronisation as the copy of ``t``."""
+        self.kernel_watch.fetch()
+        out = t.tolist() if not t.dtype.is_floating_point else t.cpu()
+        self.kernel_watch.check()
         return out
 
     def memory_report(self) -> dict:

@@ -486,3 +486,51 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
                                      c_float(top_p), _ptr(rng_state), _ptr(rng_index), _ptr(out),
                                      _stream()))
     return out
+
+
+class KernelWatch:
+    """The verdicts of kernels whose waits are bounded, brought to the host without a
+    synchronisation of their own.
+
+    ``fetch()`` enqueues an asynchronous copy of the device's error words into a pinned
+    buffer on the current stream; after the caller's next synchronisation of that stream
+    (the read of the sampled tokens, the copy of the logits) ``check()`` looks at the
+    buffer and raises :class:`KernelError` naming the kernel and its code if a wait ran
+    out, after clearing the word.  The reference logs a failed launch and goes on
+    (src/backend/cuda/mod.rs:379-397)."""
+
+    def __init__(self):
+        lib = library()
+        lib.sib_error_word_name.restype = ctypes.c_char_p
+        self.n = int(lib.sib_error_words())
+        self.host = torch.zeros(self.n, dtype=torch.int32).pin_memory()
+        self.names = [lib.sib_error_word_name(c_int(i)).decode() for i in range(self.n)]
+        self.pending = False
+
+    def fetch(self) -> None:
+        if library().sib_kernel_errors_fetch(c_void_p(self.host.data_ptr()), _stream()) != 0:
+            raise KernelError(library().sib_last_error().decode())
+        self.pending = True
+
+    def check(self) -> None:
+        """Call after the stream that ``fetch`` ran on has been synchronised."""
+        if not self.pending:
+            return
+        self.pending = False
+        words = self.host.tolist()
+        bad = [(i, c) for i, c in enumerate(words) if c]
+        if not bad:
+            return
+        for i, _ in bad:
+            set_kernel_error(i, 0)
+        self.host.zero_()
+        raise KernelError("; ".join(
+            f"a bounded wait of {self.names[i] or 'kernel %d' % i} ran out (code {c}): "
+            f"its output is incomplete" for i, c in bad))
+
+
+def set_kernel_error(word: int, code: int) -> None:
+    """Set a device error word from the host (0 clears it; tests use it to stand for a
+    kernel that gave up)."""
+    if library().sib_kernel_error_set(c_int(word), c_int(code), _stream()) != 0:
+        raise KernelError(library().sib_last_error().decode())

@@ -347,3 +347,157 @@ def test_a_batch_of_twenty(model_dirs, name, dtype):
     for s in slots:
         eng.end_sequence(s)
     assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page,room", [("A", 4, 40), ("B", 8, 12), ("C", 16, 100)])
+def test_prompts_continued_in_pieces_larger_than_a_page(model_dirs, name, page, room, dtype):
+    """A cache built with room for long continuing steps (`max_continuation`): prompts are
+    fed in pieces much larger than a page and than the window, across the ring's end, and a
+    piece beyond the room is refused with the figure in the message."""
+    from strata_inference_b200 import Engine
+    from strata_inference_b200.engine.engine import StepError
+    cfg = CONFIGS[name]
+    eng = Engine.from_dir(model_dirs[name, dtype], dtype=dtype, max_tokens=1024, page_tokens=page,
+                          max_continuation=room)
+    ring = [g for g in eng.cache.groups if g.need.window][0]
+    assert ring.ring_tokens > 0, "the window's group must be a ring for this test to mean anything"
+    most = eng.cache.max_step_tokens()
+    assert room <= most < room + page
+    top = cfg["max_position_embeddings"]
+    a, b = random_prompts(cfg, [top - 1, top - 7], seed=16)
+    ref_a = plain_logits(a, model_dirs[name, dtype], cfg)
+    ref_b = plain_logits(b, model_dirs[name, dtype], cfg)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    first = (3, 11)
+    out = eng.step([(sa, a[:first[0]]), (sb, b[:first[1]])],
+                   want=[list(range(first[0])), list(range(first[1]))])
+    got_a, got_b = [out[:first[0]]], [out[first[0]:]]
+    pa, pb = first
+    refused = False
+    while pa < len(a) or pb < len(b):
+        if not refused and pa + most + 1 > ring.ring_tokens and pa + most + 1 <= len(a):
+            # one position more than the room, where it would wrap around the ring
+            with pytest.raises(StepError, match=f"at most {most} "):
+                eng.step([(sa, a[pa:pa + most + 1])])
+            assert eng.length(sa) == pa
+            refused = True
+        na, nb = min(most, len(a) - pa), min(max(1, most - 5), len(b) - pb)
+        entries = [(s, t[p:p + n]) for s, t, p, n in ((sa, a, pa, na), (sb, b, pb, nb)) if n]
+        out = eng.step(entries, want=[list(range(len(t))) for _, t in entries])
+        if na:
+            got_a.append(out[:na])
+        if nb:
+            got_b.append(out[na:na + nb])
+        pa, pb = pa + na, pb + nb
+    eng.end_sequence(sa)
+    eng.end_sequence(sb)
+    assert refused
+    assert_logits_close(torch.cat(got_a), ref_a, dtype, f"{name} request a in long pieces")
+    assert_logits_close(torch.cat(got_b), ref_b, dtype, f"{name} request b in long pieces")
+    assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16)])
+def test_a_new_prompt_beside_sequences_that_go_on(model_dirs, name, page, dtype):
+    """A mixed step: one sequence starts (its whole prompt, from position 0, longer than the
+    window) in the step in which two others go on by one token and by several.  The new
+    sequence's rows then attend over the cache like any other continuing rows."""
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, page)
+    a, b, c = random_prompts(cfg, [50, 44, 58], seed=17)
+    refs = [plain_logits(t, model_dirs[name, dtype], cfg) for t in (a, b, c)]
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    eng.step([(sa, a[:30]), (sb, b[:21])])
+    most = eng.cache.max_step_tokens()
+    few = min(3, most)
+    sc = eng.new_sequence()
+    n_c = min(40, eng.cache.max_step_tokens(0))       # a prompt may fill the ring once
+    got = eng.step([(sa, a[30:31]), (sc, c[:n_c]), (sb, b[21:21 + few])],
+                   want=[[0], list(range(n_c)), list(range(few))])
+    ref = torch.cat([refs[0][30:31], refs[2][:n_c], refs[1][21:21 + few]])
+    assert_logits_close(got, ref, dtype, f"{name} mixed step")
+    # all three go on by one token: the new sequence's cache is as good as the others'
+    pa, pb, pc = 31, 21 + few, n_c
+    for k in range(6):
+        got = eng.step([(sa, [a[pa + k]]), (sb, [b[pb + k]]), (sc, [c[pc + k]])])
+        ref = torch.stack([refs[0][pa + k], refs[1][pb + k], refs[2][pc + k]])
+        assert_logits_close(got, ref, dtype, f"{name} after the mixed step, token {k}")
+    for s in (sa, sb, sc):
+        eng.end_sequence(s)
+    assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_failed_step_leaves_the_cache_as_it_was(model_dirs, dtype):
+    """A step whose forward pass raises gives back the pages it reserved and advances
+    nothing; the same slot then runs the same tokens as a fresh engine would."""
+    name, cfg = "B", CONFIGS["B"]
+    eng = _engine(model_dirs, name, dtype, 8)
+    toks = random_prompts(cfg, [40], seed=18)[0]
+    ref = plain_logits(toks, model_dirs[name, dtype], cfg)
+    s = eng.new_sequence()
+    eng.step([(s, toks[:10])])
+    held = eng.cache.pages_in_use()
+    first_block = eng.model.blocks[0]
+    real = first_block.forward
+
+    def broken(*a, **kw):
+        raise RuntimeError("made to fail")
+    first_block.forward = broken
+    with pytest.raises(RuntimeError, match="made to fail"):
+        eng.step([(s, toks[10:19])])
+    with pytest.raises(RuntimeError, match="made to fail"):
+        eng.decode_step([s], [toks[10]])
+    first_block.forward = real
+    assert eng.cache.pages_in_use() == held and eng.length(s) == 10
+    got = [eng.step([(s, toks[10:14])], want=[list(range(4))])]
+    for t in toks[14:]:
+        got.append(eng.step([(s, [t])]))
+    eng.end_sequence(s)
+    assert_logits_close(torch.cat(got), ref[10:], dtype, "after a failed step")
+    assert eng.cache.pages_in_use() == 0
+
+
+def test_a_kernel_that_gave_up_is_reported_and_the_slots_come_back(model_dirs):
+    """The bounded waits of the tcgen05 kernels leave a code in a device word when they run
+    out.  Here the word is set from the host (nothing is made to stall): the generation
+    loop learns of it where it reads the sampled tokens, raises, and frees its slots."""
+    from strata_inference_b200 import GenerationConfig, GenerationEngine
+    from strata_inference_b200.kernels import native
+    name = "A"
+    gen = GenerationEngine.from_dir(model_dirs[name, "bfloat16"], dtype="bfloat16", max_tokens=512)
+    prompts = random_prompts(CONFIGS[name], [9, 4], seed=19)
+    want = [o.token_ids for o in gen.generate(prompts, GenerationConfig(max_tokens=6))]
+    native.set_kernel_error(1, 2)              # "attention_prefill_tc: a load never arrived"
+    with pytest.raises(native.KernelError, match="attention_prefill_tc.*code 2"):
+        gen.generate(prompts, GenerationConfig(max_tokens=6))
+    cache = gen.engine.cache
+    assert cache.n_free_slots == cache.max_slots and cache.pages_in_use() == 0
+    # the word was cleared with the report: the engine works again
+    assert [o.token_ids for o in gen.generate(prompts, GenerationConfig(max_tokens=6))] == want
+    native.set_kernel_error(0, 3)              # during decoding: found at the next token read
+    seen = []
+
+    def on_token(i, t):
+        seen.append(t)
+        if len(seen) == 4:
+            native.set_kernel_error(0, 3)
+        return True
+    native.set_kernel_error(0, 0)
+    with pytest.raises(native.KernelError, match="gemm_tcgen05.*code 3"):
+        gen.generate(prompts, GenerationConfig(max_tokens=6), on_token)
+    assert cache.n_free_slots == cache.max_slots and cache.pages_in_use() == 0
+
+
+def test_captured_steps_are_kept_for_a_few_batch_sizes_only(model_dirs):
+    name, cfg = "A", CONFIGS["A"]
+    eng = _engine(model_dirs, name, "bfloat16", 16, max_tokens=4096)
+    eng.max_graphs = 3
+    slots = [eng.new_sequence() for _ in range(6)]
+    eng.step([(s, [3, 4, 5]) for s in slots])
+    for n in (6, 5, 4, 3, 2, 6):
+        for _ in range(3):
+            eng.decode_step(slots[:n], [7] * n)
+    assert len(eng._graphs) == 3 and [k[0] for k in eng._graphs] == [3, 2, 6]
