@@ -85,14 +85,16 @@ class Engine:
 
     @classmethod
     def from_random(cls, config: Mapping, seed: int, dtype="bfloat16", matrix_std: float = None,
-                    norm_std: float = None, **kw) -> "Engine":
+                    norm_std: float = None, store=None, **kw) -> "Engine":
         """Seeded random weights drawn on the device straight into the weight buffer (no
-        files, no host copy): the model ``write_random_model(dir, config, seed, dtype)``
-        writes, tensor for tensor and bit for bit."""
+        files, no host copy): the model ``write_random_model(dir, config, seed, store)``
+        writes, tensor for tensor and bit for bit.  ``store`` is the type the folder would
+        hold (default: the compute type); bfloat16 weights run in 32-bit are the check path
+        of a bfloat16 model."""
         from ..weights import random_init
         _, spec = spec_from_config(config)
         native.require_device(torch.device(kw.get("device", "cuda:0")))
-        source = RandomSource(expected_tensors(spec), seed, parse_dtype(dtype),
+        source = RandomSource(expected_tensors(spec), seed, parse_dtype(store or dtype),
                               random_init.MATRIX_STD if matrix_std is None else matrix_std,
                               random_init.NORM_STD if norm_std is None else norm_std)
         return cls(spec, source, dtype, **kw)

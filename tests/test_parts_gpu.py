@@ -561,3 +561,137 @@ def test_toy_routed_feed_forward_beside_the_dense_one(tmp_path):
     _close(got, ref_a[17:], torch.float32, "routed tail")
     eng.end_sequence(sa)
     assert eng.cache.pages_in_use() == 0
+
+
+# ---------------------------------------------------------------- a toy mixer in captured steps
+
+class CapturableRunningMean(RunningMeanMixer):
+    """The running-mean mixer with its single-token steps written for capture: the slots
+    come from the device tensor ``ctx.seq_slot``, nothing of a step is read on the host."""
+
+    def forward(self, x, ctx, entry, cache_entry, owns_cache):
+        if ctx.max_count > 1:
+            return super().forward(x, ctx, entry, cache_entry, owns_cache)
+        state = ctx.state(cache_entry)
+        idx = ctx.seq_slot.long()                    # row b belongs to sequence b
+        sums = state[idx, :-1] + x.float()
+        counts = state[idx, -1] + 1.0
+        if owns_cache:
+            state.index_copy_(0, idx, torch.cat([sums, counts[:, None]], dim=1))
+        return ((sums / counts[:, None]) @ self.w.t()).to(x.dtype)
+
+
+def test_toy_mixer_with_state_in_captured_steps_with_changing_slots(tmp_path):
+    """Single-token steps replayed from a CUDA graph while the set of slots changes between
+    replays: a mixer that indexes its state on the device follows; one that reads the
+    step's slots on the host is stopped when the step is first run for capture."""
+    from strata_inference_b200 import Engine, register_architecture, write_random_model
+    from strata_inference_b200.parts import register_mixer
+    from strata_inference_b200.parts.base import CapturedStepError
+    from safetensors.torch import load_file
+    register_architecture("ToyRunningMean", dict, _toy_spec)
+    config = {"architectures": ["ToyRunningMean"], "hidden_size": 40, "inter": 56, "vocab": 90,
+              "layers": 2, "eps": 1e-5, "max_pos": 64}
+    d = write_random_model(str(tmp_path / "toy"), config, seed=3, dtype=torch.float32,
+                           matrix_std=0.2, norm_std=0.5)
+    W = {k: v.double() for k, v in load_file(d + "/model.safetensors").items()}
+    g = torch.Generator().manual_seed(4)
+    reqs = [torch.randint(0, 90, (n,), generator=g).tolist() for n in (30, 22, 26, 19)]
+    refs = [_toy_plain(r, W, config) for r in reqs]
+
+    register_mixer("running_mean", RunningMeanMixer)          # loops over ctx.slots on the host
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=256)
+    s = eng.new_sequence()
+    eng.step([(s, reqs[0][:5])])
+    eng.decode_step([s], [reqs[0][5]], use_graph=False)       # uncaptured steps may read the host
+    with pytest.raises(CapturedStepError, match="slots"):
+        eng.decode_step([s], [reqs[0][6]])
+    assert eng.length(s) == 6
+
+    register_mixer("running_mean", CapturableRunningMean)
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=256)
+    slots = [eng.new_sequence() for _ in range(3)]
+    pos = [7, 3, 5]
+    eng.step([(sl, r[:p]) for sl, r, p in zip(slots, reqs, pos)])
+    live = [0, 1, 2]                                          # request index per batch row
+    for k in range(12):
+        if k == 5:
+            # request 1 leaves; request 3 starts in its slot (zeroed state) and joins the
+            # same captured step, whose replays now see slots in another order
+            eng.end_sequence(slots[1])
+            new = eng.new_sequence()
+            assert new == slots[1]
+            eng.step([(new, reqs[3][:4])])
+            slots.append(new)
+            pos.append(4)
+            live = [3, 0, 2]
+        eng.decode_step([slots[i] for i in live], [reqs[i][pos[i]] for i in live])
+        ref = torch.stack([refs[i][pos[i]] for i in live])
+        _close(eng.last_logits, ref, torch.float32, f"captured toy step {k}")
+        for i in live:
+            pos[i] += 1
+    assert eng._graphs[(3, 0.0, 0, 1.0)].graph is not None    # the steps were replays
+
+
+# ---------------------------------------------------------------- a toy embedding with positions
+
+class LearnedPositionEmbedding:
+    """h = table[token] + positions[absolute position]: an embedding that needs the step's
+    positions, which it gets because embeddings are given the whole step context."""
+
+    @staticmethod
+    def tensors(params, hidden, vocab):
+        from strata_inference_b200.weights.loader import TensorDecl
+        return {"weight": TensorDecl((vocab, hidden)),
+                "positions.weight": TensorDecl((params["max_positions"], hidden))}
+
+    def __init__(self, params, hidden, vocab, weights, rt):
+        self.table = rt.cast_matrix(weights["weight"])        # (a tied head reads `table`)
+        self.positions = weights["positions.weight"].to(device=rt.device, dtype=torch.float32)
+
+    def forward(self, ctx):
+        return self.table[ctx.tokens.long()].float() + self.positions[ctx.row_pos.long()]
+
+
+def _learned_pos_spec(config):
+    from strata_inference_b200.config.spec import ModelSpec, PartSpec
+    spec = _toy_spec(config)
+    fields = dict(spec.__dict__)
+    fields["architecture"] = "ToyLearnedPositions"
+    fields["embedding"] = PartSpec("learned_positions", {"max_positions": config["max_pos"]})
+    return ModelSpec(**fields)
+
+
+def test_toy_embedding_with_learned_positions(tmp_path):
+    from strata_inference_b200 import Engine, register_architecture, write_random_model
+    from strata_inference_b200.parts import register_embedding, register_mixer
+    from safetensors.torch import load_file
+    register_mixer("running_mean", CapturableRunningMean)
+    register_embedding("learned_positions", LearnedPositionEmbedding)
+    register_architecture("ToyLearnedPositions", dict, _learned_pos_spec)
+    config = {"architectures": ["ToyLearnedPositions"], "hidden_size": 40, "inter": 56,
+              "vocab": 90, "layers": 1, "eps": 1e-5, "max_pos": 48}
+    d = write_random_model(str(tmp_path / "toy"), config, seed=6, dtype=torch.float32,
+                           matrix_std=0.2, norm_std=0.5)
+    W = {k: v.double() for k, v in load_file(d + "/model.safetensors").items()}
+    assert W["embed.positions.weight"].shape == (48, 40)
+    toks = torch.randint(0, 90, (30,), generator=torch.Generator().manual_seed(7)).tolist()
+    # the plain toy model with the positions added to the embedded tokens
+    shifted = dict(W)
+    eps = config["eps"]
+    norm = lambda x, w: x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w  # noqa: E731
+    h = W["embed.weight"][torch.tensor(toks)] + W["embed.positions.weight"][:30]
+    n = norm(h, W["layers.0.norm1.weight"])
+    h = h + (torch.cumsum(n, 0) / torch.arange(1, 31)[:, None]) @ W["layers.0.mixer.mix.weight"].T
+    n = norm(h, W["layers.0.norm2.weight"])
+    h = h + plain.geglu_ffn(n, W["layers.0.ffn.gate_proj.weight"], W["layers.0.ffn.up_proj.weight"],
+                            W["layers.0.ffn.down_proj.weight"])
+    ref = norm(h, W["norm.weight"]) @ W["embed.weight"].T
+    del shifted
+    eng = Engine.from_dir(d, dtype="float32", max_tokens=128)
+    s = eng.new_sequence()
+    got = [eng.step([(s, toks[:12])], want=[list(range(12))])]
+    for t in toks[12:]:
+        eng.decode_step([s], [t])                 # captured from the second one on
+        got.append(eng.last_logits.clone())
+    _close(torch.cat(got), ref, torch.float32, "learned positions, prompt then captured steps")

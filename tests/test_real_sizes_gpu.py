@@ -115,3 +115,140 @@ def test_window_of_4096_at_real_sizes(tmp_path, dtype):
     eng.end_sequence(s)
     err = _rel(torch.cat(outs), ref[4098:])
     assert err <= REL_TOL[dtype], f"window of 4096, {dtype}: {err:.2e}"
+
+
+# ---------------------------------------------------------------- the whole Gemma2-2B shape
+
+CFG_2B_FULL = dict(CFG_2B, num_hidden_layers=26, sliding_window=4096, max_position_embeddings=8192)
+
+
+def _stored_on_device(cfg, seed):
+    """The stored tensors that `seed` names, drawn on the device (weights are inputs of the
+    plain implementation; the generator is checked against its host formula elsewhere)."""
+    from strata_inference_b200.config.registry import spec_from_config
+    from strata_inference_b200.engine.model import expected_tensors
+    from strata_inference_b200.weights.random_init import random_tensors
+    _, spec = spec_from_config(cfg)
+    return random_tensors(expected_tensors(spec), seed, torch.bfloat16, "cuda:0")
+
+
+@pytest.fixture(scope="module")
+def full_2b():
+    cfg = CFG_2B_FULL
+    reqs = random_prompts(cfg, [320, 70, 200, 45, 130, 90], seed=28)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    with torch.no_grad(), torch.device("cuda"):
+        W = {k: v.float() for k, v in _stored_on_device(cfg, 5).items()}
+        refs = [plain.forward(t, W, cfg, dtype=torch.float32).cpu() for t in reqs]
+    del W
+    torch.cuda.empty_cache()
+    return cfg, reqs, refs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_all_26_layers_of_the_2b_shape(full_2b, dtype):
+    """Gemma2-2B's configuration at full depth (26 layers, vocabulary 256 000, window 4 096,
+    context 8 192), the model that seed 5 names: a request whole with every position wanted;
+    its last 32 tokens one by one; an unequal batch whose shortest request leaves first; a
+    second batch on the slots that the first gave back."""
+    from strata_inference_b200 import Engine
+    cfg, reqs, refs = full_2b
+    tol = REL_TOL[dtype]
+    eng = Engine.from_random(cfg, 5, dtype=dtype, store="bfloat16", max_tokens=2048, max_slots=4)
+    assert len(eng.model.blocks) == 26 and sum(len(g.entries) for g in eng.cache.groups) == 26
+    s = eng.new_sequence()
+    got = eng.step([(s, reqs[0])], want=[list(range(len(reqs[0])))])
+    eng.end_sequence(s)
+    assert _rel(got, refs[0]) <= tol, f"whole request: {_rel(got, refs[0]):.2e}"
+    s = eng.new_sequence()
+    cut = len(reqs[0]) - 32
+    outs = [eng.step([(s, reqs[0][:cut])])]
+    for t in reqs[0][cut:]:
+        outs.append(eng.step([(s, [t])]))
+    eng.end_sequence(s)
+    err = _rel(torch.cat(outs), refs[0][cut - 1:])
+    assert err <= tol, f"last 32 one by one: {err:.2e}"
+
+    def batch(which, prompt, steps, tag):
+        slots = [eng.new_sequence() for _ in which]
+        got = eng.step([(sl, reqs[i][:p]) for sl, i, p in zip(slots, which, prompt)])
+        ref = torch.stack([refs[i][p - 1] for i, p in zip(which, prompt)])
+        assert _rel(got, ref) <= tol, f"{tag} prompts: {_rel(got, ref):.2e}"
+        live = list(range(len(which)))
+        for k in range(steps):
+            for j in list(live):
+                if prompt[j] + k >= len(reqs[which[j]]):        # used up: it leaves
+                    eng.end_sequence(slots[j])
+                    live.remove(j)
+            got = eng.step([(slots[j], [reqs[which[j]][prompt[j] + k]]) for j in live])
+            ref = torch.stack([refs[which[j]][prompt[j] + k] for j in live])
+            assert _rel(got, ref) <= tol, f"{tag} step {k}: {_rel(got, ref):.2e}"
+        for j in live:
+            eng.end_sequence(slots[j])
+        return slots
+    first = batch([0, 1, 2, 3], [300, 60, 150, 40], 12, "batch 1")     # request 3 leaves after 5
+    assert eng.cache.pages_in_use() == 0
+    second = batch([4, 5, 1], [100, 85, 30], 8, "batch 2")             # request 5 leaves after 5
+    assert set(second) <= set(first) and eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_twenty_requests_at_2b_sizes(dtype):
+    """Two layers at Gemma2-2B sizes: 20 prompts of 100 to 1 600 tokens in one step, then six
+    single-token steps through the captured step (more rows than the weight-streaming
+    kernels take, prompts across several blocks of the prompt-attention kernel)."""
+    from strata_inference_b200 import Engine
+    cfg = dict(CFG_2B, vocab_size=32000, sliding_window=512, max_position_embeddings=2048)
+    g = torch.Generator().manual_seed(31)
+    lens = [100] + torch.randint(100, 1601, (18,), generator=g).tolist() + [1600]
+    reqs = random_prompts(cfg, [n + 6 for n in lens], seed=32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    with torch.no_grad(), torch.device("cuda"):
+        W = {k: v.float() for k, v in _stored_on_device(cfg, 33).items()}
+        refs = [plain.forward(t, W, cfg, dtype=torch.float32)[n - 1:].cpu()
+                for t, n in zip(reqs, lens)]
+    del W
+    eng = Engine.from_random(cfg, 33, dtype=dtype, store="bfloat16",
+                             max_tokens=sum(lens) + 64 * 21 + 256)
+    slots = [eng.new_sequence() for _ in reqs]
+    got = eng.step([(s, r[:n]) for s, r, n in zip(slots, reqs, lens)])
+    tol = REL_TOL[dtype]
+    err = _rel(got, torch.stack([f[0] for f in refs]))
+    assert err <= tol, f"20 prompts: {err:.2e}"
+    for k in range(6):
+        eng.decode_step(slots, [r[n + k] for r, n in zip(reqs, lens)])
+        err = _rel(eng.last_logits, torch.stack([f[k + 1] for f in refs]))
+        assert err <= tol, f"20 sequences, captured step {k}: {err:.2e}"
+    for s in slots:
+        eng.end_sequence(s)
+    assert eng.cache.pages_in_use() == 0
+
+
+def test_eight_prompts_of_128_to_4096_at_9b_sizes():
+    """Two layers at Gemma2-9B sizes (hidden 3584, 16 heads of 256 in 8 groups, intermediate
+    14 336, window 4 096) in bfloat16: an unequal batch of 8 prompts of 128 to 4 096 tokens
+    in one step, then four tokens each."""
+    from strata_inference_b200 import Engine
+    cfg = dict(CFG_2B, hidden_size=3584, num_attention_heads=16, num_key_value_heads=8,
+               head_dim=256, intermediate_size=14336, vocab_size=32000, sliding_window=4096,
+               max_position_embeddings=8192)
+    lens = [128, 4096, 700, 2048, 333, 4000, 1500, 129]
+    reqs = random_prompts(cfg, [n + 4 for n in lens], seed=41)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    with torch.no_grad(), torch.device("cuda"):
+        W = {k: v.float() for k, v in _stored_on_device(cfg, 6).items()}
+        refs = [plain.forward(t, W, cfg, dtype=torch.float32)[n - 1:].cpu()
+                for t, n in zip(reqs, lens)]
+    del W
+    eng = Engine.from_random(cfg, 6, dtype="bfloat16", max_tokens=sum(lens) + 64 * 10)
+    slots = [eng.new_sequence() for _ in reqs]
+    got = eng.step([(s, r[:n]) for s, r, n in zip(slots, reqs, lens)])
+    tol = REL_TOL["bfloat16"]
+    err = _rel(got, torch.stack([f[0] for f in refs]))
+    assert err <= tol, f"8 prompts: {err:.2e}"
+    for k in range(4):
+        eng.decode_step(slots, [r[n + k] for r, n in zip(reqs, lens)])
+        err = _rel(eng.last_logits, torch.stack([f[k + 1] for f in refs]))
+        assert err <= tol, f"8 sequences, step {k}: {err:.2e}"
+    for s in slots:
+        eng.end_sequence(s)
