@@ -7,16 +7,18 @@ Prints ONE JSON line.  The run: Gemma2-2B's layer sizes with random bfloat16
 weights, a batch of 8 sequences that each hold close to the 8,192-token
 context; a "step" is one decode step (one new token per sequence).
 
-* ``value``: decoded tokens per second, K steps timed on the device with CUDA
-  events around the replayed step graphs (tokens are fed from the host each
-  step; the result is not read back).
+* ``value``: decoded tokens per second: five blocks of K steps each are timed on the
+  device with CUDA events around the replayed step graphs (tokens are fed from the
+  host each step; the result is not read back); the median block counts, the
+  fastest and slowest are reported as ``spread_ms``.
 * ``e2e``: the same through the Python entry point ``GenerationEngine.generate``:
   host token lists in, host token lists out, wall clock over the decode steps.
 * ``prefill``: one 2,048-token prompt through ``Engine.step``.
 * ``roofline``: bytes a decode step has to read (every weight once, the keys and
   values each live sequence's layers attend to) / its time / the measured copy
   bandwidth.
-* ``points``: decoded tokens per second at batch 1 and 64.
+* ``points``: decoded tokens per second at batch 1 and 64, and at batch 8 of the
+  Gemma2-9B and Gemma2-27B shapes at full depth (same context) when they fit.
 
 Between timed steps nothing flushes L2: each step reads 5 GB of weights and more
 of cache, against 126 MB of L2.
@@ -158,30 +160,41 @@ def kv_bytes_per_step(engine, lengths):
     return total
 
 
-def time_decode(engine, batch, context, steps, warmup):
-    """ms per decode step (device time) for ``batch`` sequences near ``context`` positions."""
+BLOCKS = 5      # timed blocks of K steps; the median block is the number
+
+
+def time_decode(engine, batch, context, steps, warmup, blocks=BLOCKS):
+    """ms per decode step (device time; median, fastest and slowest block of ``steps``) for
+    ``batch`` sequences near ``context`` positions."""
     import torch
-    start_len = context - (steps + warmup + 2)
+    total = blocks * steps + warmup + 2
+    start_len = context - total
     slots = [engine.new_sequence() for _ in range(batch)]
     fill_context(engine, slots, start_len)
     g = torch.Generator().manual_seed(3)
-    toks = torch.randint(0, engine.vocab_size, (steps + warmup + 2, batch), generator=g).tolist()
+    toks = torch.randint(0, engine.vocab_size, (total, batch), generator=g).tolist()
     for i in range(warmup + 2):            # eager, capture, then replays
         engine.decode_step(slots, toks[i])
     torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for i in range(steps):
-        engine.decode_step(slots, toks[warmup + 2 + i])
-    end.record()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
+    marks[0].record()
+    at = warmup + 2
+    for b in range(blocks):
+        for i in range(steps):
+            engine.decode_step(slots, toks[at + i])
+        at += steps
+        marks[b + 1].record()
     torch.cuda.synchronize()
-    ms = begin.elapsed_time(end) / steps
+    engine.kernel_watch.fetch()
+    torch.cuda.synchronize()
+    engine.kernel_watch.check()            # a kernel that gave up would make the number void
+    per_step = sorted(marks[b].elapsed_time(marks[b + 1]) / steps for b in range(blocks))
     lengths = [engine.length(s) for s in slots]
     graph = engine._graphs[(batch, 0.0, 0, 1.0)]
     launches = graph.launches_per_step
     for s in slots:
         engine.end_sequence(s)
-    return ms, lengths, launches
+    return per_step[len(per_step) // 2], lengths, launches, (per_step[0], per_step[-1])
 
 
 def time_prefill(engine, n_tokens, reps=5):
@@ -200,6 +213,9 @@ def time_prefill(engine, n_tokens, reps=5):
         if i >= 2:
             times.append(begin.elapsed_time(end))
         engine.end_sequence(slot)
+    engine.kernel_watch.fetch()
+    torch.cuda.synchronize()
+    engine.kernel_watch.check()
     return statistics.median(times)
 
 
@@ -242,7 +258,8 @@ def run_ours(args):
     weight_bytes = engine.model.weight_bytes()
 
     with ClockSampler() as clocks:
-        ms, lengths, launches = time_decode(engine, batch, context, args.steps, args.warmup)
+        ms, lengths, launches, spread = time_decode(engine, batch, context, args.steps,
+                                                    args.warmup)
     value = batch * 1e3 / ms
     step_bytes = weight_bytes + kv_bytes_per_step(engine, lengths)
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -250,7 +267,7 @@ def run_ours(args):
     points = {}
     if point_batches:
         for b in point_batches:
-            pms, _, _ = time_decode(engine, b, context, max(8, args.steps // 2), args.warmup)
+            pms, _, _, _ = time_decode(engine, b, context, max(8, args.steps // 2), args.warmup, 3)
             points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
 
     T = 2048
@@ -263,7 +280,7 @@ def run_ours(args):
     # (the steps right after the 8 x 8 000-token prefill run at the clocks that prefill left:
     # 32 of them are let pass before the timed ones)
     e2e_warmup = max(args.warmup, 32)
-    n_new = args.steps + e2e_warmup
+    n_new = BLOCKS * args.steps + e2e_warmup
     g = torch.Generator().manual_seed(6)
     prompts = [torch.randint(0, engine.vocab_size, (context - n_new - 2,), generator=g).tolist()
                for _ in range(batch)]
@@ -279,9 +296,39 @@ def run_ours(args):
     timed_tokens = sum(len(o.token_ids) for o in outs) - batch * e2e_warmup
     e2e_value = timed_tokens / (t_end - stamps[e2e_warmup - 1])
 
+    # the other two shapes of the same architecture at full depth, batch 8, same context
+    other = {}
+    if point_batches and args.shape == "2b" and not args.layers:
+        del gen, engine, outs
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for shape in ("9b", "27b"):
+            ocfg = baseline_config()
+            ocfg.update(SHAPES[shape])
+            need = 2 * (ocfg["vocab_size"] * ocfg["hidden_size"] + ocfg["num_hidden_layers"] * (
+                ocfg["hidden_size"] * (2 * ocfg["num_attention_heads"]
+                                       + 2 * ocfg["num_key_value_heads"]) * ocfg["head_dim"]
+                + 3 * ocfg["hidden_size"] * ocfg["intermediate_size"])) \
+                + 8 * kv_bytes_per_sequence(ocfg, context)
+            if need > 150e9:
+                continue
+            oeng = GenerationEngine.from_random(ocfg, seed=6 if shape == "9b" else 7,
+                                                dtype="bfloat16", ctx=context,
+                                                max_tokens=8 * context, max_slots=8).engine
+            randomize_pools(oeng)
+            oms, olen, _, _ = time_decode(oeng, 8, context, max(8, args.steps // 2), args.warmup, 3)
+            obytes = oeng.model.weight_bytes() + kv_bytes_per_step(oeng, olen)
+            points[f"decode_b8_{shape}"] = round(8 * 1e3 / oms, 1)
+            other[shape] = round(obytes / (oms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            del oeng
+            gc.collect()
+            torch.cuda.empty_cache()
+
     line = {
         "metric": METRIC.replace("2B", args.shape.upper()), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "timed_blocks": BLOCKS, "spread_ms": [round(spread[0], 4), round(spread[1], 4)],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
         "impl": "ours",
@@ -303,6 +350,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
+        "roofline_other_shapes": other,
         "clocks": clocks.summary(),
     }
     print(json.dumps(line))

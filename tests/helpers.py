@@ -114,3 +114,18 @@ def assert_logits_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: 
     assert err <= REL_TOL[dtype] * scale, (
         f"{what}: max |diff| {err:.3e} exceeds {REL_TOL[dtype]:.0e} x max|ref| {scale:.3e} "
         f"(first bad row {int(((got - ref).abs().amax(dim=-1) > REL_TOL[dtype] * scale).nonzero()[0])})")
+
+
+def assert_greedy_choices_close(prompt: Sequence[int], tokens: Sequence[int], weights, cfg: dict,
+                                dtype: str, what: str = "") -> None:
+    """Greedy tokens of a reduced-precision run cannot be compared token for token with the
+    plain implementation's (one near-tie sends the two apart), but each choice can: given
+    the run's own history, the chosen token's plain logit must lie within rounding of the
+    plain maximum at that position.  A wrong but stable token fails this."""
+    logits = plain.forward(list(prompt) + list(tokens), weights, cfg, dtype=torch.float64)
+    for k, tok in enumerate(tokens):
+        row = logits[len(prompt) + k - 1]
+        gap = (row.max() - row[tok]).item()
+        assert gap <= 2 * REL_TOL[dtype] * row.abs().max().item(), (
+            f"{what}: token {k} ({tok}) lies {gap:.3e} below the best logit "
+            f"({int(row.argmax())}, {row.max().item():.3e})")

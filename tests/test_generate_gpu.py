@@ -84,7 +84,8 @@ def test_stop_tokens_context_end_and_batches_one_after_another(model_dirs):
     assert eng.engine.cache.pages_in_use() == 0
 
 
-def test_bfloat16_generation_runs_and_is_deterministic(model_dirs):
+def test_bfloat16_generation_is_deterministic_and_every_choice_is_near_the_plain_best(model_dirs):
+    from helpers import assert_greedy_choices_close
     from strata_inference_b200 import GenerationConfig, GenerationEngine
     cfg = CONFIGS["C"]
     prompts = random_prompts(cfg, [33, 4, 70], seed=6)
@@ -95,6 +96,9 @@ def test_bfloat16_generation_runs_and_is_deterministic(model_dirs):
         first = next((i for i, (u, v) in enumerate(zip(x.token_ids, y.token_ids)) if u != v), None)
         assert x.token_ids == y.token_ids, f"request {r}: the two runs differ from token {first} on"
     assert all(len(o.token_ids) == 40 for o in a)
+    W = plain_weights(model_dirs["C"])
+    for r, (p, o) in enumerate(zip(prompts, a)):
+        assert_greedy_choices_close(p, o.token_ids, W, cfg, "bfloat16", f"request {r}")
 
 
 def test_command_line_json(model_dirs):
