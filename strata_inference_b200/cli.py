@@ -54,7 +54,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--backend", default="auto", help="compute backend: auto, cuda")
     ap.add_argument("--log-disable", action="store_true", help="suppress all logging")
     ap.add_argument("--profile", action="store_true",
-                    help="per-token times on standard error")
+                    help="per-token times, and per-kernel times of one prompt step and one "
+                         "single-token step, on standard error (also: STRATA_PROFILE=1)")
     ap.add_argument("-c", "--ctx", type=int, default=None,
                     help="context length override (lowers the maximum sequence length)")
     ap.add_argument("--dump-logits", default=None,
@@ -70,8 +71,33 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+def _print_kernel_tables(engine, prompt: List[int]) -> None:
+    """The first request's prompt as one step and one single-token step after it, run once
+    more with CUDA events around every kernel."""
+    from .engine.profile import (format_table, load_peaks, profile_decode_graph,
+                                 profile_step)
+    peaks = load_peaks()
+    slot = engine.new_sequence()
+    try:
+        for _ in range(2):                        # the first run pays one-time set-ups
+            rows, ms = profile_step(lambda: engine.step([(slot, prompt)]))
+            if _ == 0:
+                engine.end_sequence(slot)
+                slot = engine.new_sequence()
+        print(format_table(f"prompt step, {len(prompt)} tokens", rows, ms, peaks), file=sys.stderr)
+        if engine.length(slot) + 5 < engine.max_seq_len:
+            rows, ms = profile_decode_graph(engine, [slot], [prompt[-1]])
+            print(format_table(f"single-token step near position {engine.length(slot)} "
+                               f"(captured, events between the kernels)", rows, ms, peaks),
+                  file=sys.stderr)
+    finally:
+        engine.end_sequence(slot)
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     args = build_parser().parse_args(argv)
+    if os.environ.get("STRATA_PROFILE", "") not in ("", "0"):
+        args.profile = True
     given = [x is not None for x in (args.prompt, args.file, args.token_ids)]
     if sum(given) != 1:
         print("Error: give exactly one of --prompt, --file, --token-ids", file=sys.stderr)
@@ -99,7 +125,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             cfg_path = args.config or os.path.join(args.model, "config.json")
             with open(cfg_path) as f:
                 config = json.load(f)
-            write_random_model(args.model, config, args.random_weights, torch.bfloat16)
+            write_random_model(args.model, config, args.random_weights, torch.bfloat16,
+                               device="cuda:0" if torch.cuda.is_available() else "cpu")
             log(f"wrote random weights (seed {args.random_weights}) to {args.model}")
         need = args.cache_tokens
         if need is None:
@@ -138,6 +165,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         end = time.perf_counter()
         if dump is not None:
             dump.close()
+        if args.profile:
+            _print_kernel_tables(engine.engine, prompts[0])
     except Exception as e:  # one line, as the reference prints it
         print(f"Error: {e}", file=sys.stderr)
         return 1

@@ -11,8 +11,9 @@ sm_100, they raise.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 
@@ -104,7 +105,141 @@ def _want(t: torch.Tensor, dtype: torch.dtype, name: str, contiguous: bool = Tru
 
 
 # --------------------------------------------------------------------------
+# Per-kernel timing.  Inside ``with KernelProfile() as prof:`` every launcher of this
+# module (and whatever else is wrapped in ``prof.region``) is bracketed by CUDA events;
+# ``prof.rows()`` then gives, per kernel class, the calls, the device time and the bytes
+# and operations that the work needs by its shapes.  Outside such a block the wrappers
+# cost one comparison.  The reference's counterpart is a device synchronisation and a
+# wall-clock figure per layer (src/model/layer.rs:1265,1365-1375).
 
+_profile: Optional["KernelProfile"] = None
+
+
+class KernelProfile:
+    """``plan``: an earlier profile of the same launch sequence.  With a plan the events
+    are made for recording inside a CUDA graph (they are re-recorded by every replay) and
+    each launch takes its kernel class and work from the plan, in order, instead of
+    working them out (which may read device memory and cannot be done while capturing)."""
+
+    def __init__(self, plan: Optional["KernelProfile"] = None):
+        self.events: List[Tuple[str, torch.cuda.Event, torch.cuda.Event, float, float]] = []
+        self.plan = [(n, b, f) for n, _, _, b, f in plan.events] if plan is not None else None
+        self._next = 0
+
+    def __enter__(self) -> "KernelProfile":
+        global _profile
+        self._outer, _profile = _profile, self
+        return self
+
+    def __exit__(self, *exc) -> None:
+        global _profile
+        _profile = self._outer
+
+    def planned(self) -> Tuple[str, float, float]:
+        item = self.plan[self._next % len(self.plan)]
+        self._next += 1
+        return item
+
+    def region(self, name: str, nbytes: float, flops: float):
+        return _Region(self, name, nbytes, flops)
+
+    def rows(self, last: Optional[int] = None) -> List[Dict]:
+        """One row per kernel class, longest first (synchronises the device).  ``last``:
+        only the last so many launches (the ones a graph replays)."""
+        torch.cuda.synchronize()
+        table: Dict[str, Dict] = {}
+        for name, start, end, nbytes, flops in (self.events[-last:] if last else self.events):
+            r = table.setdefault(name, {"name": name, "calls": 0, "ms": 0.0, "bytes": 0.0,
+                                        "flops": 0.0})
+            r["calls"] += 1
+            r["ms"] += start.elapsed_time(end)
+            r["bytes"] += nbytes
+            r["flops"] += flops
+        return sorted(table.values(), key=lambda r: -r["ms"])
+
+
+class _Region:
+    def __init__(self, prof, name, nbytes, flops):
+        self.prof = prof
+        if prof.plan is not None:
+            name, nbytes, flops = prof.planned()
+        self.name, self.nbytes, self.flops = name, nbytes, flops
+
+    def __enter__(self):
+        external = self.prof.plan is not None
+        self.start = torch.cuda.Event(enable_timing=True, external=external)
+        self.end = torch.cuda.Event(enable_timing=True, external=external)
+        self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        self.end.record()
+        self.prof.events.append((self.name, self.start, self.end, float(self.nbytes),
+                                 float(self.flops)))
+
+
+def profile_region(name: str, nbytes: float, flops: float):
+    """A region of the active profile, or nothing when none is active."""
+    return _profile.region(name, nbytes, flops) if _profile is not None else _NO_REGION
+
+
+class _NoRegion:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_REGION = _NoRegion()
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
+def _timed(work: Callable):
+    """Wrap a launcher: under an active profile it is timed and ``work(*args)`` gives
+    (kernel class, bytes, operations) from the call's arguments."""
+    def deco(fn):
+        @functools.wraps(fn)
+        def wrapper(*args, **kw):
+            if _profile is None:
+                return fn(*args, **kw)
+            name, nbytes, flops = ("", 0, 0) if _profile.plan is not None else work(*args, **kw)
+            with _profile.region(name, nbytes, flops):
+                return fn(*args, **kw)
+        return wrapper
+    return deco
+
+
+def _attention_cache_work(kind, row_pos, k_pool, n_heads, head_dim, window, rows, value_dim=None):
+    """Keys and values a row at ``row_pos`` reads from the cache (reads the positions back:
+    only done under a profile)."""
+    seen = row_pos.to(torch.int64) + 1
+    if window > 0:
+        seen = seen.clamp(max=window)
+    keys = int(seen.sum().item())
+    n_kv = k_pool.shape[1]
+    nbytes = keys * n_kv * (head_dim + (value_dim or head_dim)) * k_pool.element_size()
+    return kind, nbytes, 4.0 * keys * n_heads * head_dim
+
+
+def _prompt_work(kind, qkv, seq_len, n_heads, head_dim, window):
+    """Prompts from position 0: (query, key) pairs inside the causal mask and the window."""
+    pairs = 0
+    for n in seq_len.to(torch.int64).tolist():
+        if window and n > window:
+            pairs += window * (window + 1) // 2 + (n - window) * window
+        else:
+            pairs += n * (n + 1) // 2
+    return kind, _nbytes(qkv) + qkv.shape[0] * n_heads * head_dim * qkv.element_size(), \
+        4.0 * pairs * n_heads * head_dim
+
+
+# --------------------------------------------------------------------------
+
+@_timed(lambda tokens, table, scale, out: ("embed_rows", 2 * _nbytes(out), 0))
 def embed_rows(tokens: torch.Tensor, table: torch.Tensor, scale: float,
                out: torch.Tensor) -> torch.Tensor:
     """out[r] = scale * table[tokens[r]] in 32-bit."""
@@ -135,6 +270,7 @@ def randn_fill(dst: torch.Tensor, rows: int, cols: int, group: int, group_stride
         c_int(BF16 if stored_dtype == torch.bfloat16 else F32), _stream()))
 
 
+@_timed(lambda gate_up, out, group=0: ("gelu_mul", _nbytes(gate_up, out), 0))
 def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.Tensor:
     """out[r, i] = gelu_tanh(gate(r, i)) * up(r, i); gate_up rows are [gates | ups]
     (group 0) or groups of ``group`` gates followed by their ups."""
@@ -148,6 +284,7 @@ def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor, group: int = 0) -> torch.
     return out
 
 
+@_timed(lambda x, cap: ("softcap", 2 * _nbytes(x), 0))
 def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     """x = cap * tanh(x / cap) in place (32-bit)."""
     _want(x, torch.float32, "x")
@@ -155,6 +292,8 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+@_timed(lambda x, gain, eps, out, rows=None: (
+    "rms_norm", out.shape[0] * x.shape[1] * x.element_size() + _nbytes(out), 0))
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[i] = rms(x[rows[i] if rows else i]) * gain; statistics in 32-bit."""
@@ -175,6 +314,8 @@ def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
     return out
 
 
+@_timed(lambda a, post_gain, post_eps, h, pre_gain, pre_eps, out: (
+    "add_rms_norm", _nbytes(a, out) + 2 * _nbytes(h), 0))
 def add_rms_norm(a: torch.Tensor, post_gain: Optional[torch.Tensor], post_eps: float,
                  h: torch.Tensor, pre_gain: Optional[torch.Tensor], pre_eps: float,
                  out: Optional[torch.Tensor]) -> None:
@@ -198,6 +339,7 @@ def add_rms_norm(a: torch.Tensor, post_gain: Optional[torch.Tensor], post_eps: f
                                       c_int(rows), c_int(hidden), _stream()))
 
 
+@_timed(lambda qkv, *a, **kw: ("rope_store", 2 * _nbytes(qkv), 0))
 def rope_store(qkv: torch.Tensor, row_pos, row_seq, seq_slot, seq_end,
                inv_freq: Optional[torch.Tensor], rotary_dim: int, style: int,
                k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
@@ -232,6 +374,13 @@ def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits:
                                                           c_int(head_dim), c_int(splits)))
 
 
+@_timed(lambda q, q_stride, k_new, v_new, kv_stride, k_pool, v_pool, page_table, page_tokens,
+        ring_tokens, row_pos, row_seq, seq_slot, seq_start, seq_row0, out, scratch, n_heads, n_kv,
+        head_dim, scale, softcap, window, splits: (
+            _attention_cache_work("attention_rows (cache)", row_pos, k_pool, n_heads, head_dim,
+                                  window, out.shape[0]) if k_pool is not None else
+            ("attention_rows (prompt)", 2 * _nbytes(out) * (1 + 2 * n_kv / n_heads),
+             2.0 * (row_pos.to(torch.int64) + 1).sum().item() * 2 * n_heads * head_dim)))
 def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor],
                    v_new: Optional[torch.Tensor], kv_stride: int,
                    k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
@@ -275,6 +424,10 @@ def attention_decode_resident_warps(n_heads: int, n_kv: int, head_dim: int) -> i
                                                              c_int(head_dim)))
 
 
+@_timed(lambda q, q_stride, k_pool, v_pool, page_table, page_tokens, ring_tokens, row_pos, row_seq,
+        seq_slot, out, scratch, tickets, n_heads, n_kv, head_dim, scale, softcap, window, splits,
+        warps=4: _attention_cache_work("attention_decode", row_pos, k_pool, n_heads, head_dim,
+                                       window, out.shape[0]))
 def attention_decode(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                      page_table: torch.Tensor, page_tokens: int, ring_tokens: int, row_pos,
                      row_seq, seq_slot, out: torch.Tensor, scratch: Optional[torch.Tensor],
@@ -315,6 +468,9 @@ def attention_prefill_supports(n_heads: int, n_kv: int, head_dim: int) -> bool:
                                                          c_int(head_dim)))
 
 
+@_timed(lambda qkv, out, seq_row0, seq_len, n_seqs, max_len, n_heads, n_kv, head_dim, scale,
+        softcap, window: _prompt_work("attention_prefill (mma.sync)", qkv, seq_len, n_heads,
+                                      head_dim, window))
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                       max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                       softcap: float, window: int) -> torch.Tensor:
@@ -348,6 +504,9 @@ def attention_prefill_tc_split(n_seqs: int, max_len: int, n_heads: int, n_kv: in
     return int(nbytes.value), int(n_tickets.value)
 
 
+@_timed(lambda qkv, out, seq_row0, seq_len, n_seqs, max_len, n_heads, n_kv, head_dim, scale,
+        softcap, window, scratch=None, tickets=None: _prompt_work(
+            "attention_prefill_tc (tcgen05)", qkv, seq_len, n_heads, head_dim, window))
 def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                          max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                          softcap: float, window: int, scratch: Optional[torch.Tensor] = None,
@@ -381,6 +540,12 @@ def attention_prefill_tc_error(clear: bool = True) -> int:
 SKINNY_MAX_ROWS = 64
 
 
+def _product_work(kind, x, w, out):
+    return (f"{kind} {w.shape[0]}x{w.shape[1]}", _nbytes(w, out) + x.shape[0] * x.shape[1]
+            * x.element_size(), 2.0 * x.shape[0] * w.shape[0] * w.shape[1])
+
+
+@_timed(lambda x, w, out, epilogue=EPI_NONE, cap=0.0: _product_work("skinny_linear", x, w, out))
 def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
                   cap: float = 0.0) -> torch.Tensor:
     """out = x . w^T for at most 64 rows of bfloat16 x (see csrc/linear_skinny.cu)."""
@@ -399,6 +564,7 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     return out
 
 
+@_timed(lambda x, w, out, *a, **kw: _product_work("skinny_linear_rope", x, w, out))
 def skinny_linear_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_pos, row_seq,
                        seq_slot, seq_end, inv_freq: torch.Tensor,
                        k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
@@ -439,6 +605,8 @@ def gemm_tcgen05_supports(R: int, N: int, K: int, x_stride: int) -> bool:
                                                     c_longlong(x_stride)))
 
 
+@_timed(lambda x, w, out, epilogue=EPI_NONE, cap=0.0, one_block=False: _product_work(
+    "gemm_tcgen05", x, w, out))
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
                  cap: float = 0.0, one_block: bool = False) -> torch.Tensor:
     """out = x . w^T for bfloat16 x and w on tcgen05 (see csrc/gemm_tcgen05.cu).  More than
@@ -465,6 +633,7 @@ def gemm_tcgen05_error(clear: bool = True) -> int:
     return int(library().sib_gemm_tcgen05_error(c_int(1 if clear else 0)))
 
 
+@_timed(lambda logits, *a, **kw: ("sample_rows", _nbytes(logits), 0))
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
                 rng_state: Optional[torch.Tensor], out: torch.Tensor,
                 rng_index: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -132,10 +132,13 @@ class Runtime:
             return native.gemm_tcgen05(x, w, out, epilogue, cap)
         if epilogue == native.EPI_GEGLU:
             raise ValueError("the gated epilogue exists in the hand-written products only")
-        if out_dtype == x.dtype:
-            y = torch.matmul(x, w.t())
-        else:
-            y = torch.mm(x, w.t(), out_dtype=out_dtype)
+        with native.profile_region(f"library product {N}x{K}",
+                                   (N * K + R * K) * x.element_size() + R * N * 4,
+                                   2.0 * R * N * K):
+            if out_dtype == x.dtype:
+                y = torch.matmul(x, w.t())
+            else:
+                y = torch.mm(x, w.t(), out_dtype=out_dtype)
         if epilogue == native.EPI_SOFTCAP:
             if y.dtype != torch.float32:
                 raise ValueError("the soft cap epilogue is applied to 32-bit outputs")

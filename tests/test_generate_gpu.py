@@ -183,3 +183,21 @@ def test_trace_replay(model_dirs, tmp_path, dtype):
                             f"batch step {i}")
     for k, i in enumerate(range(84, 90)):
         assert_logits_close(_read(out, tail + k, V), refs[2][i:i + 1], dtype, f"c token {i}")
+
+
+def test_command_line_profile_prints_a_table_per_kernel(model_dirs):
+    """--profile: per-token times and, for one prompt step and one captured single-token
+    step, the device time of every kernel class with its share of the peak."""
+    prompt = random_prompts(CONFIGS["B"], [20], seed=8)[0]
+    cmd = [sys.executable, "-m", "strata_inference_b200.cli", "-m", model_dirs["B"],
+           "--token-ids", ",".join(map(str, prompt)), "-n", "4", "--temp", "0", "--profile",
+           "--no-display-prompt"]
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert r.returncode == 0, r.stderr
+    err = r.stderr
+    assert err.count("[profile] request 0 token") == 4
+    assert "[profile] prompt step, 20 tokens" in err and "single-token step near position" in err
+    table = [l.split() for l in err.splitlines() if l.startswith("[profile] attention")]
+    assert len(table) >= 2 and all(float(row[-1]) >= 0.0 for row in table)
+    for kernel in ("add_rms_norm", "rms_norm", "embed_rows", "sample_rows", "(between kernels)"):
+        assert kernel in err, kernel
