@@ -34,7 +34,10 @@ bool sib_chained_launches();   // false when the environment sets SIB_CHAINED_LA
 // "their" word of a small per-device table when a wait ran out.  The table is allocated
 // at the first use on a device; the host fetches it with an asynchronous copy on the
 // step's stream and looks at it wherever it synchronises anyway (runtime.cu).
-enum SibErrorWord { SIB_ERR_GEMM_TCGEN05 = 0, SIB_ERR_ATTENTION_PREFILL_TC = 1, SIB_ERROR_WORDS = 8 };
+enum SibErrorWord {
+    SIB_ERR_GEMM_TCGEN05 = 0, SIB_ERR_ATTENTION_PREFILL_TC = 1, SIB_ERR_LINEAR_STREAM = 2,
+    SIB_ERROR_WORDS = 8
+};
 int* sib_error_word(int word);   // device address of the current device's word; null on failure
 
 template <typename... KArgs, typename... Args>

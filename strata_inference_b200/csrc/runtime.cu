@@ -4,6 +4,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 static thread_local char g_error[512] = "";
 
@@ -50,7 +51,7 @@ SIB_EXPORT int sib_compiled_arch() {
 static int* g_error_words[64] = {};
 static std::mutex g_error_mutex;
 static const char* const kErrorWordNames[SIB_ERROR_WORDS] = {
-    "gemm_tcgen05", "attention_prefill_tc", "", "", "", "", "", ""};
+    "gemm_tcgen05", "attention_prefill_tc", "linear_stream", "", "", "", "", ""};
 
 static int* error_table() {
     int dev = 0;
@@ -129,4 +130,40 @@ SIB_EXPORT int sib_gemm_tcgen05_error(int clear) { return error_word_now(SIB_ERR
 
 SIB_EXPORT int sib_attention_prefill_tc_error(int clear) {
     return error_word_now(SIB_ERR_ATTENTION_PREFILL_TC, clear);
+}
+
+// ---------------------------------------------------------------------------
+// Tensor maps (tma.cuh).
+// ---------------------------------------------------------------------------
+SibEncodeTiledFn sib_encode_tiled_fn() {
+    static SibEncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = (SibEncodeTiledFn)ptr;
+    return fn;
+}
+
+int sib_make_bf16_map(CUtensorMap* map, const void* base, long long rows, long long cols,
+                      long long row_stride, int box_rows, const char* who) {
+    SibEncodeTiledFn enc = sib_encode_tiled_fn();
+    if (!enc) {
+        sib_set_error("%s: cuTensorMapEncodeTiled is not available", who);
+        return -1;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        sib_set_error("%s: cuTensorMapEncodeTiled failed with code %d", who, (int)r);
+        return -1;
+    }
+    return 0;
 }

@@ -75,6 +75,12 @@ class Runtime:
         # takes up to native.SKINNY_MAX_ROWS); measured on a B200 at Gemma2-2B sizes it
         # is ahead of the library product up to 16 rows and behind it from 32 on.
         self.skinny_max_rows = 16
+        # SIB_LINEAR_STREAM=1: few-row products go to the kernel that stages its weights through
+        # shared memory (csrc/linear_stream.cu) instead of the one that loads them straight
+        # into registers.  Alone it is the faster of the two on most shapes; inside a chained
+        # step it is slower (2B shape, batch 8: 3.29 against 2.51 ms), because a block of it
+        # needs a third of an SM's shared memory before it can start under its predecessor.
+        self.stream_products = os.environ.get("SIB_LINEAR_STREAM", "0") == "1"
         # SIB_FUSE_ROTATION=0: rotation and cache write always run as a kernel of their own
         self.fuse_rotation = os.environ.get("SIB_FUSE_ROTATION", "1") != "0"
         # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
@@ -120,6 +126,8 @@ class Runtime:
         if (x.dtype == torch.bfloat16 and 0 < R <= self.skinny_max_rows and K % 8 == 0
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
+            if self.stream_products:
+                return native.linear_stream(x, w, out, epilogue, cap)
             return native.skinny_linear(x, w, out, epilogue, cap)
         aligned = (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                    and x.data_ptr() % 16 == 0)

@@ -463,6 +463,67 @@ def test_skinny_linear(R, N, K):
                torch.bfloat16, "skinny gated")
 
 
+@pytest.mark.parametrize("R,N,K,ksplit,stages", [
+    (1, 128, 64, 0, 0), (3, 144, 200, 0, 0), (8, 2304, 2048, 0, 0), (16, 4096, 2304, 0, 0),
+    (9, 300, 328, 1, 2), (16, 272, 1024, 8, 2), (5, 48, 1600, 5, 3), (12, 1000, 776, 3, 12),
+    (2, 18432, 2304, 0, 0), (7, 2304, 9216, 0, 0), (1, 256, 128, 2, 1),
+])
+def test_linear_stream(R, N, K, ksplit, stages):
+    """The few-row product with TMA-staged weights: sizes that are no multiples of its
+    tiles (rows of 128, k of 64), every split of k over a cluster, rings shorter and longer
+    than the run of k, all epilogues and both output types."""
+    n = _native()
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    xd, wd = x.to(DEV), w.to(DEV)
+    out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
+    n.linear_stream(xd, wd, out, n.EPI_NONE, 0.0, ksplit, stages)
+    _close(out, ref, torch.float32, "stream f32 out", factor=20)
+    # a strided input (rows of a wider buffer) and a strided output
+    wide = torch.zeros(R, K + 16, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = xd
+    out16 = torch.full((R, N + 8), float("nan"), dtype=torch.bfloat16, device=DEV)
+    n.linear_stream(wide[:, :K], wd, out16[:, :N], n.EPI_NONE, 0.0, ksplit, stages)
+    _close(out16[:, :N], ref, torch.bfloat16, "stream bf16 out")
+    assert torch.isnan(out16[:, N:].float()).all()
+    capped = torch.empty(R, N, dtype=torch.float32, device=DEV)
+    n.linear_stream(xd, wd, capped, n.EPI_SOFTCAP, 0.7, ksplit, stages)
+    _close(capped, 0.7 * torch.tanh(ref / 0.7), torch.float32, "stream soft cap", factor=20)
+    if N % 16 == 0:
+        gated = torch.empty(R, N // 2, dtype=torch.bfloat16, device=DEV)
+        n.linear_stream(xd, wd, gated, n.EPI_GEGLU, 0.0, ksplit, stages)
+        y = ref.view(R, N // 16, 2, 8)
+        _close(gated, (plain.gelu_tanh(y[:, :, 0]) * y[:, :, 1]).reshape(R, N // 2),
+               torch.bfloat16, "stream gated")
+    # the same sums whatever the split and the ring (up to the order of the partial sums)
+    again = torch.empty(R, N, dtype=torch.float32, device=DEV)
+    n.linear_stream(xd, wd, again, n.EPI_NONE, 0.0, 1, 2)
+    _close(again, out.double().cpu(), torch.float32, "stream, one block a tile", factor=5)
+    torch.cuda.synchronize()
+    watch = n.KernelWatch()
+    watch.fetch()
+    torch.cuda.synchronize()
+    watch.check()
+
+
+def test_linear_stream_refuses_what_it_cannot_do():
+    n = _native()
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(n.KernelError, match="1 to 16 rows"):
+        n.linear_stream(torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV), w,
+                        torch.empty(17, 32, dtype=torch.float32, device=DEV))
+    with pytest.raises(n.KernelError, match="multiples of 8"):
+        n.linear_stream(torch.zeros(2, 60, dtype=torch.bfloat16, device=DEV),
+                        torch.zeros(32, 60, dtype=torch.bfloat16, device=DEV),
+                        torch.empty(2, 32, dtype=torch.float32, device=DEV))
+    with pytest.raises(n.KernelError, match="groups of 16"):
+        n.linear_stream(torch.zeros(2, 64, dtype=torch.bfloat16, device=DEV),
+                        torch.zeros(24, 64, dtype=torch.bfloat16, device=DEV),
+                        torch.empty(2, 12, dtype=torch.bfloat16, device=DEV), n.EPI_GEGLU)
+
+
 def test_skinny_linear_refuses_what_it_cannot_do():
     n = _native()
     x = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)
