@@ -51,7 +51,7 @@ SIB_EXPORT int sib_compiled_arch() {
 static int* g_error_words[64] = {};
 static std::mutex g_error_mutex;
 static const char* const kErrorWordNames[SIB_ERROR_WORDS] = {
-    "gemm_tcgen05", "attention_prefill_tc", "linear_stream", "", "", "", "", ""};
+    "gemm_tcgen05", "attention_prefill_tc", "linear_stream", "decode_chain", "", "", "", ""};
 
 static int* error_table() {
     int dev = 0;
@@ -163,6 +163,31 @@ int sib_make_bf16_map(CUtensorMap* map, const void* base, long long rows, long l
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         sib_set_error("%s: cuTensorMapEncodeTiled failed with code %d", who, (int)r);
+        return -1;
+    }
+    return 0;
+}
+
+int sib_make_bf16_map_k_tiles(CUtensorMap* map, const void* base, long long rows, long long cols,
+                              long long row_stride, int box_rows, int box_tiles, const char* who) {
+    SibEncodeTiledFn enc = sib_encode_tiled_fn();
+    if (!enc) {
+        sib_set_error("%s: cuTensorMapEncodeTiled is not available", who);
+        return -1;
+    }
+    if (cols % 64 != 0) {
+        sib_set_error("%s: %lld columns are not whole blocks of 64", who, cols);
+        return -1;
+    }
+    cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, 128u};
+    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)box_tiles};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        sib_set_error("%s: cuTensorMapEncodeTiled (3-d) failed with code %d", who, (int)r);
         return -1;
     }
     return 0;

@@ -55,6 +55,16 @@ __device__ __forceinline__ void sib_tma_load_2d(void* dst, const CUtensorMap* ma
         : "memory");
 }
 
+// One box of a 3-d tensor map (c0 along the contiguous dimension, as above).
+__device__ __forceinline__ void sib_tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                                int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(sib_smem_u32(dst)),
+        "l"(map), "r"(sib_smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
 typedef CUresult (*SibEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                      const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -66,3 +76,9 @@ SibEncodeTiledFn sib_encode_tiled_fn();   // null if the driver does not offer i
 // rows: boxes of box_rows x 64 elements (128 bytes), 128-byte swizzle, zeros outside.
 int sib_make_bf16_map(CUtensorMap* map, const void* base, long long rows, long long cols,
                       long long row_stride, int box_rows, const char* who);
+
+// The same matrix (cols a multiple of 64) seen as [cols / 64][rows][64]: a box takes
+// box_tiles 64-wide blocks of k of box_rows rows, laid out [block of k][row][64] in shared
+// memory, so that one copy brings box_tiles * 128 contiguous bytes of every row.
+int sib_make_bf16_map_k_tiles(CUtensorMap* map, const void* base, long long rows, long long cols,
+                              long long row_stride, int box_rows, int box_tiles, const char* who);

@@ -138,6 +138,15 @@ class DecoderModel:
     def hidden_states(self, ctx) -> torch.Tensor:
         """Run every schedule entry over the step's rows; returns the 32-bit
         residual stream [rows, hidden]."""
+        rt = self.rt
+        if rt.chain_steps and rt.dtype == torch.bfloat16 and 0 < ctx.n_rows <= rt.skinny_max_rows:
+            # few rows: what lies between two attention kernels runs as one kernel
+            with rt.chaining(ctx.n_rows):
+                return self._walk(ctx)
+        return self._walk(ctx)
+
+    def _walk(self, ctx) -> torch.Tensor:
+        from ..parts.base import chain_suspended
         h = self.embedding.forward(ctx)
         schedule = self.spec.schedule
         normed = None
@@ -145,7 +154,11 @@ class DecoderModel:
             block = self.blocks[e.layer]
             nxt = self.blocks[schedule[pos + 1].layer].first_norm if pos + 1 < len(schedule) else None
             cache_entry = pos if e.cache_of is None else e.cache_of
-            normed = block.forward(h, normed, ctx, pos, cache_entry, e.cache_of is None, nxt)
+            if self.rt.chain is not None and not getattr(block, "chain_safe", False):
+                with chain_suspended(self.rt):
+                    normed = block.forward(h, normed, ctx, pos, cache_entry, e.cache_of is None, nxt)
+            else:
+                normed = block.forward(h, normed, ctx, pos, cache_entry, e.cache_of is None, nxt)
         return h
 
     def logits(self, h: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -113,6 +113,14 @@ def _want(t: torch.Tensor, dtype: torch.dtype, name: str, contiguous: bool = Tru
 # wall-clock figure per layer (src/model/layer.rs:1265,1365-1375).
 
 _profile: Optional["KernelProfile"] = None
+# Set while a chain of deferred steps is being collected (parts/base.py ProductChain): called
+# before any other launch of this module, so that the chain's kernel runs first.
+_pending: Optional[Callable[[], None]] = None
+
+
+def set_pending(flush: Optional[Callable[[], None]]) -> None:
+    global _pending
+    _pending = flush
 
 
 class KernelProfile:
@@ -204,6 +212,8 @@ def _timed(work: Callable):
     def deco(fn):
         @functools.wraps(fn)
         def wrapper(*args, **kw):
+            if _pending is not None:
+                _pending()          # deferred work that this launch may depend on goes first
             if _profile is None:
                 return fn(*args, **kw)
             name, nbytes, flops = ("", 0, 0) if _profile.plan is not None else work(*args, **kw)
@@ -729,3 +739,133 @@ def set_kernel_error(word: int, code: int) -> None:
     kernel that gave up)."""
     if library().sib_kernel_error_set(c_int(word), c_int(code), _stream()) != 0:
         raise KernelError(library().sib_last_error().decode())
+
+
+# --------------------------------------------------------------------------
+# decode_chain: several dependent few-row steps as one kernel (csrc/decode_chain.cu)
+
+CHAIN_PRODUCT, CHAIN_NORM = 0, 1
+EPI_ROPE = 3
+
+
+class ChainPhase(ctypes.Structure):
+    """Mirrors SibChainPhase of csrc/decode_chain.h."""
+    _fields_ = [
+        ("kind", c_int), ("epi", c_int),
+        ("w", c_void_p), ("x", c_void_p), ("y", c_void_p),
+        ("N", c_int), ("K", c_int), ("x_stride", c_int), ("y_stride", c_int), ("out_f32", c_int),
+        ("cap", c_float),
+        ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p), ("seq_end", c_void_p),
+        ("inv_freq", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("page_table", c_void_p),
+        ("n_heads", c_int), ("n_kv", c_int), ("head_dim", c_int), ("max_pages", c_int),
+        ("page_tokens", c_int), ("ring_tokens", c_int),
+        ("a", c_void_p), ("post_gain", c_void_p), ("h", c_void_p), ("pre_gain", c_void_p),
+        ("out", c_void_p), ("rows", c_void_p),
+        ("post_eps", c_float), ("pre_eps", c_float),
+        ("hidden", c_int), ("a_stride", c_int), ("out_stride", c_int),
+    ]
+
+
+def _addr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def chain_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+                  cap: float = 0.0, rope: Optional[dict] = None) -> ChainPhase:
+    """A product phase: out = epilogue(x . w^T).  ``rope``: the arguments of
+    ``skinny_linear_rope`` by name, for the q|k|v product that rotates and stores."""
+    _want(x, torch.bfloat16, "x", contiguous=False)
+    _want(w, torch.bfloat16, "w")
+    R, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("chain_product: shapes do not fit")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("chain_product: outputs are bfloat16 or float32")
+    ph = ChainPhase(kind=CHAIN_PRODUCT, epi=EPI_ROPE if rope is not None else epilogue,
+                    w=w.data_ptr(), x=x.data_ptr(), y=out.data_ptr(), N=N, K=K,
+                    x_stride=x.stride(0), y_stride=out.stride(0),
+                    out_f32=1 if out.dtype == torch.float32 else 0, cap=cap)
+    if rope is not None:
+        n_kv = rope["n_kv"]
+        for name in ("row_pos", "row_seq", "seq_slot", "seq_end"):
+            _want(rope[name], torch.int32, name)
+            setattr(ph, name, rope[name].data_ptr())
+        _want(rope["inv_freq"], torch.float32, "inv_freq")
+        if rope["inv_freq"].numel() * 2 != rope["head_dim"]:
+            raise KernelError("chain_product: one frequency per pair of the whole head")
+        ph.inv_freq = rope["inv_freq"].data_ptr()
+        if n_kv:
+            _want(rope["k_pool"], torch.bfloat16, "k_pool")
+            _want(rope["v_pool"], torch.bfloat16, "v_pool")
+            _want(rope["page_table"], torch.int32, "page_table")
+            if tuple(rope["k_pool"].shape[1:]) != (n_kv, rope["page_tokens"], rope["head_dim"]):
+                raise KernelError("chain_product: pool layout must be [pages, kv_heads, page_tokens, head_dim]")
+            ph.k_pool, ph.v_pool = rope["k_pool"].data_ptr(), rope["v_pool"].data_ptr()
+            ph.page_table = rope["page_table"].data_ptr()
+            ph.max_pages = rope["page_table"].shape[1]
+        ph.n_heads, ph.n_kv, ph.head_dim = rope["n_heads"], n_kv, rope["head_dim"]
+        ph.page_tokens, ph.ring_tokens = rope["page_tokens"], rope["ring_tokens"]
+    return ph
+
+
+def chain_norm(a: Optional[torch.Tensor], post_gain: Optional[torch.Tensor], post_eps: float,
+               h: torch.Tensor, pre_gain: Optional[torch.Tensor], pre_eps: float,
+               out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> ChainPhase:
+    """A "norm, add, norm" phase (see ``add_rms_norm``); without ``a`` a plain norm of the
+    rows of h that ``rows`` names."""
+    _want(h, torch.float32, "h")
+    hidden = h.shape[1]
+    if a is not None:
+        _want(a, torch.bfloat16, "a", contiguous=False)
+        if tuple(a.shape) != tuple(h.shape) or a.stride(1) != 1:
+            raise KernelError("chain_norm: a and h differ in shape")
+    for gname, gt in (("post_gain", post_gain), ("pre_gain", pre_gain)):
+        if gt is not None:
+            _want(gt, torch.float32, gname)
+            if gt.numel() != hidden:
+                raise KernelError(f"chain_norm: {gname} has the wrong length")
+    if pre_gain is not None:
+        if out is None:
+            raise KernelError("chain_norm: pre_gain needs out")
+        _want(out, torch.bfloat16, "out", contiguous=False)
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    return ChainPhase(kind=CHAIN_NORM, a=_addr(a), post_gain=_addr(post_gain), h=h.data_ptr(),
+                      pre_gain=_addr(pre_gain), out=_addr(out), rows=_addr(rows),
+                      post_eps=post_eps, pre_eps=pre_eps, hidden=hidden,
+                      a_stride=a.stride(0) if a is not None else 0,
+                      out_stride=out.stride(0) if out is not None else 0)
+
+
+def decode_chain_max_phases() -> int:
+    return int(library().sib_decode_chain_max_phases())
+
+
+def _chain_work(phases, rows, sync, stages=0):
+    nbytes = flops = 0
+    for ph in phases:
+        if ph.kind == CHAIN_PRODUCT:
+            nbytes += ph.N * ph.K * 2 + rows * (ph.K + ph.N) * 2
+            flops += 2.0 * rows * ph.N * ph.K
+        else:
+            nbytes += rows * ph.hidden * 12
+    return f"decode_chain of {len(phases)}", nbytes, flops
+
+
+@_timed(_chain_work)
+def _decode_chain(phases, rows, sync, stages=0):
+    arr = (ChainPhase * len(phases))(*phases)
+    _check(library().sib_decode_chain(arr, c_int(len(phases)), c_int(rows), c_int(stages),
+                                      _ptr(sync), _stream()))
+
+
+def decode_chain(phases, rows: int, sync: torch.Tensor, stages: int = 0) -> None:
+    """Run ``phases`` (from ``chain_product`` / ``chain_norm``) in order as one kernel for a
+    step of ``rows`` rows.  ``sync``: two int32 counters on the device, zero before the
+    first call (every call leaves them zero)."""
+    _want(sync, torch.int32, "sync")
+    if sync.numel() < 2:
+        raise KernelError("decode_chain: two counters are needed")
+    _decode_chain(list(phases), rows, sync, stages)

@@ -37,6 +37,8 @@ _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 
 
 class Attention:
+    chain_safe = True      # deferred results are read by this runtime's and native's launchers only
+
     @staticmethod
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
         nh, nkv, hd = params["num_heads"], params["num_kv_heads"], params["head_dim"]
@@ -148,16 +150,19 @@ class Attention:
                 and x.data_ptr() % 16 == 0):
             # few rows: the product rotates q and k and writes k and v into the cache itself
             qkv = torch.empty((R, w_in.shape[0]), dtype=x.dtype, device=x.device)
-            native.skinny_linear_rope(x, w_in, qkv, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
-                                      ctx.seq_end, rotary[0], view.k if owns_cache else None,
-                                      view.v if owns_cache else None,
-                                      view.page_table if owns_cache else None, view.page_tokens,
-                                      view.ring_tokens, nh, nkv, hd)
+            rt.linear_rope(x, w_in, qkv, row_pos=ctx.row_pos, row_seq=ctx.row_seq,
+                           seq_slot=ctx.seq_slot, seq_end=ctx.seq_end, inv_freq=rotary[0],
+                           k_pool=view.k if owns_cache else None,
+                           v_pool=view.v if owns_cache else None,
+                           page_table=view.page_table if owns_cache else None,
+                           page_tokens=view.page_tokens, ring_tokens=view.ring_tokens,
+                           n_heads=nh, n_kv=nkv, head_dim=hd)
         else:
             qkv = rt.linear(x, w_in)
             if rotary is not None:
                 inv_freq, rot, style = rotary
             else:
+                rt.flush()      # a position part of its own works on q and k with its own code
                 q_view = qkv[:, : nh * hd].view(R, nh, hd)
                 k_view = qkv[:, nh * hd:(nh + nkv) * hd].view(R, nkv, hd) if nkv else None
                 self.position.apply(q_view, k_view, ctx)

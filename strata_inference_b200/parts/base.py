@@ -86,6 +86,13 @@ class Runtime:
         # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
         # 256 x 256 tiles) beats the library product followed by the activation kernel
         self.gated_gemm_min_rows = 128
+        # SIB_DECODE_CHAIN=1: the steps between two attention kernels of a step of few rows run
+        # as ONE chain kernel (csrc/decode_chain.cu) instead of one kernel each.  Measured on
+        # the Gemma2-2B shape it is the slower of the two so far (a layer's products and norms:
+        # 60 against 47 us at batch 8), so it is off unless asked for.
+        self.chain_steps = os.environ.get("SIB_DECODE_CHAIN", "0") == "1"
+        self.chain: Optional[ProductChain] = None
+        self._chain_sync: Optional[torch.Tensor] = None
         self._scratch: Optional[torch.Tensor] = None
         self._tickets: Optional[torch.Tensor] = None
         self._retired: list = []       # outgrown buffers that captured graphs may still name
@@ -112,6 +119,56 @@ class Runtime:
             self._tickets = torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device)
         return self._tickets
 
+    # ---- chains of deferred steps ------------------------------------------
+    def chaining(self, rows: int):
+        """A context in which the few-row products and the "norm, add, norm" steps issued
+        through this runtime are collected and run as ONE kernel (csrc/decode_chain.cu) as
+        soon as anything else is launched through ``kernels.native`` (or the context ends).
+        Results of deferred steps are tensors like any other, but their contents exist only
+        after the chain ran: code that reads them with anything but this runtime's methods
+        or the launchers of ``kernels.native`` calls ``flush()`` first.  Blocks whose parts
+        do not promise that (``chain_safe``) run with the chain suspended."""
+        return _Chaining(self, rows)
+
+    def flush(self) -> None:
+        if self.chain is not None:
+            self.chain.flush()
+
+    def chain_sync(self) -> torch.Tensor:
+        if self._chain_sync is None:
+            self._chain_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+        return self._chain_sync
+
+    def _chainable(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> bool:
+        R, K = x.shape
+        return (self.chain is not None and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and 0 < R <= self.chain.rows and K % 8 == 0 and x.stride(1) == 1
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
+                and out_dtype in (torch.bfloat16, torch.float32))
+
+    def linear_rope(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, **rope) -> torch.Tensor:
+        """The q|k|v product of few rows that rotates q and k and writes k and v into the
+        cache (``native.skinny_linear_rope``'s arguments by name), deferred when a chain is
+        being collected."""
+        if self._chainable(x, w, out.dtype):
+            self.chain.add(native.chain_product(x, w, out, rope=rope), (x, w, out))
+            return out
+        return native.skinny_linear_rope(
+            x, w, out, rope["row_pos"], rope["row_seq"], rope["seq_slot"], rope["seq_end"],
+            rope["inv_freq"], rope["k_pool"], rope["v_pool"], rope["page_table"],
+            rope["page_tokens"], rope["ring_tokens"], rope["n_heads"], rope["n_kv"],
+            rope["head_dim"])
+
+    def add_rms_norm(self, a: torch.Tensor, post_gain, post_eps: float, h: torch.Tensor, pre_gain,
+                     pre_eps: float, out: Optional[torch.Tensor]) -> None:
+        """``native.add_rms_norm``, deferred when a chain is being collected."""
+        if (self.chain is not None and a.dtype == torch.bfloat16 and a.stride(1) == 1
+                and a.shape[0] <= self.chain.rows and (out is None or out.stride(1) == 1)):
+            self.chain.add(native.chain_norm(a, post_gain, post_eps, h, pre_gain, pre_eps, out),
+                           (a, h, out))
+            return
+        native.add_rms_norm(a, post_gain, post_eps, h, pre_gain, pre_eps, out)
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                epilogue: int = native.EPI_NONE, cap: float = 0.0) -> torch.Tensor:
         """x[R, K] . w[N, K]^T.  Few bfloat16 rows go to the weight-streaming
@@ -123,6 +180,12 @@ class Runtime:
         R, K = x.shape
         N = w.shape[0]
         n_out = N // 2 if epilogue == native.EPI_GEGLU else N
+        if self._chainable(x, w, out_dtype) and (out_dtype == torch.bfloat16
+                                                 or epilogue != native.EPI_GEGLU):
+            out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
+            self.chain.add(native.chain_product(x, w, out, epilogue, cap), (x, w, out))
+            return out
+        self.flush()        # (a library product below is not launched through kernels.native)
         if (x.dtype == torch.bfloat16 and 0 < R <= self.skinny_max_rows and K % 8 == 0
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
@@ -152,6 +215,76 @@ class Runtime:
                 raise ValueError("the soft cap epilogue is applied to 32-bit outputs")
             native.softcap_(y, cap)
         return y
+
+
+class ProductChain:
+    """Deferred few-row steps, in the order they were issued, run as one kernel."""
+
+    def __init__(self, rt: Runtime, rows: int):
+        self.rt = rt
+        self.rows = rows
+        self.phases: list = []
+        self.keep: list = []          # the steps' tensors, alive until the kernel is launched
+        self.most = native.decode_chain_max_phases()
+
+    def add(self, phase, tensors) -> None:
+        if len(self.phases) == self.most:
+            self.flush()
+        self.phases.append(phase)
+        self.keep.append(tensors)
+
+    def flush(self) -> None:
+        if not self.phases:
+            return
+        # (the steps' tensors stay referenced until the kernel is launched: memory that is
+        # handed back earlier could be given to someone else, and written, before it runs)
+        phases, keep = self.phases, self.keep
+        self.phases, self.keep = [], []
+        native.decode_chain(phases, self.rows, self.rt.chain_sync())
+        del keep
+
+
+class _Chaining:
+    def __init__(self, rt: Runtime, rows: int):
+        self.rt, self.rows = rt, rows
+
+    def __enter__(self) -> ProductChain:
+        self.outer = self.rt.chain
+        if self.outer is not None:
+            self.outer.flush()
+        self.rt.chain = ProductChain(self.rt, self.rows)
+        native.set_pending(self.rt.chain.flush)
+        return self.rt.chain
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        chain, self.rt.chain = self.rt.chain, self.outer
+        native.set_pending(self.outer.flush if self.outer is not None else None)
+        if exc_type is None:
+            chain.flush()
+
+
+class _ChainSuspended:
+    """Runs a part that does not know about deferred steps: what was collected goes
+    first, and nothing is deferred meanwhile."""
+
+    def __init__(self, rt: Runtime):
+        self.rt = rt
+
+    def __enter__(self) -> None:
+        self.chain = self.rt.chain
+        if self.chain is not None:
+            self.chain.flush()
+            self.rt.chain = None
+            native.set_pending(None)
+
+    def __exit__(self, *exc) -> None:
+        if self.chain is not None:
+            self.rt.chain = self.chain
+            native.set_pending(self.chain.flush)
+
+
+def chain_suspended(rt: Runtime) -> _ChainSuspended:
+    return _ChainSuspended(rt)
 
 
 class CapturedStepError(RuntimeError):

@@ -21,7 +21,6 @@ from typing import Mapping, Optional
 import torch
 
 from ..config.spec import ConfigError
-from ..kernels import native
 from .registry import register_block
 
 
@@ -49,15 +48,27 @@ class SandwichBlock:
     def first_norm(self):
         return self.pre_mixer
 
+    @property
+    def chain_safe(self) -> bool:
+        """Whether this block may run while few-row steps are deferred into a chain
+        (parts/base.py Runtime.chaining): its mixer and feed-forward promise to touch
+        deferred results through the runtime and ``kernels.native`` only, and its norms are
+        the kind the residual kernel applies."""
+        return (getattr(self.mixer, "chain_safe", False)
+                and getattr(self.feed_forward, "chain_safe", False)
+                and all(_fusable(n) for n in (self.pre_mixer, self.post_mixer, self.pre_ff,
+                                              self.post_ff)))
+
     def _add_then_norm(self, y: torch.Tensor, post, h: torch.Tensor, nxt) -> Optional[torch.Tensor]:
         """h += post(y) (or y); returns nxt(h) if nxt is given."""
         if _fusable(post) and _fusable(nxt):
             out = torch.empty_like(y) if nxt is not None else None
-            native.add_rms_norm(y, post.gain if post is not None else None,
-                                post.eps if post is not None else 0.0, h,
-                                nxt.gain if nxt is not None else None,
-                                nxt.eps if nxt is not None else 0.0, out)
+            self.rt.add_rms_norm(y, post.gain if post is not None else None,
+                                 post.eps if post is not None else 0.0, h,
+                                 nxt.gain if nxt is not None else None,
+                                 nxt.eps if nxt is not None else 0.0, out)
             return out
+        self.rt.flush()         # the steps below read y and h outside the chain
         if post is not None:
             y = post.forward(y, out_dtype=torch.float32)
         h.add_(y.to(torch.float32))
@@ -66,6 +77,7 @@ class SandwichBlock:
     def forward(self, h: torch.Tensor, normed: Optional[torch.Tensor], ctx, entry: int,
                 cache_entry: int, owns_cache: bool, next_norm=None) -> Optional[torch.Tensor]:
         if normed is None:
+            self.rt.flush()
             normed = self.pre_mixer.forward(h, out_dtype=self.rt.dtype)
         a = self.mixer.forward(normed, ctx, entry, cache_entry, owns_cache)
         n2 = self._add_then_norm(a, self.post_mixer, h, self.pre_ff)

@@ -26,6 +26,8 @@ _GROUP = 8
 
 
 class GatedMLP:
+    chain_safe = True      # deferred results are read by this runtime's and native's launchers only
+
     @staticmethod
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
         inter = params["intermediate_size"]

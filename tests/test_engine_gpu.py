@@ -501,3 +501,37 @@ def test_captured_steps_are_kept_for_a_few_batch_sizes_only(model_dirs):
         for _ in range(3):
             eng.decode_step(slots[:n], [7] * n)
     assert len(eng._graphs) == 3 and [k[0] for k in eng._graphs] == [3, 2, 6]
+
+
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16)])
+def test_steps_of_few_rows_as_one_chain_kernel(model_dirs, name, page):
+    """The optional chain kernel (everything between two attention kernels of a step of at
+    most 16 rows as one launch, deferred steps collected by the runtime): prompts of few
+    tokens, single tokens of unequal batches, captured steps; bfloat16."""
+    from strata_inference_b200 import Engine
+    dtype = "bfloat16"
+    cfg = CONFIGS[name]
+    eng = Engine.from_dir(model_dirs[name, dtype], dtype=dtype, max_tokens=1024, page_tokens=page)
+    eng.rt.chain_steps = True
+    reqs = random_prompts(cfg, [40, 28, 35], seed=23)
+    refs = [plain_logits(t, model_dirs[name, dtype], cfg) for t in reqs]
+    slots = [eng.new_sequence() for _ in reqs]
+    first = [5, 3, 7]                                   # 15 rows: the prompts go through the chain too
+    got = eng.step([(s, r[:n]) for s, r, n in zip(slots, reqs, first)],
+                   want=[list(range(n)) for n in first])
+    assert_logits_close(got, torch.cat([f[:n] for f, n in zip(refs, first)]), dtype, f"{name} prompts")
+    pos = list(first)
+    before = eng.rt.chain_sync().clone()
+    for k in range(20):
+        toks = [r[p] for r, p in zip(reqs, pos)]
+        if k < 10:
+            got = eng.step([(s, [t]) for s, t in zip(slots, toks)])
+        else:
+            eng.decode_step(slots, toks)                # captured from the second one on
+            got = eng.last_logits
+        assert_logits_close(got, torch.stack([f[p] for f, p in zip(refs, pos)]), dtype,
+                            f"{name} chained step {k}")
+        pos = [p + 1 for p in pos]
+    assert eng.rt.chain_sync().tolist() == before.tolist() == [0, 0]
+    for s in slots:
+        eng.end_sequence(s)

@@ -524,6 +524,145 @@ def test_linear_stream_refuses_what_it_cannot_do():
                         torch.empty(2, 12, dtype=torch.bfloat16, device=DEV), n.EPI_GEGLU)
 
 
+def _chain_case(R, H, nh, nkv, hd, inter, seed):
+    """Operands of a decoder's steps between two attention kernels, for R rows."""
+    g = torch.Generator().manual_seed(seed)
+    bf = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(torch.bfloat16).to(DEV)  # noqa: E731
+    f32 = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(DEV)  # noqa: E731
+    return dict(
+        attn=bf(R, nh * hd), w_o=bf(H, nh * hd, s=(nh * hd) ** -0.5), h=f32(R, H),
+        g_post=f32(H, s=0.3) + 1, g_pre=f32(H, s=0.3) + 1, g_post2=f32(H, s=0.3) + 1,
+        g_next=f32(H, s=0.3) + 1, w_gu=bf(2 * inter, H, s=H ** -0.5), w_down=bf(H, inter, s=inter ** -0.5),
+        w_qkv=bf((nh + 2 * nkv) * hd, H, s=H ** -0.5))
+
+
+@pytest.mark.parametrize("R,H,nh,nkv,hd,inter", [
+    (3, 320, 4, 2, 32, 400), (8, 2304, 8, 4, 256, 9216), (13, 200, 5, 1, 48, 104),
+    (16, 1024, 6, 3, 128, 1200), (1, 64, 4, 2, 16, 128),
+])
+def test_decode_chain_runs_a_layers_steps_as_one_kernel(R, H, nh, nkv, hd, inter):
+    """Output projection, norm-add-norm, gated feed-forward, norm-add-norm and the next
+    q|k|v with rotation and cache write as ONE kernel, against the same steps run one
+    kernel each and against the plain implementation's functions."""
+    n = _native()
+    c = _chain_case(R, H, nh, nkv, hd, inter, seed=R + H)
+    eps1, eps2 = 1e-6, 1e-5
+    theta, page, ring = 700.0, 8, 0
+    positions = [5 + 3 * i for i in range(R)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
+    row_pos, row_seq, seq_slot = i32(positions), i32(list(range(R))), i32(list(range(R)))
+    seq_end = i32([p + 1 for p in positions])
+    pages_per_seq = -(-(max(positions) + 1) // page)
+    table = torch.randperm(R * pages_per_seq).to(torch.int32).view(R, pages_per_seq).to(DEV)
+    inv_freq = torch.pow(torch.tensor(theta), (-1.0 / hd) * torch.arange(hd // 2).float() * 2).to(DEV)
+    N3 = (nh + 2 * nkv) * hd
+
+    def pools():
+        z = torch.zeros(R * pages_per_seq, nkv, page, hd, dtype=torch.bfloat16, device=DEV)
+        return z, z.clone()
+
+    # the steps one kernel each
+    a1 = torch.empty(R, H, dtype=torch.bfloat16, device=DEV)
+    n.skinny_linear(c["attn"], c["w_o"], a1)
+    h1 = c["h"].clone()
+    x1 = torch.empty(R, H, dtype=torch.bfloat16, device=DEV)
+    n.add_rms_norm(a1, c["g_post"], eps1, h1, c["g_pre"], eps2, x1)
+    t1 = torch.empty(R, inter, dtype=torch.bfloat16, device=DEV)
+    n.skinny_linear(x1, c["w_gu"], t1, n.EPI_GEGLU)
+    f1 = torch.empty(R, H, dtype=torch.bfloat16, device=DEV)
+    n.skinny_linear(t1, c["w_down"], f1)
+    x2 = torch.empty(R, H, dtype=torch.bfloat16, device=DEV)
+    n.add_rms_norm(f1, c["g_post2"], eps1, h1, c["g_next"], eps2, x2)
+    qkv1 = torch.empty(R, N3, dtype=torch.bfloat16, device=DEV)
+    kp1, vp1 = pools()
+    n.skinny_linear_rope(x2, c["w_qkv"], qkv1, row_pos, row_seq, seq_slot, seq_end, inv_freq,
+                         kp1, vp1, table, page, ring, nh, nkv, hd)
+
+    # the same as one kernel
+    sync = torch.zeros(2, dtype=torch.int32, device=DEV)
+    for stages in (0, 2):
+        a2 = torch.full((R, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        h2 = c["h"].clone()
+        y1 = torch.full((R, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        t2 = torch.full((R, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+        f2 = torch.full((R, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        y2 = torch.full((R, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qkv2 = torch.full((R, N3), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kp2, vp2 = pools()
+        rope = dict(row_pos=row_pos, row_seq=row_seq, seq_slot=seq_slot, seq_end=seq_end,
+                    inv_freq=inv_freq, k_pool=kp2, v_pool=vp2, page_table=table, page_tokens=page,
+                    ring_tokens=ring, n_heads=nh, n_kv=nkv, head_dim=hd)
+        phases = [
+            n.chain_product(c["attn"], c["w_o"], a2),
+            n.chain_norm(a2, c["g_post"], eps1, h2, c["g_pre"], eps2, y1),
+            n.chain_product(y1, c["w_gu"], t2, n.EPI_GEGLU),
+            n.chain_product(t2, c["w_down"], f2),
+            n.chain_norm(f2, c["g_post2"], eps1, h2, c["g_next"], eps2, y2),
+            n.chain_product(y2, c["w_qkv"], qkv2, rope=rope),
+        ]
+        n.decode_chain(phases, R, sync, stages)
+        torch.cuda.synchronize()
+        assert sync.tolist() == [0, 0]                    # the counters were put back
+        for got, want, what in ((a2, a1, "output projection"), (y1, x1, "first norm"),
+                                (t2, t1, "gated product"), (f2, f1, "down"), (y2, x2, "second norm"),
+                                (qkv2, qkv1, "q|k|v rotated"), (kp2, kp1, "keys in the cache"),
+                                (vp2, vp1, "values in the cache")):
+            assert torch.isfinite(got.float()).all(), what
+            _close(got, want.double().cpu(), torch.bfloat16, f"chain, {what} (stages {stages})")
+        # (the sub-layer outputs are bfloat16: one unit in their last place moves the sum)
+        _close(h2, h1.double().cpu(), torch.bfloat16, "residual stream")
+    # and against the plain functions (bfloat16 roundings of the intermediates apart)
+    h0 = c["h"].double().cpu()
+    a = c["attn"].double().cpu() @ c["w_o"].double().cpu().T
+    r = h0 + plain.rms_norm(a, c["g_post"].double().cpu() - 1, eps1)
+    x = plain.rms_norm(r, c["g_pre"].double().cpu() - 1, eps2)
+    gu = (x @ c["w_gu"].double().cpu().T).view(R, inter // 8, 2, 8)
+    t = (plain.gelu_tanh(gu[:, :, 0]) * gu[:, :, 1]).reshape(R, inter)
+    f = t @ c["w_down"].double().cpu().T
+    r2 = r + plain.rms_norm(f, c["g_post2"].double().cpu() - 1, eps1)
+    _close(h2, r2, torch.bfloat16, "residual stream against plain")
+    x_next = plain.rms_norm(r2, c["g_next"].double().cpu() - 1, eps2)
+    q = (x_next @ c["w_qkv"].double().cpu().T)[:, :nh * hd].view(R, nh, hd)
+    q_rot = torch.stack([plain.rope_neox(q[i:i + 1], torch.tensor([positions[i]]), theta)[0]
+                         for i in range(R)])
+    _close(qkv2[:, :nh * hd].view(R, nh, hd), q_rot, torch.bfloat16, "q against plain", factor=3)
+    watch = n.KernelWatch()
+    watch.fetch()
+    torch.cuda.synchronize()
+    watch.check()
+
+
+def test_decode_chain_single_phases_and_refusals():
+    n = _native()
+    g = torch.Generator().manual_seed(3)
+    sync = torch.zeros(2, dtype=torch.int32, device=DEV)
+    for R, N, K in ((5, 1000, 328), (16, 256000, 256), (2, 48, 3072)):
+        x = torch.randn(R, K, generator=g).to(torch.bfloat16).to(DEV)
+        w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+        ref = x.double().cpu() @ w.double().cpu().T
+        out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
+        n.decode_chain([n.chain_product(x, w, out, n.EPI_SOFTCAP, 0.9)], R, sync)
+        _close(out, 0.9 * torch.tanh(ref / 0.9), torch.float32, f"capped 32-bit product {N}x{K}",
+               factor=20)
+    # a plain norm of chosen rows (what a model's last norm is)
+    h = torch.randn(6, 200, generator=g).to(DEV)
+    gain = (torch.randn(200, generator=g) * 0.2 + 1).to(DEV)
+    rows = torch.tensor([4, 0, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, 200, dtype=torch.bfloat16, device=DEV)
+    n.decode_chain([n.chain_norm(None, None, 0.0, h, gain, 1e-6, out, rows)], 3, sync)
+    _close(out, plain.rms_norm(h[rows.long()].double().cpu(), gain.double().cpu() - 1, 1e-6),
+           torch.bfloat16, "plain norm of chosen rows")
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(n.KernelError, match="1 to 16"):
+        n.decode_chain([n.chain_product(x, w, torch.empty(17, 32, dtype=torch.bfloat16, device=DEV))],
+                       17, sync)
+    ph = n.chain_product(x[:2], w, torch.empty(2, 32, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(n.KernelError, match="phases"):
+        n.decode_chain([ph] * 9, 2, sync)
+    assert sync.tolist() == [0, 0]
+
+
 def test_skinny_linear_refuses_what_it_cannot_do():
     n = _native()
     x = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)
