@@ -29,6 +29,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 #endif
 
 bool sib_chained_launches();   // false when the environment sets SIB_CHAINED_LAUNCH=0
+int sib_carveout();            // the shared-memory carve-out (percent) every kernel asks for, or -1
+
+// Every kernel of a step asks for the same split of an SM's memory between shared memory
+// and L1: a kernel that needs another split than its predecessor cannot start under it.
+template <typename K> inline void sib_same_carveout(K kernel) {
+    const int c = sib_carveout();
+    if (c >= 0) cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, c);
+}
 
 // Kernels whose waits are bounded (mbarrier waits of the tcgen05 kernels) leave a code in
 // "their" word of a small per-device table when a wait ran out.  The table is allocated
@@ -54,6 +62,7 @@ inline cudaError_t sib_launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = sib_chained_launches() ? 1 : 0;
+    sib_same_carveout(kernel);
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -635,6 +635,7 @@ SIB_EXPORT int sib_decode_chain(const SibChainPhase* phases, int n_phases, int R
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = sib_chained_launches() ? 1 : 0;
+    sib_same_carveout(kernel);
     e = cudaLaunchKernelEx(&cfg, kernel, ch);
     if (e != cudaSuccess) {
         sib_set_error("decode_chain: launch failed: %s", cudaGetErrorString(e));

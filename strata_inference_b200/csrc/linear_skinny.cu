@@ -298,6 +298,7 @@ static int launch_skinny(const void* W, const void* x, void* y, int R, int N, in
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = sib_chained_launches() ? 2 : 1;
+    sib_same_carveout(kernel);
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)W,
                                        (const __nv_bfloat16*)x, (OutT*)y, R, N, K, x_stride,
                                        y_stride, cap, ksplit, rope);

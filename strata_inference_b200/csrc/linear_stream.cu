@@ -27,6 +27,8 @@
 // device's error word for this kernel (the host reports it) and the block winds down.
 // Plain counterpart: tests/plain_gemma2.py (x @ W.T), gelu_tanh(), lm_head().
 // Reference: src/model/layer.rs:22-43 (x . W^T, weights [out, in]).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -278,6 +280,7 @@ int launch_stream(const CUtensorMap& wmap, const StreamArgs& p, size_t smem, cud
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = sib_chained_launches() ? 2 : 1;
+    sib_same_carveout(kernel);
     e = cudaLaunchKernelEx(&cfg, kernel, wmap, p);
     if (e != cudaSuccess) {
         sib_set_error("linear_stream: launch failed: %s", cudaGetErrorString(e));
@@ -343,7 +346,17 @@ SIB_EXPORT int sib_linear_stream(const void* W, const void* x, void* y, int out_
     // the block's activations must fit beside the ring: split k further if they do not
     while (stream_smem(NT, KT, ks, 2) > 200 * 1024 && ks < 8 && ks < KT) ++ks;
     const int kt_per = (KT + ks - 1) / ks;
-    int st = stages > 0 ? stages : 6;
+    static int env_stages = -1, env_ks = -1;
+    if (env_stages < 0) {
+        const char* v = getenv("SIB_LS_STAGES");
+        env_stages = v ? atoi(v) : 0;
+        const char* k = getenv("SIB_LS_KSPLIT");
+        env_ks = k ? atoi(k) : 0;
+    }
+    if (ksplit == 0 && env_ks > 0 && tiles < g_ls_sm_count[dev] / 2) {
+        ks = env_ks > KT ? KT : env_ks;
+    }
+    int st = stages > 0 ? stages : (env_stages > 0 ? env_stages : 6);
     if (st > kt_per) st = kt_per;
     while (st > 2 && stream_smem(NT, KT, ks, st) > 200 * 1024) --st;
     const size_t smem = stream_smem(NT, KT, ks, st);

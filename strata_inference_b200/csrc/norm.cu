@@ -203,6 +203,74 @@ add_rms_norm_bf16_warp_kernel(const __nv_bfloat16* __restrict__ a, const float* 
     }
 }
 
+// One block per row, one 8-element group per thread, the row in registers: every load of a
+// row is issued before anything is computed (the gains even before the kernel ahead of this
+// one has finished), so a row costs two block-wide sums and no pass over shared memory.
+__global__ void __launch_bounds__(1024)
+add_rms_norm_bf16_group_kernel(const __nv_bfloat16* __restrict__ a, const float* __restrict__ post_gain,
+                               float post_eps, float* __restrict__ h,
+                               const float* __restrict__ pre_gain, float pre_eps,
+                               __nv_bfloat16* __restrict__ out, int hidden) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    const int c = 8 * threadIdx.x;
+    const bool live = c < hidden;
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+    float4 pg0 = one, pg1 = one, qg0 = one, qg1 = one;
+    if (live && post_gain) {
+        pg0 = *reinterpret_cast<const float4*>(post_gain + c);
+        pg1 = *reinterpret_cast<const float4*>(post_gain + c + 4);
+    }
+    if (live && pre_gain) {
+        qg0 = *reinterpret_cast<const float4*>(pre_gain + c);
+        qg1 = *reinterpret_cast<const float4*>(pre_gain + c + 4);
+    }
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * hidden + c;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    float4 h0 = make_float4(0.f, 0.f, 0.f, 0.f), h1 = h0;
+    if (live) {
+        raw = *reinterpret_cast<const uint4*>(a + base);
+        h0 = *reinterpret_cast<const float4*>(h + base);
+        h1 = *reinterpret_cast<const float4*>(h + base + 4);
+    }
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        v[2 * k] = __uint_as_float(w[k] << 16);
+        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        ss += v[2 * k] * v[2 * k] + v[2 * k + 1] * v[2 * k + 1];
+    }
+    if (post_gain) {
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)hidden + post_eps);
+        v[0] *= inv * pg0.x; v[1] *= inv * pg0.y; v[2] *= inv * pg0.z; v[3] *= inv * pg0.w;
+        v[4] *= inv * pg1.x; v[5] *= inv * pg1.y; v[6] *= inv * pg1.z; v[7] *= inv * pg1.w;
+    }
+    h0.x += v[0]; h0.y += v[1]; h0.z += v[2]; h0.w += v[3];
+    h1.x += v[4]; h1.y += v[5]; h1.z += v[6]; h1.w += v[7];
+    if (live) {
+        *reinterpret_cast<float4*>(h + base) = h0;
+        *reinterpret_cast<float4*>(h + base + 4) = h1;
+    }
+    if (!pre_gain) return;
+    float ss2 = h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
+                h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)hidden + pre_eps);
+    if (live) {
+        const __nv_bfloat162 o0 = __floats2bfloat162_rn(h0.x * inv2 * qg0.x, h0.y * inv2 * qg0.y);
+        const __nv_bfloat162 o1 = __floats2bfloat162_rn(h0.z * inv2 * qg0.z, h0.w * inv2 * qg0.w);
+        const __nv_bfloat162 o2 = __floats2bfloat162_rn(h1.x * inv2 * qg1.x, h1.y * inv2 * qg1.y);
+        const __nv_bfloat162 o3 = __floats2bfloat162_rn(h1.z * inv2 * qg1.z, h1.w * inv2 * qg1.w);
+        *reinterpret_cast<uint4*>(out + base) =
+            make_uint4(*reinterpret_cast<const uint32_t*>(&o0), *reinterpret_cast<const uint32_t*>(&o1),
+                       *reinterpret_cast<const uint32_t*>(&o2), *reinterpret_cast<const uint32_t*>(&o3));
+    }
+}
+
 template <int NG>
 static int launch_warp_norm(const void* a, const float* post_gain, float post_eps, float* h,
                             const float* pre_gain, float pre_eps, void* out, int n_rows,
@@ -211,6 +279,25 @@ static int launch_warp_norm(const void* a, const float* post_gain, float post_ep
                        (const __nv_bfloat16*)a, post_gain, post_eps, h, pre_gain, pre_eps,
                        (__nv_bfloat16*)out, n_rows);
     return sib_check_launch("add_rms_norm");
+}
+
+#include <stdlib.h>
+#include <string.h>
+
+// SIB_NORM_KERNEL=warp keeps the warp-per-row kernel for many rows.
+static int norm_kernel_mode() {
+    const char* v = getenv("SIB_NORM_KERNEL");
+    return (v && strcmp(v, "warp") == 0) ? 1 : 0;
+}
+// From this many rows on the group-per-thread kernel runs (SIB_NORM_GROUP_ROWS overrides).
+static int group_rows_threshold() {
+    static int t = -1;
+    if (t < 0) {
+        const char* v = getenv("SIB_NORM_GROUP_ROWS");
+        t = v ? atoi(v) : 32;
+        if (t < 1) t = 1;
+    }
+    return t;
 }
 
 static int norm_threads(int hidden) {
@@ -275,8 +362,16 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
     if (dtype == SIB_BF16 && hidden % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
         ((uintptr_t)h % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
         ((uintptr_t)post_gain % 16) == 0 && ((uintptr_t)pre_gain % 16) == 0) {
-        // many rows: a warp per row keeps the device full without block barriers; few rows
-        // (decoding): a block per row has the shorter latency
+        // many rows: a block per row with one 8-element group per thread, every load issued
+        // at once (SIB_NORM_KERNEL=warp: a warp per row, the row in registers)
+        static const int mode = norm_kernel_mode();
+        if (n_rows >= group_rows_threshold() && hidden / 8 <= 1024 && mode != 1) {
+            const int threads = (hidden / 8 + 31) / 32 * 32;
+            sib_launch_chained(add_rms_norm_bf16_group_kernel, dim3(n_rows), dim3(threads), 0,
+                               (cudaStream_t)stream, (const __nv_bfloat16*)a, post_gain, post_eps, h,
+                               pre_gain, pre_eps, (__nv_bfloat16*)out, hidden);
+            return sib_check_launch("add_rms_norm");
+        }
         if (n_rows >= 512 && hidden % 256 == 0 && hidden / 256 <= 18) {
             cudaStream_t s = (cudaStream_t)stream;
 #define NORM_CASE(NG) \

@@ -82,7 +82,11 @@ __global__ void rope_store_kernel(RopeStoreArgs p) {
 // head rotated.  One block per row; a thread takes 8 pairs (x[i..i+8) with
 // x[i+half..i+half+8)) of a q or k head, or 8 elements of a v head.
 // A row's units of work are dealt out over the threads of gridDim.y blocks.
+// TABLE: the block first puts the row's cosines and sines (one pair per rotated pair of
+// a head: the same for every head) into shared memory; else every unit takes its own.
+template <bool TABLE>
 __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
+    extern __shared__ float2 cs_table[];       // [head_dim / 2] (cos, sin), with TABLE
     pdl_trigger();
     const int r = blockIdx.x;
     const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
@@ -105,6 +109,13 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
             cell_off = ((size_t)page * p.n_kv * p.page_tokens + cell % p.page_tokens) * hd;
         }
     }
+    if (TABLE) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float ang = (float)pos * p.inv_freq[i];
+            cs_table[i] = make_float2(cosf(ang), sinf(ang));
+        }
+        __syncthreads();
+    }
     // (positions, slots and page tables are written by the host before the step: only from
     // here on does the kernel need what the kernel before it wrote)
     pdl_wait();
@@ -124,8 +135,16 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
             float ra[2], rb[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float ang = (float)pos * p.inv_freq[i0 + 2 * k + e];
-                const float c = cosf(ang), s = sinf(ang);
+                float c, s;
+                if (TABLE) {
+                    const float2 t = cs_table[i0 + 2 * k + e];
+                    c = t.x;
+                    s = t.y;
+                } else {
+                    const float ang = (float)pos * p.inv_freq[i0 + 2 * k + e];
+                    c = cosf(ang);
+                    s = sinf(ang);
+                }
                 ra[e] = a[e] * c - bq[e] * s;
                 rb[e] = a[e] * s + bq[e] * c;
             }
@@ -180,10 +199,15 @@ SIB_EXPORT int sib_rope_store(void* qkv, int dtype, const int* row_pos, const in
         // sines and cosines of a row are not one block's serial work
         const int units = (n_heads + n_kv) * (head_dim / 16);
         if (rows < 64)
-            sib_launch_chained(rope_store_bf16_kernel, dim3(rows, (units + 31) / 32), dim3(32), 0,
-                               (cudaStream_t)stream, p);
+            sib_launch_chained(rope_store_bf16_kernel<false>, dim3(rows, (units + 31) / 32), dim3(32),
+                               0, (cudaStream_t)stream, p);
+        else if (head_dim <= 4096)
+            // many rows: a block per row shares one table of the row's cosines and sines
+            sib_launch_chained(rope_store_bf16_kernel<true>, dim3(rows), dim3(128),
+                               (size_t)(head_dim / 2) * sizeof(float2), (cudaStream_t)stream, p);
         else
-            sib_launch_chained(rope_store_bf16_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, p);
+            sib_launch_chained(rope_store_bf16_kernel<false>, dim3(rows), dim3(128), 0,
+                               (cudaStream_t)stream, p);
         return sib_check_launch("rope_store");
     }
     int threads = 32;

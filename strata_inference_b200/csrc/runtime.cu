@@ -32,6 +32,16 @@ bool sib_chained_launches() {
     return enabled == 1;
 }
 
+int sib_carveout() {
+    static int value = -2;
+    if (value == -2) {
+        const char* v = getenv("SIB_CARVEOUT");
+        value = v ? atoi(v) : -1;
+        if (value > 100) value = 100;
+    }
+    return value;
+}
+
 SIB_EXPORT const char* sib_last_error() { return g_error; }
 
 // The architecture this library was compiled for; the loader refuses any other.

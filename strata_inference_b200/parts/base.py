@@ -80,7 +80,7 @@ class Runtime:
         # into registers.  Alone it is the faster of the two on most shapes; inside a chained
         # step it is slower (2B shape, batch 8: 3.29 against 2.51 ms), because a block of it
         # needs a third of an SM's shared memory before it can start under its predecessor.
-        self.stream_products = os.environ.get("SIB_LINEAR_STREAM", "0") == "1"
+        self.stream_products = os.environ.get("SIB_LINEAR_STREAM", "0")
         # SIB_FUSE_ROTATION=0: rotation and cache write always run as a kernel of their own
         self.fuse_rotation = os.environ.get("SIB_FUSE_ROTATION", "1") != "0"
         # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
@@ -189,7 +189,9 @@ class Runtime:
         if (x.dtype == torch.bfloat16 and 0 < R <= self.skinny_max_rows and K % 8 == 0
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
-            if self.stream_products:
+            mode = self.stream_products
+            if mode == "1" or (mode == "down" and K >= 2 * N) or (mode == "small" and N * K < 30e6) \
+                    or (mode == "notgu" and epilogue != native.EPI_GEGLU and N < 100000):
                 return native.linear_stream(x, w, out, epilogue, cap)
             return native.skinny_linear(x, w, out, epilogue, cap)
         aligned = (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
