@@ -357,6 +357,41 @@ def run_ours(args):
     return 0
 
 
+def run_kernel_tables(args):
+    """Where the step's time goes: the decode step of the timed run (same shape, batch and
+    context) captured with an event before and after every kernel, and one prompt step."""
+    import torch
+    from strata_inference_b200 import GenerationEngine
+    from strata_inference_b200.engine.profile import (format_table, load_peaks,
+                                                      profile_decode_graph, profile_prompt_graph)
+    cfg = baseline_config()
+    cfg.update(SHAPES[args.shape])
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    context, batch = args.context, args.batch
+    gen = GenerationEngine.from_random(cfg, seed=5, dtype="bfloat16", ctx=context,
+                                       max_tokens=batch * context, max_slots=batch)
+    engine = gen.engine
+    randomize_pools(engine)
+    peaks = load_peaks()
+    slots = [engine.new_sequence() for _ in range(batch)]
+    fill_context(engine, slots, context - 16)
+    rows, ms = profile_decode_graph(engine, slots, [5] * batch)
+    print(format_table(f"Gemma2-{args.shape.upper()} shape, {cfg['num_hidden_layers']} layers: "
+                       f"captured decode step, batch {batch}, {context - 16} positions each", rows,
+                       ms, peaks))
+    for s in slots:
+        engine.end_sequence(s)
+    T = 2048
+    toks = torch.randint(0, engine.vocab_size, (T,), generator=torch.Generator().manual_seed(4)).tolist()
+    slot = engine.new_sequence()
+    rows, ms = profile_prompt_graph(engine, slot, toks)
+    engine.end_sequence(slot)
+    print(format_table(f"prompt step, {T} tokens (captured; the events between the kernels keep "
+                       f"them from overlapping)", rows, ms, peaks))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,6 +403,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the named configuration (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--kernels", action="store_true",
+                    help="instead of the timed run: per-kernel tables (CUDA events around every "
+                         "kernel) of the captured decode step at --batch and of a 2,048-token "
+                         "prompt step, on standard output")
     ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
                     help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
@@ -382,6 +421,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.kernels:
+        return run_kernel_tables(args)
     return run_ours(args)
 
 

@@ -75,16 +75,13 @@ def _print_kernel_tables(engine, prompt: List[int]) -> None:
     """The first request's prompt as one step and one single-token step after it, run once
     more with CUDA events around every kernel."""
     from .engine.profile import (format_table, load_peaks, profile_decode_graph,
-                                 profile_step)
+                                 profile_prompt_graph)
     peaks = load_peaks()
     slot = engine.new_sequence()
     try:
-        for _ in range(2):                        # the first run pays one-time set-ups
-            rows, ms = profile_step(lambda: engine.step([(slot, prompt)]))
-            if _ == 0:
-                engine.end_sequence(slot)
-                slot = engine.new_sequence()
-        print(format_table(f"prompt step, {len(prompt)} tokens", rows, ms, peaks), file=sys.stderr)
+        rows, ms = profile_prompt_graph(engine, slot, prompt)
+        print(format_table(f"prompt step, {len(prompt)} tokens (captured, events between the "
+                           f"kernels)", rows, ms, peaks), file=sys.stderr)
         if engine.length(slot) + 5 < engine.max_seq_len:
             rows, ms = profile_decode_graph(engine, [slot], [prompt[-1]])
             print(format_table(f"single-token step near position {engine.length(slot)} "

@@ -71,6 +71,37 @@ def profile_decode_graph(engine, slots, tokens, replays: int = 3) -> Tuple[List[
     return rows, begin.elapsed_time(end)
 
 
+def profile_prompt_graph(engine, slot: int, tokens, replays: int = 3) -> Tuple[List[Dict], float]:
+    """A prompt step (``tokens`` for the fresh sequence ``slot``, the last row's logits) with
+    an event before and after every kernel, captured into a CUDA graph and replayed, so
+    that the host's launch times are not in the figures.  The sequence is advanced once."""
+    import torch
+    ctx = engine._context([(slot, list(tokens))], None)
+    engine.cache.sync_tables()
+
+    def forward():
+        h = engine.model.hidden_states(ctx)
+        return engine.model.logits(h, ctx.want_rows)
+    forward()
+    with native.KernelProfile() as eager:
+        forward()
+    n = len(eager.events)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with native.KernelProfile(plan=eager) as captured:
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            forward()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(replays):
+        if i == replays - 1:
+            begin.record()
+        graph.replay()
+    end.record()
+    rows = captured.rows(last=n)
+    engine.cache.advance(slot, len(tokens))
+    return rows, begin.elapsed_time(end)
+
+
 def format_table(title: str, rows: List[Dict], total_ms: float, peaks: Dict) -> str:
     lines = [f"[profile] {title}: {total_ms * 1e3:.0f} us on the device, "
              f"{sum(r['calls'] for r in rows)} launches; fractions of {peaks['source']} peaks "
