@@ -14,6 +14,16 @@ masked; softmax; weighted sum of v; output projection.
 A step whose sequences all begin at position 0 (prompts) attends over the
 step's own k and v rows; any other step attends over the cache.  A run that
 borrows another schedule entry's cache projects q only and reads that cache.
+
+Fast paths inside this general part (each falls back to the general kernels
+when its condition does not hold, with the same result): for at most 16
+bfloat16 rows, a position part that offers ``rotary()`` with half-split pairs
+over the WHOLE head lets the q|k|v product rotate and store in its own
+epilogue (partial rotary or interleaved pairs take the product and then the
+rotate-and-store kernel); prompts take the tcgen05 attention for head sizes
+64/128/256 with at most two query heads per kv head, else the mma.sync
+kernel, else the general one; single rows over the cache take the
+bandwidth-tuned kernel for head sizes 64/128/256 and groups of 1, 2, 4 or 8.
 """
 
 from __future__ import annotations

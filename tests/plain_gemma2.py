@@ -8,7 +8,9 @@ sequence from scratch with dense CPU tensor arithmetic.
 It rests on the formulas of strata-ai-labs/strata-inference (a Rust crate:
 its model code can be neither imported nor compiled where these tests run, so
 nothing here was checked against its binaries).  Each function cites the file
-and lines of that project that it restates.  Four formulas are not in that
+and lines of that project that it restates; tests/test_reference_cases.py
+applies the inputs and expectations of that project's own unit tests of these
+operations to the functions below.  Four formulas are not in that
 project's Gemma2 path and are stated here from the architecture's definition
 instead: the ``1 + w`` gain of the RMS norms, the ``query_pre_attn_scalar``
 score scale, the alternation of sliding and global layers, and the soft cap
