@@ -42,6 +42,10 @@ struct AttnDecodeArgs {
     int max_pages, page_tokens, ring_tokens;
     int window, splits;
     float scale, softcap;
+    // The kernel before this one wrote at most the last `fresh` positions of a row's sequence
+    // (1 in a single-token step): tiles of keys below them may be loaded before that kernel
+    // has finished.  0: every load waits for it.
+    int fresh;
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -73,8 +77,11 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
 // The most splits of a (row, kv head) a launch takes.
 constexpr int MAX_SPLITS = 128;
 
-// HD: head size (64, 128 or 256).  G: query heads per kv head (1, 2, 4 or 8).
-template <int HD, int G>
+// HD: head size (64, 128 or 256).  G: query heads per kv head (1, 2, 4 or 8).  EARLY: the first
+// tile of keys may be fetched before the kernel ahead of this one has finished (it shortens
+// the chain of waits of a step of one or two rows; with more rows the registers that the
+// tile holds across the wait cost more than the wait: batch 8 ran 2 % slower with it).
+template <int HD, int G, bool EARLY>
 __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p) {
     constexpr int KB = HD / 32;          // 32-wide blocks of the head dimension
     constexpr int LPK = HD / 8;          // lanes that cover one value row
@@ -111,6 +118,32 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
         const int cell0 = p.ring_tokens > 0 ? (t0 << 4) % p.ring_tokens : (t0 << 4);
         asm volatile("prefetch.global.L1 [%0];\n" ::"l"(table + cell0 / p.page_tokens));
     }
+    // One tile of keys and values: every load is issued before anything waits on one.
+    uint4 ka_r[KB], kb_r[KB], v_r[16 / KPP];
+    const int sub = lane / LPK;          // which key of a pass this lane works on
+    const int dim0 = (lane % LPK) * 8;   // its 8 dimensions
+    auto load_tile = [&](int tile) {
+        const int base = tile << 4;
+        const int cell = p.ring_tokens > 0 ? base % p.ring_tokens : base;
+        const int page = table[cell / p.page_tokens];
+        const size_t tile_off =
+            (((size_t)page * p.n_kv + kvh) * p.page_tokens + cell % p.page_tokens) * HD;
+        const __nv_bfloat16* kt = p.k_pool + tile_off;
+        const __nv_bfloat16* vt = p.v_pool + tile_off;
+        const int last = pos - base;                              // keys beyond `last` do not exist
+        const int ka = min(g, last), kb2 = min(g + 8, last);      // clamped: loads stay in the sequence
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+            ka_r[j] = ld_stream16(kt + (size_t)ka * HD + 32 * j + 8 * t);
+            kb_r[j] = ld_stream16(kt + (size_t)kb2 * HD + 32 * j + 8 * t);
+        }
+#pragma unroll
+        for (int i = 0; i < 16 / KPP; ++i)
+            v_r[i] = ld_stream16(vt + (size_t)min(i * KPP + sub, last) * HD + dim0);
+    };
+    // the first tile's keys and values, if the kernel before this one cannot have written them
+    const bool early = EARLY && p.fresh > 0 && t0 < t1 && (t0 << 4) + 15 < pos - p.fresh + 1;
+    if (early) load_tile(t0);
     pdl_wait();
 
     // query heads of this kv head as the B operand: lane (g, t) holds head g
@@ -131,30 +164,11 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p)
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
     }
-    const int sub = lane / LPK;          // which key of a pass this lane works on
-    const int dim0 = (lane % LPK) * 8;   // its 8 dimensions
 
     for (int tile = t0; tile < t1; ++tile) {
         const int base = tile << 4;                               // first position of the tile
-        const int cell = p.ring_tokens > 0 ? base % p.ring_tokens : base;
-        const int page = table[cell / p.page_tokens];
-        const size_t tile_off =
-            (((size_t)page * p.n_kv + kvh) * p.page_tokens + cell % p.page_tokens) * HD;
-        const __nv_bfloat16* kt = p.k_pool + tile_off;
-        const __nv_bfloat16* vt = p.v_pool + tile_off;
-        const int last = pos - base;                              // keys beyond `last` do not exist
+        if (!(early && tile == t0)) load_tile(tile);
         // ---- scores: 16 keys x G heads ----
-        const int ka = min(g, last), kb2 = min(g + 8, last);      // clamped: loads stay in the sequence
-        // every load of the tile is issued before anything waits on one
-        uint4 ka_r[KB], kb_r[KB], v_r[16 / KPP];
-#pragma unroll
-        for (int j = 0; j < KB; ++j) {
-            ka_r[j] = ld_stream16(kt + (size_t)ka * HD + 32 * j + 8 * t);
-            kb_r[j] = ld_stream16(kt + (size_t)kb2 * HD + 32 * j + 8 * t);
-        }
-#pragma unroll
-        for (int i = 0; i < 16 / KPP; ++i)
-            v_r[i] = ld_stream16(vt + (size_t)min(i * KPP + sub, last) * HD + dim0);
         float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < KB; ++j) {
@@ -353,7 +367,7 @@ SIB_EXPORT int sib_attention_decode_resident_warps(int n_heads, int n_kv, int he
     int per_sm = 0;
     cudaError_t e = cudaErrorInvalidValue;
 #define ASK(HD, GG)                                                                         \
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, GG>, 128, \
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, GG, false>, 128, \
                                                       (size_t)4 * GG * (HD + 2) * sizeof(float))
 #define BY_G(HD)                    \
     do {                            \
@@ -371,11 +385,12 @@ SIB_EXPORT int sib_attention_decode_resident_warps(int n_heads, int n_kv, int he
     return per_sm * 4 * sms;
 }
 
-SIB_EXPORT int sib_attention_decode(
+static int attention_decode(
     const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
     int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
     const int* seq_slot, void* out, float* partial, int* tickets, int rows, int n_heads, int n_kv,
-    int head_dim, float scale, float softcap, int window, int splits, int warps, void* stream) {
+    int head_dim, float scale, float softcap, int window, int splits, int warps, int fresh,
+    void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(sib_attention_decode_supports(n_heads, n_kv, head_dim, page_tokens),
                 "attention_decode: heads=%d kv_heads=%d head_dim=%d page_tokens=%d is not a shape "
@@ -399,14 +414,21 @@ SIB_EXPORT int sib_attention_decode(
     AttnDecodeArgs p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                      (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, partial, tickets, row_pos, row_seq,
                      seq_slot, page_table, q_stride, rows, n_heads, n_kv, max_pages, page_tokens,
-                     ring_tokens, window, splits, scale, softcap};
+                     ring_tokens, window, splits, scale, softcap, fresh};
     const long long blocks = (long long)rows * n_kv * splits;
     SIB_REQUIRE(blocks < (1ll << 31), "attention_decode: too many rows (%d)", rows);
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;
-#define GO(HD, GG) \
-    sib_launch_chained(attention_decode_kernel<HD, GG>, dim3((unsigned)blocks), dim3(32 * warps), \
-                       (size_t)warps * GG * (HD + 2) * sizeof(float), s, p)
+    const bool early_keys = fresh > 0 && rows <= 2;
+#define GO(HD, GG)                                                                                 \
+    do {                                                                                           \
+        if (early_keys)                                                                            \
+            sib_launch_chained(attention_decode_kernel<HD, GG, true>, dim3((unsigned)blocks),      \
+                               dim3(32 * warps), (size_t)warps * GG * (HD + 2) * sizeof(float), s, p); \
+        else                                                                                       \
+            sib_launch_chained(attention_decode_kernel<HD, GG, false>, dim3((unsigned)blocks),     \
+                               dim3(32 * warps), (size_t)warps * GG * (HD + 2) * sizeof(float), s, p); \
+    } while (0)
 #define BY_G(HD)                  \
     do {                          \
         if (G == 1) GO(HD, 1);    \
@@ -420,6 +442,32 @@ SIB_EXPORT int sib_attention_decode(
 #undef BY_G
 #undef GO
     return sib_check_launch("attention_decode");
+}
+
+SIB_EXPORT int sib_attention_decode(
+    const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+    int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
+    const int* seq_slot, void* out, float* partial, int* tickets, int rows, int n_heads, int n_kv,
+    int head_dim, float scale, float softcap, int window, int splits, int warps, void* stream) {
+    return attention_decode(q, q_stride, k_pool, v_pool, page_table, max_pages, page_tokens,
+                            ring_tokens, row_pos, row_seq, seq_slot, out, partial, tickets, rows,
+                            n_heads, n_kv, head_dim, scale, softcap, window, splits, warps, 0, stream);
+}
+
+// The same for a caller that knows how many positions per sequence the kernel before this
+// one has written at most (`fresh`: the largest number of rows a sequence has in this step;
+// the keys and values below them are older than that kernel and are fetched while it runs).
+SIB_EXPORT int sib_attention_decode_fresh(
+    const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+    int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
+    const int* seq_slot, void* out, float* partial, int* tickets, int rows, int n_heads, int n_kv,
+    int head_dim, float scale, float softcap, int window, int splits, int warps, int fresh,
+    void* stream) {
+    SIB_REQUIRE(fresh >= 0, "attention_decode: %d fresh positions", fresh);
+    return attention_decode(q, q_stride, k_pool, v_pool, page_table, max_pages, page_tokens,
+                            ring_tokens, row_pos, row_seq, seq_slot, out, partial, tickets, rows,
+                            n_heads, n_kv, head_dim, scale, softcap, window, splits, warps, fresh,
+                            stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -436,18 +436,21 @@ def attention_decode_resident_warps(n_heads: int, n_kv: int, head_dim: int) -> i
 
 @_timed(lambda q, q_stride, k_pool, v_pool, page_table, page_tokens, ring_tokens, row_pos, row_seq,
         seq_slot, out, scratch, tickets, n_heads, n_kv, head_dim, scale, softcap, window, splits,
-        warps=4: _attention_cache_work("attention_decode", row_pos, k_pool, n_heads, head_dim,
-                                       window, out.shape[0]))
+        warps=4, fresh=0: _attention_cache_work("attention_decode", row_pos, k_pool, n_heads,
+                                                head_dim, window, out.shape[0]))
 def attention_decode(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                      page_table: torch.Tensor, page_tokens: int, ring_tokens: int, row_pos,
                      row_seq, seq_slot, out: torch.Tensor, scratch: Optional[torch.Tensor],
                      tickets: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
                      scale: float, softcap: float, window: int, splits: int,
-                     warps: int = 4) -> torch.Tensor:
+                     warps: int = 4, fresh: int = 0) -> torch.Tensor:
     """Attention of single rows over the bfloat16 cache (see csrc/attention_decode.cu).
     ``splits`` blocks of ``warps`` warps share the keys of a (row, kv head); with more than one they
     need ``scratch`` for their partial results and ``tickets``: int32 counters, one
-    per (row, kv head), zero before the first call (every call leaves them zero)."""
+    per (row, kv head), zero before the first call (every call leaves them zero).
+    ``fresh``: the most positions of a sequence that the kernel before this one wrote (the
+    rows a sequence has in this step); keys below them are fetched while that kernel still
+    runs.  0: every load waits for it."""
     global _launches
     rows = out.shape[0]
     _want(out, torch.bfloat16, "out")
@@ -464,12 +467,12 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_poo
             raise KernelError(f"attention_decode: {need} bytes of scratch memory are needed")
         if tickets is None or tickets.dtype != torch.int32 or tickets.numel() < rows * n_kv:
             raise KernelError(f"attention_decode: {rows * n_kv} int32 ticket counters are needed")
-    _check(library().sib_attention_decode(
+    _check(library().sib_attention_decode_fresh(
         _ptr(q), c_int(q_stride), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
         c_int(page_table.shape[1]), c_int(page_tokens), c_int(ring_tokens), _ptr(row_pos),
         _ptr(row_seq), _ptr(seq_slot), _ptr(out), _ptr(scratch), _ptr(tickets), c_int(rows),
         c_int(n_heads), c_int(n_kv), c_int(head_dim), c_float(scale), c_float(softcap),
-        c_int(window), c_int(splits), c_int(warps), _stream()))
+        c_int(window), c_int(splits), c_int(warps), c_int(fresh), _stream()))
     return out
 
 

@@ -216,7 +216,8 @@ class Attention:
             native.attention_decode(qkv, width, view.k, view.v, view.page_table, view.page_tokens,
                                     view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot, out,
                                     scratch, tickets, nh, self.nkv, hd, self.scale, self.softcap,
-                                    self.window, splits, warps)
+                                    self.window, splits, warps,
+                                    fresh=ctx.max_count if rt.early_keys else 0)
         else:
             splits = self._splits(ctx, ctx.cache.max_seq_len)
             scratch = None

@@ -86,6 +86,9 @@ class Runtime:
         # from this many rows on the gate/up product with its gated epilogue (pairs of SMs,
         # 256 x 256 tiles) beats the library product followed by the activation kernel
         self.gated_gemm_min_rows = 128
+        # SIB_EARLY_KEYS=0: the attention over the cache fetches no keys before the kernel ahead
+        # of it has finished
+        self.early_keys = os.environ.get("SIB_EARLY_KEYS", "1") != "0"
         # SIB_DECODE_CHAIN=1: the steps between two attention kernels of a step of few rows run
         # as ONE chain kernel (csrc/decode_chain.cu) instead of one kernel each.  Measured on
         # the Gemma2-2B shape it is the slower of the two so far (a layer's products and norms:
