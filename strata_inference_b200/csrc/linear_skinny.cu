@@ -226,8 +226,8 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
                 if (head >= rope.n_heads && rope.k_pool) {
                     const int b = rope.row_seq[r];
                     int cell = pos;
-                    bool keep = true;
-                    if (rope.ring_tokens > 0) {
+                    bool keep = rope.seq_slot[b] >= 0;     // (a padding row's sequence holds no slot)
+                    if (keep && rope.ring_tokens > 0) {
                         keep = pos >= rope.seq_end[b] - rope.ring_tokens;
                         cell = pos % rope.ring_tokens;
                     }

@@ -44,9 +44,9 @@ __global__ void rope_store_kernel(RopeStoreArgs p) {
     T* dst = nullptr;
     if (is_kv && p.k_pool) {
         const int b = p.row_seq[r];
-        bool keep = true;
+        bool keep = p.seq_slot[b] >= 0;      // (a padding row's sequence holds no slot)
         int cell = pos;
-        if (p.ring_tokens > 0) {
+        if (keep && p.ring_tokens > 0) {
             keep = pos >= p.seq_end[b] - p.ring_tokens;
             cell = pos % p.ring_tokens;
         }
@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs p) {
     if (p.k_pool) {
         const int b = p.row_seq[r];
         int cell = pos;
-        keep = true;
-        if (p.ring_tokens > 0) {
+        keep = p.seq_slot[b] >= 0;           // (a padding row's sequence holds no slot)
+        if (keep && p.ring_tokens > 0) {
             keep = pos >= p.seq_end[b] - p.ring_tokens;
             cell = pos % p.ring_tokens;
         }

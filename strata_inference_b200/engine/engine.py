@@ -16,6 +16,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.paged import SequenceCache
@@ -69,7 +70,11 @@ class Engine:
         self.rng_state = torch.ones(self.cache.max_slots, dtype=torch.int64, device=self.device)
         self.kernel_watch = native.KernelWatch()
         self._graphs: Dict[Tuple, "DecodeGraph"] = {}
-        self.max_graphs = 8     # captured steps kept (by batch size and sampling options)
+        self._prompt_graphs: Dict[Tuple, "PromptGraph"] = {}
+        # captured steps kept: single-token steps by batch size and sampling options, and
+        # as many steps of prompts by rows, sequences and wanted rows
+        self.max_graphs = 8
+        self.prompt_graph_rows = 1024   # steps of prompts of up to this many rows are recorded
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
 
     # ---- construction ----------------------------------------------------
@@ -110,8 +115,10 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step --------------------------------------------------------
-    def _context(self, entries: Sequence[Tuple[int, Sequence[int]]],
+    def _prepare(self, entries: Sequence[Tuple[int, Sequence[int]]],
                  want: Optional[Sequence[Sequence[int]]]):
+        """The step's sequences ``[(slot, start, count)]``, its token ids (one array) and
+        the packed indices of its wanted rows, all checked; nothing is reserved yet."""
         if not entries:
             raise StepError("a step needs at least one sequence")
         slots = [int(s) for s, _ in entries]
@@ -121,10 +128,10 @@ class Engine:
         if min(counts) <= 0:
             raise StepError("every sequence of a step needs at least one token")
         V = self.vocab_size
-        for _, toks in entries:
-            for t in toks:
-                if not 0 <= int(t) < V:
-                    raise StepError(f"input token ID {t} exceeds vocab_size {V}")
+        tokens = np.concatenate([np.asarray(toks, dtype=np.int64).reshape(-1) for _, toks in entries])
+        if tokens.size and not (0 <= tokens.min() and tokens.max() < V):
+            bad = tokens[(tokens < 0) | (tokens >= V)][0]
+            raise StepError(f"input token ID {bad} exceeds vocab_size {V}")
         starts = [self.cache.length(s) for s in slots]
         if any(st > 0 for st in starts):
             # (a step of prompts only attends over its own rows and may be of any length)
@@ -148,12 +155,27 @@ class Engine:
                                     f"of its sequence")
                 want_rows.append(row0 + int(w))
             row0 += c
-        self.cache.reserve(list(zip(slots, counts)))
-        seqs = list(zip(slots, starts, counts))
-        flat = StepContext.pack(seqs, [t for _, toks in entries for t in toks], want_rows)
-        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+        return list(zip(slots, starts, counts)), tokens, want_rows
+
+    def _context(self, entries: Sequence[Tuple[int, Sequence[int]]],
+                 want: Optional[Sequence[Sequence[int]]]):
+        seqs, tokens, want_rows = self._prepare(entries, want)
+        self.cache.reserve([(s, n) for s, _, n in seqs])
+        return self._step_context(seqs, tokens, want_rows)
+
+    def _step_context(self, seqs, tokens, want_rows) -> StepContext:
+        host = torch.from_numpy(StepContext.pack(seqs, tokens, want_rows)).pin_memory()
         meta = host.to(self.device, non_blocking=True)
         return StepContext(meta, seqs, len(want_rows), self.cache, self.rt)
+
+    def _recorded_prompts(self, seqs, n_rows: int, n_want: int) -> bool:
+        """Whether this step goes through a recorded prompt step: prompts from position 0
+        with more rows than the few-row kernels take and so few that launching them one by
+        one costs more than running them, and few wanted rows (a recorded step keeps a
+        logits buffer of that many rows)."""
+        return (self.prompt_graph_rows > 0 and self.model.captures_prompts
+                and self.rt.skinny_max_rows < n_rows <= self.prompt_graph_rows
+                and 0 < n_want <= 64 and all(st == 0 for _, st, _ in seqs))
 
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
@@ -164,19 +186,41 @@ class Engine:
         among ITS tokens of this step whose logits are returned (default: the
         last).  Returns ``[n_wanted, vocab]`` 32-bit logits on the device, in the
         order of the entries and of ``want`` (``None`` if nothing is wanted).
+
+        Short steps of prompts are recorded into a CUDA graph the second time their shape
+        (rows rounded up to 64, sequences, wanted rows) is seen and replayed from then on
+        (``prompt_graph_rows``: the most rows of such a step; 0: none are recorded).
         """
-        ctx = self._context(entries, want)
+        seqs, tokens, want_rows = self._prepare(entries, want)
+        self.cache.reserve([(s, n) for s, _, n in seqs])
         try:
-            self.cache.sync_tables()
-            h = self.model.hidden_states(ctx)
-            logits = self.model.logits(h, ctx.want_rows) if ctx.want_rows.numel() else None
+            if self._recorded_prompts(seqs, int(tokens.size), len(want_rows)):
+                logits = self._prompt_step(seqs, tokens, want_rows)
+            else:
+                ctx = self._step_context(seqs, tokens, want_rows)
+                self.cache.sync_tables()
+                h = self.model.hidden_states(ctx)
+                logits = self.model.logits(h, ctx.want_rows) if ctx.want_rows.numel() else None
         except BaseException:
-            for slot in ctx.slots:      # hand back the pages reserved for the failed step
+            for slot, _, _ in seqs:      # hand back the pages reserved for the failed step
                 self.cache.trim(slot)
             raise
-        for slot, n in zip(ctx.slots, ctx.counts):
+        for slot, _, n in seqs:
             self.cache.advance(slot, n)
         return logits
+
+    def _prompt_step(self, seqs, tokens, want_rows) -> torch.Tensor:
+        from .graph import PromptGraph
+        rows = -(-int(tokens.size) // 64) * 64
+        key = ("prompts", rows, len(seqs), len(want_rows))
+        g = self._prompt_graphs.pop(key, None)
+        if g is None:
+            g = PromptGraph(self, rows, len(seqs), len(want_rows))
+            while len(self._prompt_graphs) >= self.max_graphs:
+                self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+        self._prompt_graphs[key] = g       # most recently used last
+        # (the graph's buffer is overwritten by its next replay: the caller gets a copy)
+        return g.run(seqs, tokens, want_rows).clone()
 
     # ---- sampling --------------------------------------------------------
     def seed_sequence(self, slot: int, seed: int) -> None:

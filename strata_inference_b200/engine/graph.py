@@ -1,4 +1,4 @@
-"""Single-token steps replayed from a CUDA graph.
+"""Steps replayed from CUDA graphs: single-token steps, and short prompt steps.
 
 Decoding launches a few hundred small kernels per step; launched one by one
 from the host they cost more than they run.  A :class:`DecodeGraph` captures
@@ -8,6 +8,12 @@ positions, slots, page tables, generator states) lives in device buffers at
 fixed addresses that are refreshed before each replay, and no launch shape
 depends on the sequences' lengths.  The kernels are the ones ``Engine.step``
 launches.
+
+A :class:`PromptGraph` does the same for a step of prompts that all start at position 0
+and have few enough rows that launching them from the host costs more than running them:
+it is recorded for a number of sequences, a number of wanted rows and a number of rows
+rounded up, and a replay fills the rows that are left over with a sequence that holds no
+slot, whose keys and values are not stored.  No other row's result depends on those rows.
 """
 
 from __future__ import annotations
@@ -15,6 +21,7 @@ from __future__ import annotations
 import gc
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..kernels import native
@@ -80,7 +87,7 @@ class DecodeGraph:
         if self.copied[stage] is not None:
             self.copied[stage].synchronize()     # (long done unless the caller runs far ahead)
         h = self.hosts[stage]
-        h.copy_(torch.tensor(StepContext.pack(seqs, tokens, range(B)), dtype=torch.int32))
+        h.copy_(torch.from_numpy(StepContext.pack(seqs, tokens, range(B))))
         self.meta.copy_(h, non_blocking=True)
         if self.copied[stage] is None:
             self.copied[stage] = torch.cuda.Event()
@@ -112,6 +119,70 @@ class DecodeGraph:
                 try:
                     with torch.cuda.graph(g, capture_error_mode="thread_local"):
                         self.logits, self.out = self._forward(seqs, capture=True)
+                finally:
+                    if collecting:
+                        gc.enable()
+                self.graph = g
+        self.calls += 1
+        return result
+
+
+class PromptGraph:
+    """The step of ``n_seqs`` prompts from position 0 with ``rows`` rows in all (filled up
+    with the rows of one more sequence without a slot) and ``n_want`` wanted rows."""
+
+    def __init__(self, engine, rows: int, n_seqs: int, n_want: int):
+        self.engine = engine
+        self.rows, self.B, self.n_want = rows, n_seqs, n_want
+        size = StepContext.packed_size(rows, n_seqs + 1, n_want)
+        self.hosts = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
+        self.copied = [None] * _STAGES
+        self.meta = torch.zeros(size, dtype=torch.int32, device=engine.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.calls = 0
+
+    def _forward(self, seqs):
+        eng = self.engine
+        ctx = StepContext(self.meta, seqs, self.n_want, eng.cache, eng.rt, graph_capture=True,
+                          from_start=True)
+        return eng.model.logits(eng.model.hidden_states(ctx), ctx.want_rows)
+
+    def run(self, seqs, tokens: np.ndarray, want_rows: Sequence[int]) -> torch.Tensor:
+        """``seqs``: ``(slot, 0, count)`` of the prompts, whose pages are reserved; returns
+        the 32-bit logits of the wanted rows, in a buffer that a later run may overwrite."""
+        eng = self.engine
+        used = int(tokens.size)
+        if len(seqs) != self.B or len(want_rows) != self.n_want or used > self.rows:
+            raise ValueError(f"this graph steps {self.B} prompts of {self.rows} rows in all")
+        padded = list(seqs) + [(-1, 0, self.rows - used)]
+        tokens = np.concatenate([tokens, np.zeros(self.rows - used, dtype=np.int64)])
+        stage = self.calls % _STAGES
+        if self.copied[stage] is not None:
+            self.copied[stage].synchronize()
+        h = self.hosts[stage]
+        h.copy_(torch.from_numpy(StepContext.pack(padded, tokens, want_rows)))
+        self.meta.copy_(h, non_blocking=True)
+        if self.copied[stage] is None:
+            self.copied[stage] = torch.cuda.Event()
+        self.copied[stage].record()
+        eng.cache.sync_tables()
+        if self.graph is not None:
+            self.graph.replay()
+            result = self.logits
+        else:
+            # Launched one by one, under the rules of a recorded step, the first two times
+            # (which warms up what the step uses); the second time the same launches are
+            # also recorded for the steps to come, which runs nothing.
+            result = self._forward(padded)
+            if self.calls >= 1:
+                g = torch.cuda.CUDAGraph()
+                collecting = gc.isenabled()
+                gc.collect()
+                gc.disable()       # (see DecodeGraph: nothing else may touch CUDA meanwhile)
+                try:
+                    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                        self.logits = self._forward(padded)
                 finally:
                     if collecting:
                         gc.enable()

@@ -135,6 +135,16 @@ class DecoderModel:
                          else self.blocks[e.layer].mixer.cache_need())
         return needs
 
+    @property
+    def captures_prompts(self) -> bool:
+        """Whether every part promises that a recorded step of prompts may be replayed for
+        other prompts (see StepContext): else prompt steps are launched one by one."""
+        # (a run that reads another run's cache reads it by slot, for every row: the rows that
+        # fill a recorded step up have none)
+        return (getattr(self.embedding, "captures_prompts", False)
+                and all(getattr(b, "captures_prompts", False) for b in self.blocks)
+                and all(e.cache_of is None for e in self.spec.schedule))
+
     def hidden_states(self, ctx) -> torch.Tensor:
         """Run every schedule entry over the step's rows; returns the 32-bit
         residual stream [rows, hidden]."""

@@ -49,6 +49,13 @@ _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 class Attention:
     chain_safe = True      # deferred results are read by this runtime's and native's launchers only
 
+    @property
+    def captures_prompts(self) -> bool:
+        """Whether a step of prompts of this part may be recorded and replayed for other
+        prompts (StepContext ``from_start``): it then reads sequences, slots and counts on
+        the device only.  True with a rotary position part, or one that promises the same."""
+        return hasattr(self.position, "rotary") or getattr(self.position, "captures_prompts", False)
+
     @staticmethod
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
         nh, nkv, hd = params["num_heads"], params["num_kv_heads"], params["head_dim"]

@@ -49,6 +49,7 @@ from __future__ import annotations
 import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.paged import KVView, SequenceCache
@@ -309,42 +310,50 @@ class StepContext:
     A *captured* step (``graph_capture=True``) is recorded once and replayed for other
     sequences, positions and slots: only the device tensors are refreshed before a replay.
     What is the same in every replay stays readable on the host (``n_rows``, ``n_seqs``,
-    ``counts``, ``max_count``, ``all_from_start``); reading ``starts``, ``slots`` or
-    ``max_end`` raises :class:`CapturedStepError`, because a value read while recording
-    would be frozen into the graph.  A part that is to run in captured steps indexes its
-    cache or state with the device tensors (``seq_slot``, ``row_pos``, ...) only.
+    ``max_count``, ``all_from_start``, and ``counts`` of single-token steps); reading
+    ``starts``, ``slots`` or ``max_end`` raises :class:`CapturedStepError`, because a value
+    read while recording would be frozen into the graph.  A part that is to run in captured
+    steps indexes its cache or state with the device tensors (``seq_slot``, ``row_pos``,
+    ...) only.
+
+    A captured step of prompts (``from_start=True``) is replayed for other prompts with the
+    same number of sequences and at most as many rows in all: its last sequence holds no
+    slot (``seq_slot`` -1) and takes the rows that are left over, nothing of it is stored,
+    and ``counts`` is not readable either; ``max_count`` is the number of rows, the most
+    that one sequence of a replay can have.
     """
 
     @staticmethod
-    def pack(seqs: Sequence[Tuple[int, int, int]], tokens: Optional[Sequence[int]],
-             want_rows: Sequence[int] = ()) -> List[int]:
-        """The step's integers for sequences ``[(slot, start, count)]``; ``tokens`` are the
-        R token ids in packed order (None: zeros)."""
-        row_pos: List[int] = []
-        row_seq: List[int] = []
-        row0: List[int] = []
-        acc = 0
-        for b, (_, start, n) in enumerate(seqs):
-            row_pos.extend(range(start, start + n))
-            row_seq.extend([b] * n)
-            row0.append(acc)
-            acc += n
-        toks = [0] * acc if tokens is None else [int(t) for t in tokens]
-        if len(toks) != acc:
-            raise ValueError(f"{len(toks)} tokens for {acc} rows")
-        return (toks + row_pos + row_seq + [int(s) for s, _, _ in seqs]
-                + [int(st) for _, st, _ in seqs] + [int(st + n) for _, st, n in seqs]
-                + row0 + [int(w) for w in want_rows])
+    def pack(seqs: Sequence[Tuple[int, int, int]], tokens, want_rows: Sequence[int] = ()) -> np.ndarray:
+        """The step's integers (an int32 array) for sequences ``[(slot, start, count)]``;
+        ``tokens`` are the R token ids in packed order (None: zeros)."""
+        B = len(seqs)
+        sq = np.asarray(seqs, dtype=np.int64).reshape(B, 3)
+        slots, starts, counts = sq[:, 0], sq[:, 1], sq[:, 2]
+        row0 = np.cumsum(counts) - counts
+        R = int(counts.sum())
+        row_seq = np.repeat(np.arange(B, dtype=np.int64), counts)
+        row_pos = np.arange(R, dtype=np.int64) - row0[row_seq] + starts[row_seq]
+        toks = np.zeros(R, dtype=np.int64) if tokens is None else np.asarray(tokens, dtype=np.int64)
+        if toks.shape != (R,):
+            raise ValueError(f"{toks.size} tokens for {R} rows")
+        want = np.asarray(list(want_rows), dtype=np.int64)
+        return np.concatenate([toks, row_pos, row_seq, slots, starts, starts + counts, row0,
+                               want]).astype(np.int32)
 
     @staticmethod
     def packed_size(n_rows: int, n_seqs: int, n_want: int) -> int:
         return 3 * n_rows + 4 * n_seqs + n_want
 
     def __init__(self, meta: torch.Tensor, seqs: Sequence[Tuple[int, int, int]], n_want: int,
-                 cache: SequenceCache, runtime: Runtime, graph_capture: bool = False):
+                 cache: SequenceCache, runtime: Runtime, graph_capture: bool = False,
+                 from_start: bool = False):
+        """``graph_capture`` with ``from_start``: a captured step of prompts that all start at
+        position 0 (replays bring other prompts of at most this step's rows in all, filled up
+        with the rows of a sequence that holds no slot: slot -1, nothing of it is stored)."""
         self.n_seqs = B = len(seqs)
-        self.counts = [int(n) for _, _, n in seqs]
-        self.n_rows = R = sum(self.counts)
+        self._counts = [int(n) for _, _, n in seqs]
+        self.n_rows = R = sum(self._counts)
         if meta.numel() < self.packed_size(R, B, n_want):
             raise ValueError("the packed step is shorter than its rows and sequences need")
         at = [0]
@@ -361,9 +370,12 @@ class StepContext:
         self.seq_end = take(B)       # [seqs] length after the step
         self.seq_row0 = take(B)      # [seqs] packed index of the sequence's first row
         self.want_rows = take(n_want)
-        self.max_count = max(self.counts)
+        # (the most rows of one sequence sizes launches: a captured step of prompts may be
+        # replayed with one sequence that takes nearly all rows)
+        self.max_count = R if (graph_capture and from_start) else max(self._counts)
         self.graph_capture = graph_capture
-        self.all_from_start = (not graph_capture) and all(st == 0 for _, st, _ in seqs)
+        self._counts_vary = graph_capture and from_start
+        self.all_from_start = from_start if graph_capture else all(st == 0 for _, st, _ in seqs)
         self._starts = [int(st) for _, st, _ in seqs]
         self._slots = [int(s) for s, _, _ in seqs]
         self._max_end = max(st + n for _, st, n in seqs)
@@ -377,6 +389,11 @@ class StepContext:
                 f"a replay runs other sequences, so captured steps may use the device "
                 f"tensors of the context only")
         return value
+
+    @property
+    def counts(self) -> List[int]:
+        """Rows per sequence (in a captured step of prompts they change between replays)."""
+        return self._host("counts", self._counts) if self._counts_vary else self._counts
 
     @property
     def starts(self) -> List[int]:

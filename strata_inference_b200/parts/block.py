@@ -59,6 +59,14 @@ class SandwichBlock:
                 and all(_fusable(n) for n in (self.pre_mixer, self.post_mixer, self.pre_ff,
                                               self.post_ff)))
 
+    @property
+    def captures_prompts(self) -> bool:
+        """Whether a recorded step of prompts of this block may be replayed for other prompts:
+        its mixer and feed-forward promise to read sequences, slots and counts on the
+        device only (the block itself and the norms work row by row)."""
+        return (getattr(self.mixer, "captures_prompts", False)
+                and getattr(self.feed_forward, "captures_prompts", False))
+
     def _add_then_norm(self, y: torch.Tensor, post, h: torch.Tensor, nxt) -> Optional[torch.Tensor]:
         """h += post(y) (or y); returns nxt(h) if nxt is given."""
         if _fusable(post) and _fusable(nxt):

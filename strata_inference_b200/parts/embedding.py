@@ -22,6 +22,8 @@ from .registry import register_embedding, register_head
 
 
 class TokenEmbedding:
+    captures_prompts = True   # row-wise: a recorded step of prompts may be replayed for others
+
     @staticmethod
     def tensors(params: Mapping, hidden: int, vocab: int) -> Dict[str, TensorDecl]:
         return {"weight": TensorDecl((vocab, hidden))}

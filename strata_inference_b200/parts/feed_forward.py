@@ -27,6 +27,7 @@ _GROUP = 8
 
 class GatedMLP:
     chain_safe = True      # deferred results are read by this runtime's and native's launchers only
+    captures_prompts = True   # row-wise: a recorded step of prompts may be replayed for others
 
     @staticmethod
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:

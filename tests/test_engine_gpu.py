@@ -535,3 +535,60 @@ def test_steps_of_few_rows_as_one_chain_kernel(model_dirs, name, page):
     assert eng.rt.chain_sync().tolist() == before.tolist() == [0, 0]
     for s in slots:
         eng.end_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16)])
+def test_short_prompt_steps_replayed_from_a_recording(model_dirs, name, page, dtype):
+    """Steps of two prompts with 17 to 64 rows in all share one recorded step (rows are
+    filled up to 64 with a sequence that holds no slot): launched one by one twice, then
+    replayed.  Every step brings other lengths, slots and wanted places; the logits at the
+    wanted places and those of two more tokens decoded from what the step left in the
+    cache equal the plain implementation's, and no page is lost."""
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, dtype, page)
+    lens = [(20, 30), (5, 12), (40, 24), (1, 60), (33, 9), (16, 16)]
+    held = []
+    for i, (a, b) in enumerate(lens):
+        reqs = random_prompts(cfg, [a + 2, b + 2], seed=70 + i)
+        refs = [plain_logits(t, model_dirs[name, dtype], cfg) for t in reqs]
+        if i == 3:      # other slots than before: the ones held so far stay taken
+            held = [eng.new_sequence() for _ in range(2)]
+        slots = [eng.new_sequence(), eng.new_sequence()]
+        want = [[a // 2, a - 1], [b - 1, 0]]
+        got = eng.step([(slots[0], reqs[0][:a]), (slots[1], reqs[1][:b])], want)
+        ref = torch.stack([refs[0][a // 2], refs[0][a - 1], refs[1][b - 1], refs[1][0]])
+        assert_logits_close(got, ref, dtype, f"{name} step {i} prompts of {a} and {b}")
+        for k in range(2):
+            got = eng.step([(slots[0], [reqs[0][a + k]]), (slots[1], [reqs[1][b + k]])])
+            ref = torch.stack([refs[0][a + k], refs[1][b + k]])
+            assert_logits_close(got, ref, dtype, f"{name} step {i} token {k} after the prompts")
+        for s in slots:
+            eng.end_sequence(s)
+    graphs = list(eng._prompt_graphs.values())
+    assert len(graphs) == 1 and graphs[0].graph is not None and graphs[0].calls == len(lens)
+    for s in held:
+        eng.end_sequence(s)
+    assert eng.cache.pages_in_use() == 0
+
+
+def test_recorded_prompt_steps_can_be_switched_off_and_are_few(model_dirs):
+    cfg = CONFIGS["A"]
+    eng = _engine(model_dirs, "A", "bfloat16", 64, max_tokens=4096)
+    toks = random_prompts(cfg, [40], seed=5)[0]
+    ref = plain_logits(toks, model_dirs["A", "bfloat16"], cfg)[-1:]
+    eng.prompt_graph_rows = 0
+    slot = eng.new_sequence()
+    assert_logits_close(eng.step([(slot, toks)]), ref, "bfloat16", "launched one by one")
+    eng.end_sequence(slot)
+    assert not eng._prompt_graphs
+    eng.prompt_graph_rows = 1024
+    eng.max_graphs = 2
+    for n_seqs in (1, 2, 3, 1):      # a recording per number of sequences; the oldest goes
+        slots = [eng.new_sequence() for _ in range(n_seqs)]
+        got = eng.step([(s, toks) for s in slots])
+        assert_logits_close(got, ref.expand(n_seqs, -1), "bfloat16", f"{n_seqs} prompts")
+        for s in slots:
+            eng.end_sequence(s)
+        assert len(eng._prompt_graphs) <= 2
+    assert [k[2] for k in eng._prompt_graphs] == [3, 1]

@@ -423,6 +423,9 @@ def test_schedule_names_a_layer_twice_and_lends_a_cache(tmp_path, dtype):
     W = {k: v.double() for k, v in load_file(d + "/model.safetensors").items()}
     eng = Engine.from_dir(d, dtype=dtype, max_tokens=512, page_tokens=16)
     assert len(eng.cache.groups) == 2 and sum(len(g.entries) for g in eng.cache.groups) == 3
+    # (a run that reads a lent cache reads it by slot: its prompt steps are not recorded and
+    # replayed with rows that have no slot)
+    assert not eng.model.captures_prompts
     toks = random_prompts(cfg, [60], seed=9)[0]
     ref = _looped_plain(toks, W, cfg)
     slot = eng.new_sequence()
