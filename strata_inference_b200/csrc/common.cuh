@@ -44,7 +44,7 @@ template <typename K> inline void sib_same_carveout(K kernel) {
 // step's stream and looks at it wherever it synchronises anyway (runtime.cu).
 enum SibErrorWord {
     SIB_ERR_GEMM_TCGEN05 = 0, SIB_ERR_ATTENTION_PREFILL_TC = 1, SIB_ERR_LINEAR_STREAM = 2,
-    SIB_ERR_DECODE_CHAIN = 3,
+    SIB_ERR_DECODE_CHAIN = 3, SIB_ERR_LINEAR_ROWS_TC = 4,
     SIB_ERROR_WORDS = 8
 };
 int* sib_error_word(int word);   // device address of the current device's word; null on failure

@@ -61,7 +61,7 @@ SIB_EXPORT int sib_compiled_arch() {
 static int* g_error_words[64] = {};
 static std::mutex g_error_mutex;
 static const char* const kErrorWordNames[SIB_ERROR_WORDS] = {
-    "gemm_tcgen05", "attention_prefill_tc", "linear_stream", "decode_chain", "", "", "", ""};
+    "gemm_tcgen05", "attention_prefill_tc", "linear_stream", "decode_chain", "linear_rows_tc", "", "", ""};
 
 static int* error_table() {
     int dev = 0;

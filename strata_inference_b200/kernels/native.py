@@ -603,6 +603,33 @@ def linear_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue:
     return out
 
 
+def linear_rows_tc_max_rows() -> int:
+    return int(library().sib_linear_rows_tc_max_rows())
+
+
+@_timed(lambda x, w, out, epilogue=EPI_NONE, cap=0.0, ksplit=0, stages=0: _product_work(
+    "linear_rows_tc", x, w, out))
+def linear_rows_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+                   cap: float = 0.0, ksplit: int = 0, stages: int = 0) -> torch.Tensor:
+    """out = x . w^T for at most 128 rows of bfloat16 x on the tcgen05 tensor cores, the
+    weights streamed through a ring of TMA stages (see csrc/linear_rows_tc.cu).  ``ksplit``
+    blocks of a cluster share a tile of 128 weight rows, ``stages`` stages are in flight per
+    block; 0 lets the launcher choose."""
+    _want(x, torch.bfloat16, "x", contiguous=False)
+    _want(w, torch.bfloat16, "w")
+    _want(out, out.dtype, "out", contiguous=False)
+    R, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if epilogue == EPI_GEGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (R, n_out) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear_rows_tc: shapes do not fit")
+    _check(library().sib_linear_rows_tc(_ptr(w), _ptr(x), _ptr(out), _code(out.dtype), c_int(R),
+                                        c_int(N), c_int(K), c_int(x.stride(0)),
+                                        c_int(out.stride(0)), c_int(epilogue), c_float(cap),
+                                        c_int(ksplit), c_int(stages), _stream()))
+    return out
+
+
 @_timed(lambda x, w, out, *a, **kw: _product_work("skinny_linear_rope", x, w, out))
 def skinny_linear_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_pos, row_seq,
                        seq_slot, seq_end, inv_freq: torch.Tensor,

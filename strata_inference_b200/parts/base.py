@@ -76,6 +76,11 @@ class Runtime:
         # takes up to native.SKINNY_MAX_ROWS); measured on a B200 at Gemma2-2B sizes it
         # is ahead of the library product up to 16 rows and behind it from 32 on.
         self.skinny_max_rows = 16
+        # Up to 128 rows against a matrix of so many rows that its 128-row tiles are several
+        # waves of blocks go to the tcgen05 weight-streaming product (csrc/linear_rows_tc.cu):
+        # there it reads at 0.91 of the copy bandwidth; with fewer tiles the library is as fast.
+        self.rows_tc_max_rows = native.linear_rows_tc_max_rows()
+        self.rows_tc_min_weight_rows = 4 * 128 * self.sm_count
         # SIB_LINEAR_STREAM=1: few-row products go to the kernel that stages its weights through
         # shared memory (csrc/linear_stream.cu) instead of the one that loads them straight
         # into registers.  Alone it is the faster of the two on most shapes; inside a chained
@@ -200,6 +205,12 @@ class Runtime:
             return native.skinny_linear(x, w, out, epilogue, cap)
         aligned = (K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                    and x.data_ptr() % 16 == 0)
+        if (x.dtype == torch.bfloat16 and aligned and R <= self.rows_tc_max_rows
+                and N >= self.rows_tc_min_weight_rows and w.is_contiguous()):
+            # some rows against very many weight rows (the logits of a batch of 17 to 128):
+            # the weight-streaming tcgen05 product, with its epilogue
+            out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
+            return native.linear_rows_tc(x, w, out, epilogue, cap)
         fused_gate = epilogue == native.EPI_GEGLU and R > self.gated_gemm_min_rows
         if x.dtype == torch.bfloat16 and aligned and (out_dtype == torch.float32 or fused_gate):
             # the tcgen05 product where its epilogue saves a pass over the outputs: 32-bit

@@ -592,3 +592,30 @@ def test_recorded_prompt_steps_can_be_switched_off_and_are_few(model_dirs):
             eng.end_sequence(s)
         assert len(eng._prompt_graphs) <= 2
     assert [k[2] for k in eng._prompt_graphs] == [3, 1]
+
+
+@pytest.mark.parametrize("name,page", [("A", 4), ("B", 8), ("C", 16)])
+def test_products_of_some_rows_on_the_streaming_tensor_core_kernel(model_dirs, name, page):
+    """Every product of 17 to 128 rows through csrc/linear_rows_tc.cu (the engine sends it
+    only matrices with very many rows: here the limit is taken away), gated and soft-capped
+    epilogues included: 20 prompts in one step, then tokens one by one."""
+    cfg = CONFIGS[name]
+    eng = _engine(model_dirs, name, "bfloat16", page, max_tokens=4096)
+    eng.rt.rows_tc_min_weight_rows = 1
+    lens = [3 + (7 * i) % 6 for i in range(20)]          # 3..8 tokens each, about 110 rows
+    reqs = random_prompts(cfg, [n + 3 for n in lens], seed=31)
+    refs = [plain_logits(t, model_dirs[name, "bfloat16"], cfg) for t in reqs]
+    slots = [eng.new_sequence() for _ in reqs]
+    from strata_inference_b200.kernels import native
+    with native.KernelProfile() as prof:
+        got = eng.step([(s, t[:n]) for s, t, n in zip(slots, reqs, lens)])
+    assert any(row["name"].startswith("linear_rows_tc") for row in prof.rows())
+    ref = torch.stack([refs[i][n - 1] for i, n in enumerate(lens)])
+    assert_logits_close(got, ref, "bfloat16", f"{name} 20 prompts")
+    for k in range(3):
+        got = eng.step([(s, [t[n + k]]) for s, t, n in zip(slots, reqs, lens)])
+        ref = torch.stack([refs[i][n + k] for i, n in enumerate(lens)])
+        assert_logits_close(got, ref, "bfloat16", f"{name} token {k} of 20 sequences")
+    for s in slots:
+        eng.end_sequence(s)
+    eng.read_back(got)       # (no bounded wait ran out)

@@ -524,6 +524,68 @@ def test_linear_stream_refuses_what_it_cannot_do():
                         torch.empty(2, 12, dtype=torch.bfloat16, device=DEV), n.EPI_GEGLU)
 
 
+@pytest.mark.parametrize("R,N,K,ksplit,stages", [
+    (17, 256, 256, 0, 0), (64, 2304, 2048, 0, 0), (33, 144, 72, 1, 1), (128, 4096, 2304, 0, 0),
+    (100, 300, 328, 2, 2), (48, 272, 1024, 8, 3), (21, 48, 1600, 4, 2), (96, 1000, 776, 8, 8),
+    (64, 18432, 2304, 0, 0), (32, 2304, 9216, 0, 0), (1, 256, 128, 2, 1), (16, 640, 520, 4, 0),
+])
+def test_linear_rows_tc(R, N, K, ksplit, stages):
+    """The weight-streaming product of up to 128 rows on tcgen05: sizes that are no multiples
+    of its tiles (128 weight rows, 64 of k, 16 rows), every split of k over a cluster, rings
+    shorter and longer than the run of k, all epilogues, both output types, strided rows."""
+    n = _native()
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    # one entry far from the rest: a row or a run of k that is dropped or taken twice shows
+    x[R - 1, K - 1] = 40.0
+    w[N - 1, K - 1] = 3.0
+    ref = x.double() @ w.double().T
+    xd, wd = x.to(DEV), w.to(DEV)
+    out = torch.full((R, N), float("nan"), dtype=torch.float32, device=DEV)
+    n.linear_rows_tc(xd, wd, out, n.EPI_NONE, 0.0, ksplit, stages)
+    _close(out, ref, torch.float32, "rows_tc f32 out", factor=20)
+    wide = torch.zeros(R, K + 16, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = xd
+    out16 = torch.full((R, N + 8), float("nan"), dtype=torch.bfloat16, device=DEV)
+    n.linear_rows_tc(wide[:, :K], wd, out16[:, :N], n.EPI_NONE, 0.0, ksplit, stages)
+    _close(out16[:, :N], ref, torch.bfloat16, "rows_tc bf16 out")
+    assert torch.isnan(out16[:, N:].float()).all()
+    capped = torch.empty(R, N, dtype=torch.float32, device=DEV)
+    n.linear_rows_tc(xd, wd, capped, n.EPI_SOFTCAP, 0.7, ksplit, stages)
+    _close(capped, 0.7 * torch.tanh(ref / 0.7), torch.float32, "rows_tc soft cap", factor=20)
+    if N % 16 == 0:
+        gated = torch.full((R, N // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+        n.linear_rows_tc(xd, wd, gated, n.EPI_GEGLU, 0.0, ksplit, stages)
+        y = ref.view(R, N // 16, 2, 8)
+        _close(gated, (plain.gelu_tanh(y[:, :, 0]) * y[:, :, 1]).reshape(R, N // 2),
+               torch.bfloat16, "rows_tc gated")
+    again = torch.empty(R, N, dtype=torch.float32, device=DEV)
+    n.linear_rows_tc(xd, wd, again, n.EPI_NONE, 0.0, 1, 2)
+    _close(again, out.double().cpu(), torch.float32, "rows_tc, one block a tile", factor=5)
+    torch.cuda.synchronize()
+    watch = n.KernelWatch()
+    watch.fetch()
+    torch.cuda.synchronize()
+    watch.check()
+
+
+def test_linear_rows_tc_refuses_what_it_cannot_do():
+    n = _native()
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(n.KernelError, match="1 to 128"):
+        n.linear_rows_tc(torch.zeros(129, 64, dtype=torch.bfloat16, device=DEV), w,
+                         torch.empty(129, 32, dtype=torch.float32, device=DEV))
+    with pytest.raises(n.KernelError, match="multiples of 8"):
+        n.linear_rows_tc(torch.zeros(20, 60, dtype=torch.bfloat16, device=DEV),
+                         torch.zeros(32, 60, dtype=torch.bfloat16, device=DEV),
+                         torch.empty(20, 32, dtype=torch.float32, device=DEV))
+    with pytest.raises(n.KernelError, match="groups of 16"):
+        n.linear_rows_tc(torch.zeros(20, 64, dtype=torch.bfloat16, device=DEV),
+                         torch.zeros(24, 64, dtype=torch.bfloat16, device=DEV),
+                         torch.empty(20, 12, dtype=torch.bfloat16, device=DEV), n.EPI_GEGLU)
+
+
 def _chain_case(R, H, nh, nkv, hd, inter, seed):
     """Operands of a decoder's steps between two attention kernels, for R rows."""
     g = torch.Generator().manual_seed(seed)
