@@ -12,7 +12,11 @@ context; a "step" is one decode step (one new token per sequence).
   host each step; the result is not read back); the median block counts, the
   fastest and slowest are reported as ``spread_ms``.
 * ``e2e``: the same through the Python entry point ``GenerationEngine.generate``:
-  host token lists in, host token lists out, wall clock over the decode steps.
+  host token lists in, host token lists out, wall clock over the decode steps.  Every
+  step copies its integers from pinned host memory and its sampled tokens are read on
+  the host; the loop keeps the device one step ahead of the host (a step takes the
+  tokens of the step before on the device, before the host has read and judged them),
+  which ``steps_ahead_of_host`` records.
 * ``prefill``: one 2,048-token prompt through ``Engine.step``.
 * ``roofline``: bytes a decode step has to read (every weight once, the keys and
   values each live sequence's layers attend to) / its time / the measured copy
@@ -344,7 +348,8 @@ def run_ours(args):
             "peaks": peaks["source"],
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "warmup_steps": e2e_warmup,
-                "h2d_bytes_per_step": 8 * batch * 4, "d2h_bytes_per_step": batch * 4},
+                "h2d_bytes_per_step": 8 * batch * 4, "d2h_bytes_per_step": batch * 4,
+                "steps_ahead_of_host": 1},
         "gpu_launches": launches * args.steps,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],

@@ -133,10 +133,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         engine = GenerationEngine.from_dir(args.model, dtype=args.dtype, ctx=args.ctx,
                                            max_tokens=need)
         load_ms = (time.perf_counter() - load_start) * 1e3
+        # (the logits of every token are dumped from inside the token callback: the device
+        # must then not be a step ahead of it)
         conf = GenerationConfig(
             max_tokens=args.max_tokens, stop_tokens=args.stop_token,
             sampling=SamplingConfig(temperature=args.temp, top_k=args.top_k, top_p=args.top_p,
-                                    seed=args.seed))
+                                    seed=args.seed),
+            look_ahead=not args.dump_logits)
         first_token_at = [None]
         last = [time.perf_counter()]
         dump = open(args.dump_logits, "w") if args.dump_logits and len(prompts) == 1 else None

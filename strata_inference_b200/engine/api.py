@@ -68,9 +68,23 @@ class EngineStepper:
         return self.engine.read_back(toks)
 
     def decode(self, slots, tokens, sampling: SamplingConfig) -> List[int]:
+        return self.decode_collect(self.decode_issue(slots, tokens, sampling))
+
+    # The same in two halves, so that the loop can issue the step after this one before it
+    # reads this one's tokens (the device then never waits for the host between steps):
+    def decode_issue(self, slots, tokens, sampling: SamplingConfig):
+        """Launch the step; ``tokens`` None: the ones the step before sampled for the same
+        slots (``can_feed_back``).  Returns a ticket for ``decode_collect``."""
         out = self.engine.decode_step(slots, tokens, sampling.temperature, sampling.top_k,
                                       sampling.top_p, use_graph=self.use_graph)
-        return self.engine.read_back(out)
+        return self.engine.read_later(out)
+
+    def decode_collect(self, ticket) -> List[int]:
+        return self.engine.read_now(ticket)
+
+    def can_feed_back(self, slots, sampling: SamplingConfig) -> bool:
+        return self.use_graph and self.engine.can_feed_back(
+            slots, sampling.temperature, sampling.top_k, sampling.top_p)
 
 
 class GenerationEngine:

@@ -76,6 +76,8 @@ class Engine:
         self.max_graphs = 8
         self.prompt_graph_rows = 1024   # steps of prompts of up to this many rows are recorded
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
+        self._read_ring = None      # pinned buffers and events of read_later, made at first use
+        self._reads = 0
 
     # ---- construction ----------------------------------------------------
     @classmethod
@@ -240,12 +242,16 @@ class Engine:
         return native.sample_rows(logits, temperature, top_k, top_p, self.rng_state, out, index)
 
     # ---- single-token steps through a captured graph ----------------------
-    def decode_step(self, slots: Sequence[int], tokens: Sequence[int], temperature: float = 0.0,
-                    top_k: int = 0, top_p: float = 1.0, use_graph: bool = True) -> torch.Tensor:
+    def decode_step(self, slots: Sequence[int], tokens: Optional[Sequence[int]],
+                    temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+                    use_graph: bool = True) -> torch.Tensor:
         """One token for each of ``slots``, then one sampled token each: the
         same kernels as ``step`` + ``sample``, replayed from a CUDA graph that
         is captured the second time a batch size is seen.  Returns the sampled
-        tokens as an int32 tensor on the device."""
+        tokens as an int32 tensor on the device (the next step of the same graph
+        overwrites it).  ``tokens`` None: the tokens that the step before sampled for the
+        same slots, taken on the device (``can_feed_back`` says whether that is possible);
+        the host may read them afterwards."""
         from .graph import DecodeGraph
         key = (len(slots), float(temperature), int(top_k), float(top_p))
         g = self._graphs.pop(key, None)
@@ -259,6 +265,35 @@ class Engine:
         out = g.run(slots, tokens, use_graph)
         self.last_logits = g.last_logits
         return out
+
+    def can_feed_back(self, slots: Sequence[int], temperature: float = 0.0, top_k: int = 0,
+                      top_p: float = 1.0) -> bool:
+        """Whether ``decode_step(slots, None, ...)`` is possible now."""
+        g = self._graphs.get((len(slots), float(temperature), int(top_k), float(top_p)))
+        return g is not None and g.can_feed_back(slots)
+
+    def read_later(self, t: torch.Tensor):
+        """Start bringing the integer tensor ``t`` (at most one value per slot) to the host:
+        the copy is enqueued now, behind the step that makes ``t`` and ahead of whatever is
+        launched next; ``read_now`` of the returned ticket waits for it."""
+        n = t.numel()
+        if self._read_ring is None:
+            self._read_ring = [(torch.zeros(self.cache.max_slots, dtype=torch.int32).pin_memory(),
+                                torch.cuda.Event()) for _ in range(4)]
+        buf, event = self._read_ring[self._reads % len(self._read_ring)]
+        self._reads += 1
+        buf[:n].copy_(t.reshape(-1), non_blocking=True)
+        self.kernel_watch.fetch()
+        event.record()
+        return buf, n, event
+
+    def read_now(self, ticket) -> List[int]:
+        """The values of a ``read_later`` ticket, and the check that no kernel so far gave up
+        on a bounded wait.  At most four tickets may be open at a time."""
+        buf, n, event = ticket
+        event.synchronize()
+        self.kernel_watch.check()
+        return buf[:n].tolist()
 
     def read_back(self, t: torch.Tensor):
         """``t`` on the host (a list for integer tensors, else a tensor), and a check that

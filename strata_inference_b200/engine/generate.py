@@ -17,6 +17,16 @@ A batch's requests start together; a finished sequence leaves the batch and
 gives its slot back at once; the next batch starts when the current one is
 done.  The loop talks to the model through a small *stepper* (prefill,
 decode, slots), so its decisions can be tested without a device.
+
+Looking ahead.  Reading a step's tokens, deciding and launching the next step leaves the
+device idle for as long as the host takes.  A stepper that can launch a step and hand out
+its tokens later (``decode_issue`` / ``decode_collect``) and can feed a step with the
+tokens the step before sampled, on the device (``can_feed_back``), is therefore kept one
+step ahead: while the host reads and judges the tokens of step n, step n + 1 is already
+running for the same sequences.  If a sequence ends at step n, its row of step n + 1 is
+dropped unseen and the others' rows are kept; every decision and every emitted token is
+the same as without looking ahead.  A sequence is never fed beyond the context's end,
+and no step is launched that no sequence could use.
 """
 
 from __future__ import annotations
@@ -44,6 +54,10 @@ class GenerationConfig:
     max_tokens: int = 256
     stop_tokens: Sequence[int] = ()
     sampling: SamplingConfig = field(default_factory=SamplingConfig)
+    # Keep the device one step ahead of the host (see the module's text).  The logits that
+    # a stepper shows for "the latest step" are then those of a later step than the token a
+    # callback is looking at: switch it off to read them token by token.
+    look_ahead: bool = True
 
 
 @dataclass
@@ -125,6 +139,11 @@ def generate(stepper, prompts: Sequence[Sequence[int]], config: GenerationConfig
                 results[i] = GenerationOutput([], MAX_TOKENS, len(prompts[i]), prefill_s)
                 live.append((i, s, int(t)))
             t_decode = time.perf_counter()
+            # a stepper without the two halves: the ticket of a step is its tokens
+            issue = getattr(stepper, "decode_issue", None) or stepper.decode
+            collect = getattr(stepper, "decode_collect", None) or (lambda ticket: ticket)
+            ahead_ok = config.look_ahead and hasattr(stepper, "decode_issue")
+            ahead = None        # ticket of a step already running for the sequences of `live`
             while live:
                 going = []
                 for i, s, tok in live:
@@ -138,7 +157,9 @@ def generate(stepper, prompts: Sequence[Sequence[int]], config: GenerationConfig
                         out.token_ids.append(tok)
                         if callback is not None and not callback(i, tok):
                             reason = CANCELLED
-                        elif stepper.length(s) >= max_seq_len:
+                        elif out.prompt_tokens + len(out.token_ids) - 1 >= max_seq_len:
+                            # (the positions the cache holds once every emitted token but
+                            # this one is fed: the context is full)
                             reason = CONTEXT_LENGTH
                         elif limit >= 0 and len(out.token_ids) >= limit:
                             # the reference runs one more step here and drops its
@@ -151,11 +172,27 @@ def generate(stepper, prompts: Sequence[Sequence[int]], config: GenerationConfig
                         out.decode_duration = time.perf_counter() - t_decode
                         held.discard(s)
                         stepper.end_sequence(s)
-                live = []
-                if going:
-                    nxt = stepper.decode([s for _, s, _ in going], [t for _, _, t in going],
-                                         config.sampling)
-                    live = [(i, s, int(t)) for (i, s, _), t in zip(going, nxt)]
+                if not going:
+                    if ahead is not None:
+                        collect(ahead)      # nobody is left to use it
+                    break
+                slots_now = [s for _, s, _ in going]
+                if ahead is not None and len(going) < len(live):
+                    # the step that is already running was fed with the tokens judged above:
+                    # the rows of the sequences that go on are the ones they need
+                    row = {s: t for (_, s, _), t in zip(live, collect(ahead))}
+                    live = [(i, s, int(row[s])) for i, s, _ in going]
+                    ahead = None
+                    continue
+                ticket = ahead if ahead is not None else issue(
+                    slots_now, [t for _, _, t in going], config.sampling)
+                ahead = None
+                if ahead_ok and stepper.can_feed_back(slots_now, config.sampling) and all(
+                        stepper.length(s) < max_seq_len for s in slots_now) and any(
+                        limit < 0 or len(results[i].token_ids) + 1 < limit for i, _, _ in going):
+                    # the step after this one, for as long as any sequence could use its token
+                    ahead = issue(slots_now, None, config.sampling)
+                live = [(i, s, int(t)) for (i, s, _), t in zip(going, collect(ticket))]
         except BaseException:
             for s in held:      # give back what the failed batch still holds
                 stepper.end_sequence(s)

@@ -41,6 +41,7 @@ class DecodeGraph:
         # copy ran.
         size = StepContext.packed_size(B, B, B)
         self.hosts = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
+        self.host_rows = [h.numpy().reshape(8, B) for h in self.hosts]     # views of the same memory
         self.copied = [None] * _STAGES
         self.meta = torch.zeros(size, dtype=torch.int32, device=engine.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -49,6 +50,7 @@ class DecodeGraph:
         self.last_logits: Optional[torch.Tensor] = None
         self.calls = 0
         self.launches_per_step = 0
+        self.last_slots: Optional[list] = None      # of the latest run
 
     def _forward(self, seqs, capture: bool):
         eng, B = self.engine, self.B
@@ -60,12 +62,22 @@ class DecodeGraph:
                            ctx.seq_slot)
         return logits, out
 
-    def run(self, slots: Sequence[int], tokens: Sequence[int], use_graph: bool = True):
+    def can_feed_back(self, slots: Sequence[int]) -> bool:
+        """Whether the next step of ``slots`` can take the tokens that the latest run sampled
+        straight from the device: the graph is recorded and that run was for these slots."""
+        return self.graph is not None and self.last_slots == [int(s) for s in slots]
+
+    def run(self, slots: Sequence[int], tokens: Optional[Sequence[int]], use_graph: bool = True):
+        """``tokens`` None: the tokens that the latest run sampled, which are still on the
+        device (see ``can_feed_back``): the host need not have read them yet."""
         eng, B = self.engine, self.B
-        if len(slots) != B or len(tokens) != B:
+        if len(slots) != B or (tokens is not None and len(tokens) != B):
             raise ValueError(f"this graph steps {B} sequences")
+        if tokens is None and not (use_graph and self.can_feed_back(slots)):
+            raise ValueError("a step can only take its tokens from the device after a replayed "
+                             "step of the same sequences")
         V = eng.vocab_size
-        for t in tokens:
+        for t in tokens or ():
             if not 0 <= int(t) < V:
                 raise ValueError(f"input token ID {t} exceeds vocab_size {V}")
         slots = [int(s) for s in slots]
@@ -78,6 +90,7 @@ class DecodeGraph:
             raise
         for s in slots:
             eng.cache.advance(s, 1)
+        self.last_slots = slots
         return result
 
     def _run(self, slots, tokens, use_graph: bool):
@@ -86,9 +99,11 @@ class DecodeGraph:
         stage = self.calls % _STAGES
         if self.copied[stage] is not None:
             self.copied[stage].synchronize()     # (long done unless the caller runs far ahead)
-        h = self.hosts[stage]
-        h.copy_(torch.from_numpy(StepContext.pack(seqs, tokens, range(B))))
-        self.meta.copy_(h, non_blocking=True)
+        StepContext.pack_single_tokens(self.host_rows[stage], slots, [st for _, st, _ in seqs],
+                                       0 if tokens is None else tokens)
+        self.meta.copy_(self.hosts[stage], non_blocking=True)
+        if tokens is None:
+            self.meta[:B].copy_(self.out, non_blocking=True)     # what the latest replay sampled
         if self.copied[stage] is None:
             self.copied[stage] = torch.cuda.Event()
         self.copied[stage].record()
@@ -123,6 +138,9 @@ class DecodeGraph:
                     if collecting:
                         gc.enable()
                 self.graph = g
+                # (the recording ran nothing: the tokens of this step, which the next step
+                # may be fed with on the device, are put where a replay would have put them)
+                self.out.copy_(result)
         self.calls += 1
         return result
 

@@ -308,6 +308,9 @@ class CapturedStepError(RuntimeError):
     """A part read a host-side value of a step that is being captured into a CUDA graph."""
 
 
+_ORDER: Dict[int, np.ndarray] = {}      # 0..B-1 by B
+
+
 class StepContext:
     """One step's rows: which sequence and position each row is, on the device for the
     kernels and on the host for launch decisions.
@@ -351,6 +354,22 @@ class StepContext:
         want = np.asarray(list(want_rows), dtype=np.int64)
         return np.concatenate([toks, row_pos, row_seq, slots, starts, starts + counts, row0,
                                want]).astype(np.int32)
+
+    @staticmethod
+    def pack_single_tokens(out: np.ndarray, slots: Sequence[int], lengths: Sequence[int],
+                           tokens: Sequence[int]) -> None:
+        """What ``pack`` gives for a step of one token for each of B sequences with every
+        row wanted, written into ``out`` (int32, [8, B]: the eight runs of the layout, each
+        of length B here) without making arrays on the way: the step that is taken
+        thousands of times in a row."""
+        order = _ORDER.get(len(slots))
+        if order is None:
+            order = _ORDER[len(slots)] = np.arange(len(slots), dtype=np.int32)
+        out[0] = tokens
+        out[1] = out[4] = lengths
+        out[2] = out[6] = out[7] = order
+        out[3] = slots
+        out[5] = out[4] + 1
 
     @staticmethod
     def packed_size(n_rows: int, n_seqs: int, n_want: int) -> int:

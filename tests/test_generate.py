@@ -174,3 +174,83 @@ def test_a_failing_step_gives_the_slots_back():
     with pytest.raises(RuntimeError, match="device fault"):
         generate(st, [[1], [2, 2]], GenerationConfig(max_tokens=10))
     assert not st.live and st.free_slots == 8
+
+
+def test_the_fast_layout_of_single_token_steps_is_the_general_one():
+    import numpy as np
+    from strata_inference_b200.parts.base import StepContext
+    slots, lengths, tokens = [5, 0, 9, 2], [17, 300, 0, 64], [11, 7, 400, 3]
+    out = np.full((8, 4), -7, dtype=np.int32)
+    StepContext.pack_single_tokens(out, slots, lengths, tokens)
+    general = StepContext.pack([(s, n, 1) for s, n in zip(slots, lengths)], tokens, range(4))
+    assert general.dtype == np.int32 and general.tolist() == out.reshape(-1).tolist()
+    assert StepContext.packed_size(4, 4, 4) == out.size
+
+
+class LookAheadStepper(ScriptedStepper):
+    """A scripted stepper that can launch a step and hand its tokens out later, and feed a
+    step with what the step before sampled: what the loop needs to stay one step ahead."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.last = None          # (slots, tokens) of the latest launched step
+        self.open = 0
+        self.fed_back = 0
+
+    def decode_issue(self, slots, tokens, sampling):
+        if tokens is None:
+            assert self.can_feed_back(slots, sampling), "nothing to feed back"
+            tokens = self.last[1]
+            self.fed_back += 1
+        out = super().decode(slots, tokens, sampling)
+        self.last = (list(slots), out)
+        self.open += 1
+        assert self.open <= 2, "more than one step ahead"
+        return out
+
+    def decode_collect(self, ticket):
+        self.open -= 1
+        return ticket
+
+    def can_feed_back(self, slots, sampling):
+        # (a slot that has ended since cannot be in `slots`: the loop asks for live ones)
+        return self.last is not None and self.last[0] == list(slots)
+
+    def prefill(self, slots, prompts, sampling):
+        self.last = None
+        return super().prefill(slots, prompts, sampling)
+
+
+def _ragged(prompt, n_fed):
+    """Tokens that depend on the prompt and the place; token 7 ends a sequence."""
+    v = (prompt[0] * 31 + n_fed * 17 + len(prompt)) % 23
+    return 7 if v == 0 and n_fed > 1 else 100 + v
+
+
+@pytest.mark.parametrize("limit", [0, 1, 2, 5, 40, -1])
+def test_looking_one_step_ahead_changes_no_decision(limit):
+    prompts = [[k + 1] * (3 + 5 * k % 11) for k in range(7)]
+    conf = GenerationConfig(max_tokens=limit, stop_tokens=[7])
+    cancel_at = {2: 4, 5: 1}      # request -> emitted tokens after which it cancels
+
+    def run(stepper, look_ahead):
+        seen = {}
+
+        def cb(i, t):
+            seen[i] = seen.get(i, 0) + 1
+            return seen[i] != cancel_at.get(i)
+        outs = generate(stepper, prompts, GenerationConfig(limit, [7], conf.sampling, look_ahead), cb)
+        assert not stepper.live, "a slot was not given back"
+        return [(o.token_ids, o.stop_reason) for o in outs]
+
+    plain = run(ScriptedStepper(_ragged, max_seq_len=30, slots=3), False)
+    ahead = LookAheadStepper(_ragged, max_seq_len=30, slots=3)
+    assert run(ahead, True) == plain
+    assert ahead.open == 0
+    if limit < 0 or limit > 2:
+        assert ahead.fed_back > 0          # it did look ahead
+    off = LookAheadStepper(_ragged, max_seq_len=30, slots=3)
+    assert run(off, False) == plain and off.fed_back == 0
+    reasons = {r for _, r in plain}
+    if limit < 0:
+        assert {STOP_TOKEN, CANCELLED, CONTEXT_LENGTH} <= reasons

@@ -84,6 +84,37 @@ def test_stop_tokens_context_end_and_batches_one_after_another(model_dirs):
     assert eng.engine.cache.pages_in_use() == 0
 
 
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_one_step_ahead_of_the_host_gives_the_same_tokens(model_dirs, temperature):
+    """The loop keeps the device one step ahead (a step is fed with the tokens of the step
+    before on the device, before the host has read them): the same tokens, stop reasons and
+    freed slots as with every step waited for, also where sequences end at different steps."""
+    from strata_inference_b200 import GenerationConfig, GenerationEngine, SamplingConfig
+    name, cfg = "B", CONFIGS["B"]
+    prompts = random_prompts(cfg, [7, 30, 2, 21, 12, 5], seed=8)
+    eng = GenerationEngine.from_dir(model_dirs[name], dtype="float32", max_tokens=512)
+    sampling = SamplingConfig(temperature=temperature, seed=9)
+    waited = eng.generate(prompts, GenerationConfig(max_tokens=-1, sampling=sampling, look_ahead=False))
+    stop = waited[1].token_ids[6]
+    fed = []
+    step = eng.engine.decode_step
+
+    def counting(slots, tokens, *a, **kw):
+        fed.append(tokens is None)
+        return step(slots, tokens, *a, **kw)
+    eng.engine.decode_step = counting
+    for limit in (-1, 9):
+        conf = dict(max_tokens=limit, stop_tokens=[stop], sampling=sampling)
+        a = eng.generate(prompts, GenerationConfig(look_ahead=False, **conf))
+        assert not any(fed)
+        b = eng.generate(prompts, GenerationConfig(look_ahead=True, **conf))
+        assert sum(fed) >= 4      # steps that took their tokens on the device
+        del fed[:]
+        assert [(o.token_ids, o.stop_reason) for o in a] == [(o.token_ids, o.stop_reason) for o in b]
+        assert len({o.stop_reason for o in a}) > 1
+        assert eng.engine.cache.pages_in_use() == 0
+
+
 def test_bfloat16_generation_is_deterministic_and_every_choice_is_near_the_plain_best(model_dirs):
     from helpers import assert_greedy_choices_close
     from strata_inference_b200 import GenerationConfig, GenerationEngine
