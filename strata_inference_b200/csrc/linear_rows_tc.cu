@@ -430,6 +430,8 @@ SIB_EXPORT int sib_linear_rows_tc_max_rows() { return 128; }
 // bandwidth; a layer's matrices have 18 to 144 tiles, so a launch is one or two waves whose
 // start (tensor memory, barriers, the first tiles' latency) and end (accumulator out, the
 // exchange between the blocks that split k) are not hidden by anything: about 5 us a launch.
+// Inside a decode step (batch 24, Gemma2-2B shape) with every product of a layer on this
+// kernel the step took 4.57 ms against 4.22 ms with the library's products.
 SIB_EXPORT int sib_linear_rows_tc(const void* W, const void* x, void* y, int out_dtype, int R, int N,
                                   int K, int x_stride, int y_stride, int epilogue, float cap,
                                   int ksplit, int stages, void* stream) {
@@ -482,8 +484,13 @@ SIB_EXPORT int sib_linear_rows_tc(const void* W, const void* x, void* y, int out
             // stages, 209-297 us with three or four, 286-394 us with six)
             stages = 2;
         } else {
-            // two blocks per SM if each still gets three stages, else one block with what fits
-            const size_t two = 112 * 1024, one = 224 * 1024;
+            // two blocks per SM if each still gets three stages, else one block with what fits.
+            // (Measured inside a decode step of 24 rows with every product on this kernel:
+            // blocks of 98 KB, two of which fill an SM's shared memory, made the step 6.45 ms
+            // with chained launches and 4.55 ms without; blocks of 78 KB 4.57 ms with them.
+            // A kernel that takes all of an SM's shared memory does not get along with
+            // programmatic dependent launches of its neighbours; so at most 80 KB a block.)
+            const size_t two = 80 * 1024, one = 224 * 1024;
             stages = (int)((two - fixed) / stage_bytes);
             if (fixed > two || stages < 3) stages = (int)((one - fixed) / stage_bytes);
             if (stages > MAX_STAGES) stages = MAX_STAGES;
