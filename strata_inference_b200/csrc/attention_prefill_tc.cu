@@ -34,7 +34,10 @@
 // Reference: src/backend/cuda/kernels.rs:3183-3430 (batched_causal_attention).
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
+#include <queue>
+#include <vector>
 
 #include "common.cuh"
 
@@ -290,6 +293,18 @@ struct TcArgs {
 template <int HD>
 __host__ __device__ constexpr size_t part_floats() { return (size_t)BM * (HD + 2); }
 
+// BALANCE.  When the host knows the prompts' lengths, a launch is a list of work items
+// instead of a grid over (block of query rows, sequence, kv head): one item per block (or
+// pair) of query rows, or two for a block whose run of key tiles is split, ordered by the
+// work in them, longest first, so that blocks are handed to the SMs in that order.  Which
+// blocks are split is what makes the longest SM's share smallest (plan_items below).
+constexpr int MAX_ITEMS = 384;
+struct TcItems {
+    int n;                       // 0: the launch is a grid (see the kernel)
+    uint32_t where[MAX_ITEMS];   // sequence << 20 | kv head << 12 | block of query rows (of NB * MP positions)
+    uint32_t what[MAX_ITEMS];    // split unit (0xFFFFFF: not split) | part << 24
+};
+
 // Barriers of one block.
 struct Bars {
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pair[4],
@@ -305,7 +320,8 @@ struct Bars {
 // leave room for two of each in flight at head size 256.
 template <int HD, int G, bool PAIR>
 __global__ void __launch_bounds__(320)
-attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
+                            const __grid_constant__ TcItems items) {
     static_assert(!PAIR || HD >= 128, "half of the value columns must fill a 128-byte row");
     constexpr int MP = BM / G;                 // positions per block
     constexpr int CH = HD / 64;                // 64-wide column chunks of a head
@@ -330,19 +346,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y, kvh = blockIdx.z % p.n_kv, part = blockIdx.z / p.n_kv;
-    const int n = p.seq_len[b];
     const int rank = PAIR ? (int)cluster_ctarank() : 0;
-    // the longest tiles first; first0: the first position of the block or of the pair
-    const int first0 = (int)(gridDim.x / NB - 1 - blockIdx.x / NB) * (NB * MP);
+    int b, kvh, part, first0;           // first0: the first position of the block or of the pair
+    size_t unit = 0;                    // which pair of partial results a split block uses
+    bool listed_split = false;
+    if (items.n > 0) {
+        const uint32_t where = items.where[blockIdx.x / NB], what = items.what[blockIdx.x / NB];
+        b = (int)(where >> 20);
+        kvh = (int)((where >> 12) & 0xFFu);
+        first0 = (int)(where & 0xFFFu) * (NB * MP);
+        part = (int)((what >> 24) & 1u);
+        listed_split = (what & 0xFFFFFFu) != 0xFFFFFFu;
+        unit = (size_t)(what & 0xFFFFFFu) * NB + rank;
+    } else {
+        b = blockIdx.y;
+        kvh = blockIdx.z % p.n_kv;
+        part = blockIdx.z / p.n_kv;
+        // the longest tiles first
+        first0 = (int)(gridDim.x / NB - 1 - blockIdx.x / NB) * (NB * MP);
+        unit = ((size_t)b * p.n_kv + kvh) * gridDim.x + blockIdx.x;
+    }
+    const int n = p.seq_len[b];
     const int p0 = first0 + rank * MP;
     if (first0 >= n) return;                               // (both blocks of a pair)
     const int row0 = p.seq_row0[b];
     const int k_hi = min(n, first0 + NB * MP);
     const int k_lo = p.window > 0 ? max(0, first0 - p.window + 1) : 0;
     int kt0 = k_lo / BN, nt = (k_hi + BN - 1) / BN - kt0;
-    // a long run of key tiles is shared with the block that has the other blockIdx.z / n_kv
-    const bool is_split = p.split_tiles > 0 && nt >= p.split_tiles;
+    // a long run of key tiles is shared with the block that has the other part
+    // (the other blockIdx.z / n_kv of a grid, the other item of a list)
+    const bool is_split = items.n > 0 ? listed_split : (p.split_tiles > 0 && nt >= p.split_tiles);
     if (part == 1 && !is_split) return;                    // (both blocks of a pair)
     if (is_split) {
         const int first_half = (nt + 1) / 2;
@@ -612,8 +645,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p) {
         const float* theirs = nullptr;       // the other half's accumulator columns of this thread
         float l_all = l + l_other;
         if (ok && is_split) {
-            // the block's place among all blocks of query rows, and its two partial results
-            const size_t unit = ((size_t)b * p.n_kv + kvh) * gridDim.x + blockIdx.x;
+            // the block's two partial results
             float* mine = p.part + (unit * 2 + part) * part_floats<HD>();
             theirs = p.part + (unit * 2 + (part ^ 1)) * part_floats<HD>();
             // layout: [HD columns][128 rows], then [128 rows][max, sum]
@@ -722,8 +754,8 @@ SIB_EXPORT int sib_attention_prefill_tc_supports(int n_heads, int n_kv, int head
 }
 
 template <int HD, int G, bool PAIR>
-static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int max_len,
-                     cudaStream_t s) {
+static int launch_tc(const CUtensorMap& map, const TcArgs& p, const TcItems& items, int n_seqs,
+                     int max_len, cudaStream_t s) {
     constexpr int ST = (HD == 256 && !PAIR) ? 1 : 2;
     constexpr int NB = PAIR ? 2 : 1;
     const size_t smem = 1024 + (size_t)BM * HD * 2 + 2 * ST * (size_t)BN * HD * 2 / NB + sizeof(Bars) +
@@ -738,6 +770,7 @@ static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int ma
     const int q_blocks = (max_len + MP - 1) / MP;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(NB * ((q_blocks + NB - 1) / NB), n_seqs, p.n_kv * (p.split_tiles > 0 ? 2 : 1));
+    if (items.n > 0) cfg.gridDim = dim3(NB * items.n, 1, 1);
     cfg.blockDim = dim3(320, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
@@ -758,7 +791,7 @@ static int launch_tc(const CUtensorMap& map, const TcArgs& p, int n_seqs, int ma
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    e = cudaLaunchKernelEx(&cfg, kernel, map, p);
+    e = cudaLaunchKernelEx(&cfg, kernel, map, p, items);
     if (e != cudaSuccess) {
         sib_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
@@ -773,6 +806,176 @@ static bool tc_pairs_allowed() {
         return !(v && v[0] == '0');
     }();
     return allowed;
+}
+
+// ---------------------------------------------------------------------------
+// BALANCE: the list of work items for prompts whose lengths the host knows.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct PlanBlock { int b, qblk, nt; };
+struct PlanItem { int b, kvh, qblk, part, unit; float cost; };
+
+// What an item costs in units of one key tile: its tiles, what a block pays before its
+// first tile and after its last (about 9 us against 2.4 us a tile), and the exchange of a
+// split block's partial results.
+static float env_float(const char* name, float fallback) {
+    const char* v = getenv(name);
+    return v ? (float)atof(v) : fallback;
+}
+static const float ITEM_OVERHEAD = env_float("SIB_PREFILL_ITEM_OVERHEAD", 4.0f);
+static const float SPLIT_OVERHEAD = env_float("SIB_PREFILL_SPLIT_OVERHEAD", 1.0f);
+
+// The items when blocks with at least `split_from` key tiles run as two halves; the time
+// of the busiest of `slots` places when items are handed out longest first.
+float plan_for(const std::vector<PlanBlock>& blocks, int n_kv, int split_from, int slots,
+               std::vector<PlanItem>* items, int* n_units) {
+    std::vector<PlanItem> list;
+    int units = 0;
+    for (const PlanBlock& blk : blocks)
+        for (int kvh = 0; kvh < n_kv; ++kvh) {
+            if (blk.nt >= split_from && blk.nt >= 2) {
+                const int first_half = (blk.nt + 1) / 2;
+                list.push_back({blk.b, kvh, blk.qblk, 0, units, first_half + ITEM_OVERHEAD + SPLIT_OVERHEAD});
+                list.push_back({blk.b, kvh, blk.qblk, 1, units,
+                                blk.nt - first_half + ITEM_OVERHEAD + SPLIT_OVERHEAD});
+                ++units;
+            } else {
+                list.push_back({blk.b, kvh, blk.qblk, 0, -1, blk.nt + ITEM_OVERHEAD});
+            }
+        }
+    std::stable_sort(list.begin(), list.end(),
+                     [](const PlanItem& x, const PlanItem& y) { return x.cost > y.cost; });
+    std::priority_queue<float, std::vector<float>, std::greater<float>> busy;
+    for (int i = 0; i < slots; ++i) busy.push(0.f);
+    float longest = 0.f;
+    for (const PlanItem& it : list) {
+        const float t = busy.top() + it.cost;
+        busy.pop();
+        busy.push(t);
+        longest = std::max(longest, t);
+    }
+    if (items) *items = list;
+    if (n_units) *n_units = units;
+    return longest;
+}
+
+bool plan_items_now(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int window, int sms,
+                    TcItems* out, int* n_units);
+
+// Fills `out` for prompts of `lens` (host memory); false if a list does not fit or pay.
+// (Every layer of a step asks for the same few plans: the last ones are kept.)
+bool plan_items(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int window, int sms,
+                TcItems* out, int* n_units) {
+    struct Kept {
+        std::vector<int> key;
+        TcItems items;
+        int units = 0;
+        bool ok = false;
+    };
+    static thread_local Kept kept[4];
+    static thread_local int next = 0;
+    if (!lens || n_seqs <= 0) return false;
+    std::vector<int> key(lens, lens + n_seqs);
+    const int tail[6] = {n_kv, G, head_dim, window, sms, tc_pairs_allowed() ? 1 : 0};
+    key.insert(key.end(), tail, tail + 6);
+    for (Kept& k : kept)
+        if (k.key == key) {
+            if (k.ok) {
+                *out = k.items;
+                if (n_units) *n_units = k.units;
+            }
+            return k.ok;
+        }
+    Kept& k = kept[next];
+    next = (next + 1) % 4;
+    k.key = key;
+    k.units = 0;
+    k.ok = plan_items_now(lens, n_seqs, n_kv, G, head_dim, window, sms, &k.items, &k.units);
+    if (k.ok) {
+        *out = k.items;
+        if (n_units) *n_units = k.units;
+    }
+    return k.ok;
+}
+
+bool plan_items_now(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int window, int sms,
+                    TcItems* out, int* n_units) {
+    static const bool allowed = [] {
+        const char* v = getenv("SIB_PREFILL_BALANCE");
+        return !(v && v[0] == '0');
+    }();
+    if (!allowed || !lens || n_seqs <= 0 || n_seqs >= 4096 || n_kv > 255) return false;
+    const bool pair = head_dim >= 128 && tc_pairs_allowed();
+    const int NB = pair ? 2 : 1, span = NB * (BM / G), slots = std::max(1, sms / NB);
+    std::vector<PlanBlock> blocks;
+    int nt_max = 0;
+    for (int b = 0; b < n_seqs; ++b) {
+        const int n = lens[b];
+        if (n < 0) return false;
+        for (int q = 0; q * span < n; ++q) {
+            if (q >= 4096 || (long long)(blocks.size() + 1) * n_kv > MAX_ITEMS) return false;
+            const int first0 = q * span, k_hi = std::min(n, first0 + span);
+            const int k_lo = window > 0 ? std::max(0, first0 - window + 1) : 0;
+            const int nt = (k_hi + BN - 1) / BN - k_lo / BN;
+            blocks.push_back({b, q, nt});
+            nt_max = std::max(nt_max, nt);
+        }
+    }
+    if (blocks.empty()) return false;
+    // no split, or every block from some length on
+    int best_from = nt_max + 1;
+    float best = plan_for(blocks, n_kv, best_from, slots, nullptr, nullptr);
+    for (int from = nt_max; from >= 2; --from) {
+        long long count = 0;
+        for (const PlanBlock& blk : blocks) count += (blk.nt >= from ? 2 : 1) * n_kv;
+        if (count > MAX_ITEMS) break;
+        const float t = plan_for(blocks, n_kv, from, slots, nullptr, nullptr);
+        if (t < best - 0.25f) {
+            best = t;
+            best_from = from;
+        }
+    }
+    std::vector<PlanItem> items;
+    plan_for(blocks, n_kv, best_from, slots, &items, n_units);
+    out->n = (int)items.size();
+    for (size_t i = 0; i < items.size(); ++i) {
+        const PlanItem& it = items[i];
+        out->where[i] = ((uint32_t)it.b << 20) | ((uint32_t)it.kvh << 12) | (uint32_t)it.qblk;
+        out->what[i] = (it.unit < 0 ? 0xFFFFFFu : (uint32_t)it.unit) | ((uint32_t)it.part << 24);
+    }
+    return true;
+}
+
+int device_sms() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return 0;
+    return sms;
+}
+
+}  // namespace
+
+// What a launch for prompts of these lengths (host memory) needs to run as a balanced list
+// of work items: bytes of scratch memory and ticket counters (int, zero between launches)
+// for the blocks it splits.  Returns the number of items, 0 if such a launch is a grid.
+SIB_EXPORT int sib_attention_prefill_tc_plan(const int* host_lens, int n_seqs, int n_heads, int n_kv,
+                                             int head_dim, int window, long long* scratch_bytes,
+                                             int* n_tickets) {
+    if (scratch_bytes) *scratch_bytes = 0;
+    if (n_tickets) *n_tickets = 0;
+    if (n_kv <= 0 || n_heads % n_kv) return 0;
+    TcItems items;
+    int units = 0;
+    if (!plan_items(host_lens, n_seqs, n_kv, n_heads / n_kv, head_dim, window, device_sms(), &items,
+                    &units))
+        return 0;
+    const int nb = (head_dim >= 128 && tc_pairs_allowed()) ? 2 : 1;
+    if (scratch_bytes)
+        *scratch_bytes = (long long)units * nb * 2 * (long long)BM * (head_dim + 2) * sizeof(float);
+    if (n_tickets) *n_tickets = units * nb * 8;
+    return items.n;
 }
 
 // Attention of `n_seqs` packed prompts that all start at position 0; `total_rows`
@@ -814,7 +1017,7 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
                                         int max_len, int n_heads, int n_kv, int head_dim,
                                         float scale, float softcap, int window, void* scratch,
                                         long long scratch_bytes, int* tickets, int n_tickets,
-                                        void* stream) {
+                                        const int* host_lens, void* stream) {
     if (n_seqs == 0 || max_len == 0) return 0;
     SIB_REQUIRE(sib_attention_prefill_tc_supports(n_heads, n_kv, head_dim, width),
                 "attention_prefill_tc: heads=%d kv_heads=%d head_dim=%d is not a shape this kernel "
@@ -852,14 +1055,31 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
     if (scratch == nullptr || tickets == nullptr || scratch_bytes < need_bytes ||
         n_tickets < need_tickets || ((uintptr_t)scratch % 16) != 0)
         split_tiles = 0;
+    const int G = n_heads / n_kv;
+    // with the lengths known on the host: a balanced list of work items, if the caller
+    // brought the memory that its split blocks need
+    static thread_local TcItems items;
+    items.n = 0;
+    if (host_lens) {
+        int units = 0;
+        if (plan_items(host_lens, n_seqs, n_kv, G, head_dim, window, device_sms(), &items, &units)) {
+            const int nb = (head_dim >= 128 && tc_pairs_allowed()) ? 2 : 1;
+            const long long bytes = (long long)units * nb * 2 * (long long)BM * (head_dim + 2) * sizeof(float);
+            if (units > 0 && (scratch == nullptr || tickets == nullptr || scratch_bytes < bytes ||
+                              n_tickets < units * nb * 8 || ((uintptr_t)scratch % 16) != 0))
+                items.n = 0;
+        } else {
+            items.n = 0;
+        }
+    }
+    if (items.n > 0) split_tiles = 0;
     TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, error_flag, (float*)scratch, tickets,
              split_tiles, n_heads, n_kv, window, scale, softcap};
     cudaStream_t s = (cudaStream_t)stream;
-    const int G = n_heads / n_kv;
 #define BY_G(HD, PAIR)                                                         \
     do {                                                                       \
-        if (G == 1) return launch_tc<HD, 1, PAIR>(map, p, n_seqs, max_len, s); \
-        return launch_tc<HD, 2, PAIR>(map, p, n_seqs, max_len, s);             \
+        if (G == 1) return launch_tc<HD, 1, PAIR>(map, p, items, n_seqs, max_len, s); \
+        return launch_tc<HD, 2, PAIR>(map, p, items, n_seqs, max_len, s);             \
     } while (0)
     if (head_dim == 64) BY_G(64, false);
     if (tc_pairs_allowed()) {

@@ -13,7 +13,7 @@ from __future__ import annotations
 import ctypes
 import functools
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Callable, Dict, List, Optional, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -517,17 +517,34 @@ def attention_prefill_tc_split(n_seqs: int, max_len: int, n_heads: int, n_kv: in
     return int(nbytes.value), int(n_tickets.value)
 
 
+def attention_prefill_tc_plan(lens: Sequence[int], n_heads: int, n_kv: int, head_dim: int,
+                              window: int):
+    """(work items, bytes of scratch memory, ticket counters) of a launch for prompts of these
+    lengths that runs as a balanced list of work items; (0, 0, 0) if it would run as a grid."""
+    from ctypes import byref
+    nbytes, n_tickets = c_longlong(0), c_int(0)
+    arr = (c_int * len(lens))(*[int(n) for n in lens])
+    n_items = library().sib_attention_prefill_tc_plan(arr, c_int(len(lens)), c_int(n_heads),
+                                                      c_int(n_kv), c_int(head_dim), c_int(window),
+                                                      byref(nbytes), byref(n_tickets))
+    return int(n_items), int(nbytes.value), int(n_tickets.value)
+
+
 @_timed(lambda qkv, out, seq_row0, seq_len, n_seqs, max_len, n_heads, n_kv, head_dim, scale,
-        softcap, window, scratch=None, tickets=None: _prompt_work(
+        softcap, window, scratch=None, tickets=None, host_lens=None: _prompt_work(
             "attention_prefill_tc (tcgen05)", qkv, seq_len, n_heads, head_dim, window))
 def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                          max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                          softcap: float, window: int, scratch: Optional[torch.Tensor] = None,
-                         tickets: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         tickets: Optional[torch.Tensor] = None,
+                         host_lens: Optional[Sequence[int]] = None) -> torch.Tensor:
     """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu).  With ``scratch``
     and ``tickets`` (int32, zero before the first call; every call leaves them zero) of the
     sizes ``attention_prefill_tc_split`` gives, a launch that cannot fill the device runs its
-    long blocks of query rows as two halves."""
+    long blocks of query rows as two halves.  With ``host_lens`` (the prompts' lengths, as
+    ``seq_len`` holds them on the device) and memory of the sizes ``attention_prefill_tc_plan``
+    gives, the launch is a list of work items ordered by their work, with the blocks split
+    that make the busiest SM's share smallest."""
     _want(qkv, torch.bfloat16, "qkv")
     _want(out, torch.bfloat16, "out")
     if out.shape[0] != qkv.shape[0] or out.shape[1] != n_heads * head_dim:
@@ -539,7 +556,9 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
         _ptr(seq_len), c_int(n_seqs), c_int(max_len), c_int(n_heads), c_int(n_kv), c_int(head_dim),
         c_float(scale), c_float(softcap), c_int(window), _ptr(scratch),
         c_longlong(scratch.numel() * scratch.element_size() if scratch is not None else 0),
-        _ptr(tickets), c_int(tickets.numel() if tickets is not None else 0), _stream()))
+        _ptr(tickets), c_int(tickets.numel() if tickets is not None else 0),
+        None if host_lens is None else (c_int * len(host_lens))(*[int(n) for n in host_lens]),
+        _stream()))
     return out
 
 

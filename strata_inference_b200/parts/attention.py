@@ -195,12 +195,21 @@ class Attention:
         if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
                 native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
             # a launch too small for the device splits its long blocks, given the memory
-            need, n_tickets = native.attention_prefill_tc_split(ctx.n_seqs, ctx.max_count, nh,
-                                                               self.nkv, hd)
+            # (with the lengths known on the host, not in a recorded step, the launch is a
+            # balanced list of work items)
+            lens = None if ctx.graph_capture else ctx.counts
+            n_items = 0
+            if lens is not None:
+                n_items, need, n_tickets = native.attention_prefill_tc_plan(lens, nh, self.nkv, hd,
+                                                                            self.window)
+            if n_items == 0:
+                lens = None
+                need, n_tickets = native.attention_prefill_tc_split(ctx.n_seqs, ctx.max_count, nh,
+                                                                   self.nkv, hd)
             native.attention_prefill_tc(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
                                         ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,
                                         self.window, rt.scratch(need) if need else None,
-                                        rt.tickets(n_tickets) if need else None)
+                                        rt.tickets(n_tickets) if need else None, lens)
         elif fresh and qkv.dtype == torch.bfloat16 and \
                 native.attention_prefill_supports(nh, self.nkv, hd):
             native.attention_prefill(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,

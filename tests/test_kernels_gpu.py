@@ -323,6 +323,54 @@ def test_attention_prefill_tc_kernel_splits_long_blocks(nh, nkv, hd, window, cap
             _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"split prefill, sequence of {T}, call {call}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,cap,lens", [
+    (8, 4, 256, 0, 50.0, [2048]), (4, 2, 256, 700, 50.0, [1500, 40, 333]),
+    (2, 2, 128, 0, 0.0, [900, 1100]), (2, 1, 64, 0, 0.0, [1300, 129, 5]),
+    (4, 2, 128, 300, 30.0, [64, 2000]), (8, 4, 256, 0, 0.0, [300])])
+def test_attention_prefill_tc_kernel_as_a_balanced_list_of_work(nh, nkv, hd, window, cap, lens):
+    """With the prompts' lengths known on the host the launch is a list of work items, the
+    longest first, and the blocks are split whose halves make the busiest SM's share
+    smallest: the same results as the plain implementation, twice through the same
+    tickets; without memory for the split blocks it falls back to a grid."""
+    n = _native()
+    g = torch.Generator().manual_seed(17)
+    dtype = torch.bfloat16
+    scale = 3.0 / math.sqrt(hd)
+    qs, refs = [], []
+    for T in lens:
+        q = torch.randn(T, nh, hd, generator=g).to(dtype)
+        k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        refs.append(plain.attention(q.double(), k.double(), v.double(), scale, cap, window))
+        qs.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    packed = torch.cat(qs, dim=0).contiguous().to(DEV)
+    row0 = [0]
+    for T in lens[:-1]:
+        row0.append(row0[-1] + T)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n_items, need, n_tickets = n.attention_prefill_tc_plan(lens, nh, nkv, hd, window)
+    if os.environ.get("SIB_PREFILL_BALANCE") == "0":
+        pytest.skip("the balanced list is switched off")
+    span = 128 // (nh // nkv) * (2 if hd >= 128 else 1)
+    blocks = sum(-(-T // span) for T in lens) * nkv
+    assert n_items >= blocks                      # every block once, split ones twice
+    assert (n_items > blocks) == (need > 0)
+    if max(lens) >= 1000:
+        assert need > 0, "a long prompt alone on the device has blocks worth splitting"
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
+    tickets = torch.zeros(max(n_tickets, 1), dtype=torch.int32, device=DEV)
+    for call in range(3):
+        out = torch.full((sum(lens), nh * hd), float("nan"), dtype=dtype, device=DEV)
+        # (the third call brings no memory: a grid, unless nothing was to be split anyway)
+        mem = (scratch, tickets) if call < 2 else (None, None)
+        n.attention_prefill_tc(packed, out, i32(row0), i32(lens), len(lens), max(lens), nh, nkv, hd,
+                               scale, cap, window, mem[0], mem[1], lens)
+        assert n.attention_prefill_tc_error() == 0
+        assert int(tickets.abs().sum()) == 0, "the tickets are put back"
+        for r0, T, ref in zip(row0, lens, refs):
+            _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"balanced prefill, sequence of {T}, call {call}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
 @pytest.mark.parametrize("hd,rot", [(48, 32), (64, 64), (16, 16)])
