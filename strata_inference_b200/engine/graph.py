@@ -117,7 +117,7 @@ class DecodeGraph:
             # that a part that cannot be captured fails here, before any recording)
             self.last_logits, result = self._forward(seqs, capture=use_graph)
             self.launches_per_step = native.launch_count() - before
-            if use_graph and self.calls >= 1:
+            if use_graph and self.calls >= 1 and native.recording_allowed():
                 # The eager run above was this step (and warmed up every library
                 # the step uses).  The capture records the same launches for the
                 # steps to come and runs nothing; its output buffers are the ones
@@ -193,7 +193,7 @@ class PromptGraph:
             # (which warms up what the step uses); the second time the same launches are
             # also recorded for the steps to come, which runs nothing.
             result = self._forward(padded)
-            if self.calls >= 1:
+            if self.calls >= 1 and native.recording_allowed():
                 g = torch.cuda.CUDAGraph()
                 collecting = gc.isenabled()
                 gc.collect()

@@ -202,6 +202,12 @@ class _NoRegion:
 _NO_REGION = _NoRegion()
 
 
+def recording_allowed() -> bool:
+    """False while a profile without a plan is active: its events and the work it reads
+    from the device cannot go into a CUDA graph, so steps are not recorded meanwhile."""
+    return _profile is None or _profile.plan is not None
+
+
 def _nbytes(*tensors) -> int:
     return sum(t.numel() * t.element_size() for t in tensors if t is not None)
 

@@ -619,3 +619,26 @@ def test_products_of_some_rows_on_the_streaming_tensor_core_kernel(model_dirs, n
     for s in slots:
         eng.end_sequence(s)
     eng.read_back(got)       # (no bounded wait ran out)
+
+
+def test_a_profiled_step_is_not_recorded(model_dirs):
+    """While a kernel profile is being taken, steps are launched kernel by kernel (a
+    profile's events cannot go into a CUDA graph); afterwards they are recorded as usual."""
+    from strata_inference_b200.engine.profile import profile_step
+    cfg = CONFIGS["A"]
+    eng = _engine(model_dirs, "A", "bfloat16", 64)
+    toks = random_prompts(cfg, [40], seed=5)[0]
+    ref = plain_logits(toks, model_dirs["A", "bfloat16"], cfg)[-1:]
+    for i in range(3):
+        slot = eng.new_sequence()
+        got = []
+        rows, ms = profile_step(lambda: got.append(eng.step([(slot, toks)])))
+        assert any(r["name"].startswith("attention") for r in rows) and ms > 0
+        assert_logits_close(got[0], ref, "bfloat16", f"profiled prompt step {i}")
+        eng.end_sequence(slot)
+    graph = list(eng._prompt_graphs.values())[0]
+    assert graph.graph is None
+    slot = eng.new_sequence()
+    assert_logits_close(eng.step([(slot, toks)]), ref, "bfloat16", "recorded afterwards")
+    assert graph.graph is not None
+    eng.end_sequence(slot)
