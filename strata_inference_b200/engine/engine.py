@@ -176,7 +176,7 @@ class Engine:
         one costs more than running them, and few wanted rows (a recorded step keeps a
         logits buffer of that many rows)."""
         return (self.prompt_graph_rows > 0 and self.model.captures_prompts
-                and self.rt.skinny_max_rows < n_rows <= self.prompt_graph_rows
+                and self.rt.fused_rope_max_rows < n_rows <= self.prompt_graph_rows
                 and 0 < n_want <= 64 and all(st == 0 for _, st, _ in seqs))
 
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],

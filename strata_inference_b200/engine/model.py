@@ -149,7 +149,7 @@ class DecoderModel:
         """Run every schedule entry over the step's rows; returns the 32-bit
         residual stream [rows, hidden]."""
         rt = self.rt
-        if rt.chain_steps and rt.dtype == torch.bfloat16 and 0 < ctx.n_rows <= rt.skinny_max_rows:
+        if rt.chain_steps and rt.dtype == torch.bfloat16 and 0 < ctx.n_rows <= rt.chain_max_rows:
             # few rows: what lies between two attention kernels runs as one kernel
             with rt.chaining(ctx.n_rows):
                 return self._walk(ctx)

@@ -162,7 +162,7 @@ class Attention:
         w_in = self.w_qkv if owns_cache else self.w_q
         rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
         if (rotary is not None and rotary[1] == hd and rotary[2] == native.ROPE_HALF_SPLIT
-                and x.dtype == torch.bfloat16 and rt.fuse_rotation and 0 < R <= rt.skinny_max_rows
+                and x.dtype == torch.bfloat16 and rt.fuse_rotation and 0 < R <= rt.fused_rope_max_rows
                 and self.hidden % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0):
             # few rows: the product rotates q and k and writes k and v into the cache itself

@@ -72,10 +72,16 @@ class Runtime:
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
         torch.set_float32_matmul_precision("highest")
-        # Up to this many rows a product goes to the weight-streaming kernel (which
-        # takes up to native.SKINNY_MAX_ROWS); measured on a B200 at Gemma2-2B sizes it
-        # is ahead of the library product up to 16 rows and behind it from 32 on.
-        self.skinny_max_rows = 16
+        # Up to this many rows a product goes to the weight-streaming kernel (which takes up
+        # to native.SKINNY_MAX_ROWS).  Measured inside decode steps on a B200: with 9 to 16
+        # rows (two activation tiles per warp) the library product is ahead, by 3-9 % of the
+        # step at Gemma2-2B sizes, 9 % at 9B and 16 % at 27B sizes (batch 16); with up to 8
+        # rows the kernel is far ahead (a layer's products: 45 us against 66 us).
+        self.skinny_max_rows = 8
+        # The q|k|v product that rotates and stores in its epilogue stays ahead of the
+        # library product followed by the rotation kernel up to 16 rows (and behind from 17).
+        self.fused_rope_max_rows = 16
+        self.chain_max_rows = 16     # what the (optional) chain kernel of few-row steps takes
         # Up to 128 rows against a matrix of so many rows that its 128-row tiles are several
         # waves of blocks go to the tcgen05 weight-streaming product (csrc/linear_rows_tc.cu):
         # there it reads at 0.91 of the copy bandwidth; with fewer tiles the library is as fast.

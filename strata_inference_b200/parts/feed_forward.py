@@ -68,7 +68,8 @@ class GatedMLP:
         rt = self.rt
         R = x.shape[0]
         if (self.group == _GROUP and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
-                and (R <= rt.skinny_max_rows or R > rt.gated_gemm_min_rows)):
+                and (R <= rt.skinny_max_rows or R > rt.gated_gemm_min_rows
+                     or (rt.chain is not None and R <= rt.chain_max_rows))):
             t = rt.linear(x, self.w_gate_up, epilogue=native.EPI_GEGLU)
         else:
             gate_up = rt.linear(x, self.w_gate_up)
