@@ -79,8 +79,9 @@ constexpr int MAX_SPLITS = 128;
 
 // HD: head size (64, 128 or 256).  G: query heads per kv head (1, 2, 4 or 8).  EARLY: the first
 // tile of keys may be fetched before the kernel ahead of this one has finished (it shortens
-// the chain of waits of a step of one or two rows; with more rows the registers that the
-// tile holds across the wait cost more than the wait: batch 8 ran 2 % slower with it).
+// the chain of waits of a step of one row: batch 1 runs 1.5 % faster with it; with more rows
+// the registers that the tile holds across the wait cost more than the wait: batch 2 ran 3 %
+// and batch 8 2 % slower with it).
 template <int HD, int G, bool EARLY>
 __global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p) {
     constexpr int KB = HD / 32;          // 32-wide blocks of the head dimension
@@ -419,7 +420,7 @@ static int attention_decode(
     SIB_REQUIRE(blocks < (1ll << 31), "attention_decode: too many rows (%d)", rows);
     cudaStream_t s = (cudaStream_t)stream;
     const int G = n_heads / n_kv;
-    const bool early_keys = fresh > 0 && rows <= 2;
+    const bool early_keys = fresh > 0 && rows == 1;
 #define GO(HD, GG)                                                                                 \
     do {                                                                                           \
         if (early_keys)                                                                            \
