@@ -76,6 +76,7 @@ class Engine:
         self.max_graphs = 8
         self.prompt_graph_rows = 1024   # steps of prompts of up to this many rows are recorded
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
+        self._latest_step = None    # key of the recorded single-token step that ran last, if one did
         self._read_ring = None      # pinned buffers and events of read_later, made at first use
         self._reads = 0
 
@@ -194,6 +195,7 @@ class Engine:
         (``prompt_graph_rows``: the most rows of such a step; 0: none are recorded).
         """
         seqs, tokens, want_rows = self._prepare(entries, want)
+        self._latest_step = None        # (no later step may be fed with an earlier step's tokens)
         self.cache.reserve([(s, n) for s, _, n in seqs])
         try:
             if self._recorded_prompts(seqs, int(tokens.size), len(want_rows)):
@@ -262,15 +264,21 @@ class Engine:
                 # [sequences, vocab] 32-bit logits buffer beside its activations)
                 self._graphs.pop(next(iter(self._graphs)))
         self._graphs[key] = g       # most recently used last
+        if tokens is None and self._latest_step != key:
+            raise StepError("a step can take its tokens from the device only right after a step "
+                            "of the same sequences through the same recorded step")
+        self._latest_step = None
         out = g.run(slots, tokens, use_graph)
+        self._latest_step = key
         self.last_logits = g.last_logits
         return out
 
     def can_feed_back(self, slots: Sequence[int], temperature: float = 0.0, top_k: int = 0,
                       top_p: float = 1.0) -> bool:
         """Whether ``decode_step(slots, None, ...)`` is possible now."""
-        g = self._graphs.get((len(slots), float(temperature), int(top_k), float(top_p)))
-        return g is not None and g.can_feed_back(slots)
+        key = (len(slots), float(temperature), int(top_k), float(top_p))
+        g = self._graphs.get(key)
+        return g is not None and self._latest_step == key and g.can_feed_back(slots)
 
     def read_later(self, t: torch.Tensor):
         """Start bringing the integer tensor ``t`` (at most one value per slot) to the host:

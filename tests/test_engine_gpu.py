@@ -642,3 +642,31 @@ def test_a_profiled_step_is_not_recorded(model_dirs):
     assert_logits_close(eng.step([(slot, toks)]), ref, "bfloat16", "recorded afterwards")
     assert graph.graph is not None
     eng.end_sequence(slot)
+
+
+def test_tokens_are_fed_on_the_device_only_right_after_the_step_that_sampled_them(model_dirs):
+    from strata_inference_b200.engine.engine import StepError
+    cfg = CONFIGS["A"]
+    eng = _engine(model_dirs, "A", "float32", 64)
+    toks = random_prompts(cfg, [30, 30], seed=12)
+    ref = [plain_logits(t, model_dirs["A", "float32"], cfg) for t in toks]
+    slots = [eng.new_sequence(), eng.new_sequence()]
+    eng.step([(s, t[:20]) for s, t in zip(slots, toks)])
+    assert not eng.can_feed_back(slots)
+    fed = [t[20] for t in toks]
+    for i in range(3):          # launched, recorded, replayed: greedy tokens of the plain logits
+        out = eng.decode_step(slots, fed)
+        want = [int(ref[b][20 + i].argmax()) for b in range(2)]
+        fed = eng.read_back(out)
+        assert fed == want
+        toks = [t[:21 + i] + [w] + t[22 + i:] for t, w in zip(toks, want)]
+        ref = [plain_logits(t, model_dirs["A", "float32"], cfg) for t in toks]
+    assert eng.can_feed_back(slots) and not eng.can_feed_back(slots[::-1])
+    out = eng.decode_step(slots, None)            # fed with `fed`, on the device
+    assert eng.read_back(out) == [int(ref[b][23].argmax()) for b in range(2)]
+    eng.step([(slots[0], [toks[0][24]])])         # another step in between: no feeding back
+    assert not eng.can_feed_back(slots)
+    with pytest.raises(StepError, match="right after"):
+        eng.decode_step(slots, None)
+    for s in slots:
+        eng.end_sequence(s)
