@@ -397,6 +397,44 @@ def run_kernel_tables(args):
     return 0
 
 
+def run_sweep(args):
+    """Decode steps over batch sizes at --context, and prompt steps over lengths: one line
+    each with the time, tokens a second and the fraction of the measured peak."""
+    import torch
+    from strata_inference_b200 import GenerationEngine
+    cfg = baseline_config()
+    cfg.update(SHAPES[args.shape])
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    context = args.context
+    peaks = measured_peaks()
+    batches = [b for b in (1, 2, 4, 8, 12, 16, 17, 24, 32, 48, 64, 96, 128)
+               if b * kv_bytes_per_sequence(cfg, context) < 120e9]
+    top = max(batches)
+    gen = GenerationEngine.from_random(cfg, seed=5, dtype="bfloat16", ctx=context,
+                                       max_tokens=max(top * context, 2 * 8192), max_slots=top)
+    engine = gen.engine
+    engine.max_graphs = 2
+    randomize_pools(engine)
+    weight_bytes = engine.model.weight_bytes()
+    print(f"Gemma2-{args.shape.upper()} shape, {cfg['num_hidden_layers']} layers, context {context}: "
+          f"decode steps (peak {peaks['hbm_gbs']:.0f} GB/s, {peaks['source']})")
+    for b in batches:
+        ms, lengths, _, _ = time_decode(engine, b, context, 12, 3, 3)
+        moved = weight_bytes + kv_bytes_per_step(engine, lengths)
+        print(f"  batch {b:4d}: {ms:7.3f} ms  {b * 1e3 / ms:8.0f} tok/s  "
+              f"{moved / (ms * 1e-3) / 1e9 / peaks['hbm_gbs']:.2f} of the copy bandwidth", flush=True)
+    print(f"prompt steps, one prompt (peak {peaks['bf16_tflops']:.0f} TFLOP/s)")
+    for T in (64, 128, 256, 512, 1024, 2048, 4096, 8192):
+        if T >= engine.max_seq_len:
+            continue
+        ms = time_prefill(engine, T, reps=3)
+        frac = prefill_flops(cfg, T) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
+        print(f"  {T:5d} tokens: {ms:7.2f} ms  {T / ms:6.1f} k tok/s  {frac:.2f} of the bf16 peak",
+              flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,6 +450,9 @@ def main():
                     help="instead of the timed run: per-kernel tables (CUDA events around every "
                          "kernel) of the captured decode step at --batch and of a 2,048-token "
                          "prompt step, on standard output")
+    ap.add_argument("--sweep", action="store_true",
+                    help="instead of the timed run: decode steps over batch sizes at --context "
+                         "and prompt steps over lengths, one line each, on standard output")
     ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
                     help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
@@ -428,6 +469,8 @@ def main():
         args.warmup = 3
     if args.kernels:
         return run_kernel_tables(args)
+    if args.sweep:
+        return run_sweep(args)
     return run_ours(args)
 
 
