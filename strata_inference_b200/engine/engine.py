@@ -180,6 +180,13 @@ class Engine:
                 and self.rt.fused_rope_max_rows < n_rows <= self.prompt_graph_rows
                 and 0 < n_want <= 64 and all(st == 0 for _, st, _ in seqs))
 
+    def _recorded_tokens(self, seqs, n_want: int) -> bool:
+        """Whether this step goes through a recorded single-token step that returns logits:
+        one token for every sequence, few wanted rows, parts that may be recorded."""
+        return (self.prompt_graph_rows > 0 and self.model.captures_prompts
+                and len(seqs) <= self.prompt_graph_rows and 0 < n_want <= 64
+                and all(n == 1 for _, _, n in seqs))
+
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
         """Run one step.
@@ -192,7 +199,8 @@ class Engine:
 
         Short steps of prompts are recorded into a CUDA graph the second time their shape
         (rows rounded up to 64, sequences, wanted rows) is seen and replayed from then on
-        (``prompt_graph_rows``: the most rows of such a step; 0: none are recorded).
+        (``prompt_graph_rows``: the most rows of such a step; 0: none are recorded); so are
+        steps of one token for every sequence, by the number of sequences and wanted rows.
         """
         seqs, tokens, want_rows = self._prepare(entries, want)
         self._latest_step = None        # (no later step may be fed with an earlier step's tokens)
@@ -200,6 +208,8 @@ class Engine:
         try:
             if self._recorded_prompts(seqs, int(tokens.size), len(want_rows)):
                 logits = self._prompt_step(seqs, tokens, want_rows)
+            elif self._recorded_tokens(seqs, len(want_rows)):
+                logits = self._prompt_step(seqs, tokens, want_rows, from_start=False)
             else:
                 ctx = self._step_context(seqs, tokens, want_rows)
                 self.cache.sync_tables()
@@ -213,13 +223,13 @@ class Engine:
             self.cache.advance(slot, n)
         return logits
 
-    def _prompt_step(self, seqs, tokens, want_rows) -> torch.Tensor:
+    def _prompt_step(self, seqs, tokens, want_rows, from_start: bool = True) -> torch.Tensor:
         from .graph import PromptGraph
-        rows = -(-int(tokens.size) // 64) * 64
-        key = ("prompts", rows, len(seqs), len(want_rows))
+        rows = -(-int(tokens.size) // 64) * 64 if from_start else int(tokens.size)
+        key = ("prompts" if from_start else "tokens", rows, len(seqs), len(want_rows))
         g = self._prompt_graphs.pop(key, None)
         if g is None:
-            g = PromptGraph(self, rows, len(seqs), len(want_rows))
+            g = PromptGraph(self, rows, len(seqs), len(want_rows), from_start)
             while len(self._prompt_graphs) >= self.max_graphs:
                 self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
         self._prompt_graphs[key] = g       # most recently used last

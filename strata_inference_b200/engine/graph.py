@@ -147,12 +147,16 @@ class DecodeGraph:
 
 class PromptGraph:
     """The step of ``n_seqs`` prompts from position 0 with ``rows`` rows in all (filled up
-    with the rows of one more sequence without a slot) and ``n_want`` wanted rows."""
+    with the rows of one more sequence without a slot) and ``n_want`` wanted rows; or, with
+    ``from_start=False``, the step of one token for each of ``n_seqs == rows`` sequences
+    wherever they stand (nothing to fill up), which returns logits where ``DecodeGraph``
+    samples."""
 
-    def __init__(self, engine, rows: int, n_seqs: int, n_want: int):
+    def __init__(self, engine, rows: int, n_seqs: int, n_want: int, from_start: bool = True):
         self.engine = engine
         self.rows, self.B, self.n_want = rows, n_seqs, n_want
-        size = StepContext.packed_size(rows, n_seqs + 1, n_want)
+        self.from_start = from_start
+        size = StepContext.packed_size(rows, n_seqs + (1 if from_start else 0), n_want)
         self.hosts = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
         self.copied = [None] * _STAGES
         self.meta = torch.zeros(size, dtype=torch.int32, device=engine.device)
@@ -163,18 +167,24 @@ class PromptGraph:
     def _forward(self, seqs):
         eng = self.engine
         ctx = StepContext(self.meta, seqs, self.n_want, eng.cache, eng.rt, graph_capture=True,
-                          from_start=True)
+                          from_start=self.from_start)
         return eng.model.logits(eng.model.hidden_states(ctx), ctx.want_rows)
 
     def run(self, seqs, tokens: np.ndarray, want_rows: Sequence[int]) -> torch.Tensor:
-        """``seqs``: ``(slot, 0, count)`` of the prompts, whose pages are reserved; returns
-        the 32-bit logits of the wanted rows, in a buffer that a later run may overwrite."""
+        """``seqs``: ``(slot, start, count)`` of the step's sequences, whose pages are reserved;
+        returns the 32-bit logits of the wanted rows, in a buffer that a later run may
+        overwrite."""
         eng = self.engine
         used = int(tokens.size)
         if len(seqs) != self.B or len(want_rows) != self.n_want or used > self.rows:
-            raise ValueError(f"this graph steps {self.B} prompts of {self.rows} rows in all")
-        padded = list(seqs) + [(-1, 0, self.rows - used)]
-        tokens = np.concatenate([tokens, np.zeros(self.rows - used, dtype=np.int64)])
+            raise ValueError(f"this graph steps {self.B} sequences of {self.rows} rows in all")
+        if self.from_start:
+            padded = list(seqs) + [(-1, 0, self.rows - used)]
+            tokens = np.concatenate([tokens, np.zeros(self.rows - used, dtype=np.int64)])
+        else:
+            if used != self.rows or any(n != 1 for _, _, n in seqs):
+                raise ValueError("this graph steps one token for each sequence")
+            padded = list(seqs)
         stage = self.calls % _STAGES
         if self.copied[stage] is not None:
             self.copied[stage].synchronize()

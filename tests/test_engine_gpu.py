@@ -565,8 +565,11 @@ def test_short_prompt_steps_replayed_from_a_recording(model_dirs, name, page, dt
             assert_logits_close(got, ref, dtype, f"{name} step {i} token {k} after the prompts")
         for s in slots:
             eng.end_sequence(s)
-    graphs = list(eng._prompt_graphs.values())
+    graphs = [g for key, g in eng._prompt_graphs.items() if key[0] == "prompts"]
     assert len(graphs) == 1 and graphs[0].graph is not None and graphs[0].calls == len(lens)
+    # (the single-token steps in between were recorded too, as one step of two sequences)
+    tokens = [g for key, g in eng._prompt_graphs.items() if key[0] == "tokens"]
+    assert len(tokens) == 1 and tokens[0].graph is not None and tokens[0].calls == 2 * len(lens)
     for s in held:
         eng.end_sequence(s)
     assert eng.cache.pages_in_use() == 0
