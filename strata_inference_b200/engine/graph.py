@@ -163,6 +163,7 @@ class PromptGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.calls = 0
+        self.unrecordable: Optional[str] = None     # why recording failed, if it did
 
     def _forward(self, seqs):
         eng = self.engine
@@ -203,7 +204,7 @@ class PromptGraph:
             # (which warms up what the step uses); the second time the same launches are
             # also recorded for the steps to come, which runs nothing.
             result = self._forward(padded)
-            if self.calls >= 1 and native.recording_allowed():
+            if self.calls >= 1 and native.recording_allowed() and not self.unrecordable:
                 g = torch.cuda.CUDAGraph()
                 collecting = gc.isenabled()
                 gc.collect()
@@ -211,9 +212,13 @@ class PromptGraph:
                 try:
                     with torch.cuda.graph(g, capture_error_mode="thread_local"):
                         self.logits = self._forward(padded)
+                    self.graph = g
+                except RuntimeError as e:
+                    # (the step itself has run; steps of this shape stay launched one by one)
+                    self.unrecordable = f"{type(e).__name__}: {e}"
+                    self.logits = None
                 finally:
                     if collecting:
                         gc.enable()
-                self.graph = g
         self.calls += 1
         return result
