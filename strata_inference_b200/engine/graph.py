@@ -51,6 +51,7 @@ class DecodeGraph:
         self.calls = 0
         self.launches_per_step = 0
         self.last_slots: Optional[list] = None      # of the latest run
+        self.out_is_latest = False      # whether `out` holds the tokens that the latest run sampled
 
     def _forward(self, seqs, capture: bool):
         eng, B = self.engine, self.B
@@ -65,7 +66,8 @@ class DecodeGraph:
     def can_feed_back(self, slots: Sequence[int]) -> bool:
         """Whether the next step of ``slots`` can take the tokens that the latest run sampled
         straight from the device: the graph is recorded and that run was for these slots."""
-        return self.graph is not None and self.last_slots == [int(s) for s in slots]
+        return (self.graph is not None and self.out_is_latest
+                and self.last_slots == [int(s) for s in slots])
 
     def run(self, slots: Sequence[int], tokens: Optional[Sequence[int]], use_graph: bool = True):
         """``tokens`` None: the tokens that the latest run sampled, which are still on the
@@ -111,7 +113,9 @@ class DecodeGraph:
         if self.graph is not None and use_graph:
             self.graph.replay()
             result, self.last_logits = self.out, self.logits
+            self.out_is_latest = True
         else:
+            self.out_is_latest = False      # (unless this run is recorded below)
             before = native.launch_count()
             # (a step that will be captured runs eagerly under the same rules first, so
             # that a part that cannot be captured fails here, before any recording)
@@ -141,6 +145,7 @@ class DecodeGraph:
                 # (the recording ran nothing: the tokens of this step, which the next step
                 # may be fed with on the device, are put where a replay would have put them)
                 self.out.copy_(result)
+                self.out_is_latest = True
         self.calls += 1
         return result
 
