@@ -22,6 +22,9 @@
 // each is done by a radix walk over the order-preserving integer image of z,
 // 4 bits a pass (16 buckets of count and mass per pass, 8 passes a search).
 // All sums are taken in a fixed order, so a draw is reproducible.
+// With top-k on and few candidates (at most SAMPLE_LIST at or above the k-th key, ties
+// included) only the first of the three searches runs, without masses; the candidates are
+// gathered into a list, sorted and walked one after the other (sample_from_short_list).
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -31,10 +34,14 @@ namespace cg = cooperative_groups;
 #define SAMPLE_CLUSTER 8
 #define SAMPLE_THREADS 512
 #define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+#define SAMPLE_LIST 256     // a top-k set of at most this many candidates is sorted and walked as a list
 
 __device__ __forceinline__ uint32_t order_key(float z) {
     const uint32_t u = __float_as_uint(z);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t key) {      // the z of a key
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
 struct SampleArgs {
@@ -68,6 +75,12 @@ struct SampleShared {
     float scan_f[SAMPLE_THREADS];
     int result;
     float before_f, total_f;
+    // the candidates of a short top-k list (used in the cluster's first block)
+    float list_z[SAMPLE_LIST];
+    int list_i[SAMPLE_LIST];
+    float sorted_z[SAMPLE_LIST];
+    int sorted_i[SAMPLE_LIST];
+    int list_n;
 };
 
 struct Cluster {
@@ -140,7 +153,7 @@ struct Crossing {
 // running mass reaches (inclusive) / exceeds (!inclusive) fraction x (mass of the set).
 __device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, float inv_t,
                                   float zmax, const Kept& kept, bool by_mass, int want_count,
-                                  float fraction, bool inclusive) {
+                                  float fraction, bool inclusive, bool with_mass = true) {
     SampleShared* sh = c.sh;
     Crossing r;
     r.key = 0;
@@ -163,7 +176,7 @@ __device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, 
             const uint32_t key = order_key(z);
             if (key > kept.floor_key && (key & path_mask) == (r.key & path_mask)) {
                 const int b = (key >> shift) & 15;
-                sh->bins_f[b][threadIdx.x] += expf(z - zmax);
+                if (with_mass) sh->bins_f[b][threadIdx.x] += expf(z - zmax);
                 sh->bins_i[b][threadIdx.x] += 1;
             }
         }
@@ -291,6 +304,79 @@ __device__ int nth_with_key(Cluster& c, const float* row, int lo, int hi, float 
     return cluster_share_found(c, sh->result);
 }
 
+// The top-k set as a list, when it is short: every block appends its elements with a key
+// of at least `floor_key` to the first block's list; the first block sorts the list
+// (descending z, ties by index: the order of the reference's sorted candidates), keeps
+// `top_k` of them and does the rest as the reference does it, one candidate after the
+// other: softmax, the shortest prefix whose mass reaches top_p, renormalisation, the draw
+// (src/engine/sampler.rs:100-152).  Returns the token in the first block's first thread
+// (-1 elsewhere); the caller shares it.
+__device__ int sample_from_short_list(Cluster& c, const float* row, int lo, int hi, float inv_t,
+                                      float zmax, uint32_t floor_key, int top_k, float top_p,
+                                      float r, int fallback) {
+    SampleShared* sh = c.sh;
+    for (int i = lo + threadIdx.x; i < hi; i += SAMPLE_THREADS) {
+        const float z = row[i] * inv_t;
+        if (order_key(z) >= floor_key) {
+            const int slot = atomicAdd(&c.first->list_n, 1);
+            if (slot < SAMPLE_LIST) {
+                c.first->list_z[slot] = z;
+                c.first->list_i[slot] = i;
+            }
+        }
+    }
+    c.g.sync();
+    int token = -1;
+    if (c.rank == 0) {
+        const int n = min(sh->list_n, SAMPLE_LIST);
+        if ((int)threadIdx.x < n) {
+            const float z = sh->list_z[threadIdx.x];
+            const int idx = sh->list_i[threadIdx.x];
+            int before = 0;
+            for (int j = 0; j < n; ++j) {
+                const float zj = sh->list_z[j];
+                before += (zj > z) || (zj == z && sh->list_i[j] < idx);
+            }
+            sh->sorted_z[before] = z;
+            sh->sorted_i[before] = idx;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int kept = min(n, top_k);
+            float total = 0.f;
+            for (int j = 0; j < kept; ++j) {
+                sh->list_z[j] = expf(sh->sorted_z[j] - zmax);      // (the list's own maximum is zmax)
+                total += sh->list_z[j];
+            }
+            int cut = kept;
+            float mass = total;           // of the candidates that stay
+            if (top_p < 1.0f) {
+                float cum = 0.f;
+                mass = 0.f;
+                for (int j = 0; j < kept; ++j) {
+                    const float pj = sh->list_z[j] / total;
+                    cum += pj;
+                    mass += sh->list_z[j];
+                    if (cum >= top_p) {
+                        cut = j + 1;
+                        break;
+                    }
+                }
+            }
+            token = kept > 0 ? sh->sorted_i[cut - 1] : fallback;
+            float cum = 0.f;
+            for (int j = 0; j < cut; ++j) {
+                cum += sh->list_z[j] / mass;
+                if (r < cum) {
+                    token = sh->sorted_i[j];
+                    break;
+                }
+            }
+        }
+    }
+    return token;
+}
+
 __global__ void __cluster_dims__(SAMPLE_CLUSTER, 1, 1) __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(SampleArgs p) {
     extern __shared__ __align__(16) unsigned char sample_smem[];
@@ -307,6 +393,7 @@ sample_rows_kernel(SampleArgs p) {
     const int lo = min(V, c.rank * per_block), hi = min(V, lo + per_block);
     const int which = p.rng_index ? p.rng_index[rowi] : rowi;
     const unsigned long long rng_before = p.temperature > 0.f ? p.rng[which] : 0ull;
+    if (threadIdx.x == 0) sh->list_n = 0;
     c.g.sync();   // every block is running and has read the generator's state
 
     // ---- the maximum and its first index ----
@@ -422,13 +509,26 @@ sample_rows_kernel(SampleArgs p) {
         if (token < 0) token = V - 1;      // the reference's fallback: the last candidate
     } else {
         Kept kept{0u, 0, 0.f};
+        bool listed = false;
         if (use_k) {
+            // (the search for the k-th largest counts only: no masses are summed)
             const Crossing k = find_crossing(c, row, lo, hi, inv_t, zmax, kept, false, p.top_k, 0.f,
-                                             true);
-            kept.floor_key = k.key;
-            kept.floor_ties = max(0, min(k.ties, p.top_k - k.above_count));
-            kept.floor_q = k.q;
+                                             true, false);
+            if (k.above_count + k.ties <= SAMPLE_LIST) {
+                listed = true;
+                token = sample_from_short_list(c, row, lo, hi, inv_t, zmax, k.key, p.top_k, p.top_p,
+                                               r, best_i);
+                token = cluster_share_found(c, token);
+                if (token < 0) token = best_i;
+            } else {
+                kept.floor_key = k.key;
+                kept.floor_ties = max(0, min(k.ties, p.top_k - k.above_count));
+                kept.floor_q = expf(key_value(k.key) - zmax);
+            }
         }
+        if (listed) {
+            // (done above)
+        } else {
         if (use_p) {
             const Crossing q = find_crossing(c, row, lo, hi, inv_t, zmax, kept, true, 0, p.top_p,
                                              true);
@@ -446,6 +546,7 @@ sample_rows_kernel(SampleArgs p) {
         rank = max(0, min(rank, d.ties - 1));
         token = nth_with_key(c, row, lo, hi, inv_t, d.key, rank);
         if (token < 0) token = best_i;
+        }
     }
     if (c.rank == 0 && threadIdx.x == 0) p.out[rowi] = token;
     c.g.sync();         // the first block's memory stays until every block has read it

@@ -810,7 +810,8 @@ def test_greedy_takes_the_first_maximum(vocab):
 
 
 @pytest.mark.parametrize("temperature,top_k,top_p", [
-    (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.9), (1.0, 40, 0.95), (2.0, 1, 1.0), (0.5, 3, 0.3)])
+    (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.9), (1.0, 40, 0.95), (2.0, 1, 1.0), (0.5, 3, 0.3),
+    (1.0, 400, 0.9), (1.5, 256, 1.0), (0.9, 257, 0.99)])
 def test_sampling_matches_the_plain_sampler_draw_by_draw(temperature, top_k, top_p):
     """Same generator, same draws: the kernel picks the token the plain sampler
     picks, except where a draw falls within rounding of a boundary."""
@@ -834,6 +835,59 @@ def test_sampling_matches_the_plain_sampler_draw_by_draw(temperature, top_k, top
             want = plain.sample_token(logits[r], temperature, top_k, top_p, rng)
             differ += want != got[d][r]
     assert differ <= 2, f"{differ} of {rows * draws} draws differ from the plain sampler"
+
+
+@pytest.mark.parametrize("n_top,top_k,top_p", [(100, 7, 1.0), (100, 7, 0.5), (300, 7, 0.9), (1000, 5, 0.9),
+                                                (3, 40, 0.95)])
+def test_sampling_with_ties_at_the_edge_of_top_k(n_top, top_k, top_p):
+    """Many equal logits at the k-th place: the lowest indices stay (few ties go through the
+    sorted list, more than it holds through the general search)."""
+    n = _native()
+    g = torch.Generator().manual_seed(9)
+    vocab, draws = 1000, 60
+    logits = torch.randn(2, vocab, generator=g)
+    where = torch.randperm(vocab, generator=g)[:n_top]
+    logits[0, where] = 4.0
+    logits[1, where] = 4.0
+    logits[1, int(where[0])] = 6.0       # one above the ties
+    seeds = [11, 12]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    dev = logits.to(DEV)
+    out = torch.empty(2, dtype=torch.int32, device=DEV)
+    got = []
+    for _ in range(draws):
+        n.sample_rows(dev, 0.9, top_k, top_p, state, out)
+        got.append(out.tolist())
+    differ = 0
+    for r in range(2):
+        rng = plain.XorShift64(seeds[r])
+        for d in range(draws):
+            differ += plain.sample_token(logits[r], 0.9, top_k, top_p, rng) != got[d][r]
+    assert differ <= 2, f"{differ} of {2 * draws} draws differ from the plain sampler"
+
+
+def test_sampling_at_the_vocabulary_of_the_real_model():
+    n = _native()
+    g = torch.Generator().manual_seed(10)
+    vocab, rows, draws = 256000, 3, 12
+    # (sharp enough that the sets the filters keep are hundreds of tokens, not a hundred thousand:
+    # the plain sampler adds the probabilities one by one in 32-bit, which drifts over so many)
+    logits = torch.randn(rows, vocab, generator=g) * 6.0
+    seeds = [5, 6, 7]
+    dev = logits.to(DEV)
+    for temperature, top_k, top_p in ((0.8, 40, 0.95), (1.0, 0, 0.9), (0.7, 300, 1.0)):
+        state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        got = []
+        for _ in range(draws):
+            n.sample_rows(dev, temperature, top_k, top_p, state, out)
+            got.append(out.tolist())
+        differ = 0
+        for r in range(rows):
+            rng = plain.XorShift64(seeds[r])
+            for d in range(draws):
+                differ += plain.sample_token(logits[r], temperature, top_k, top_p, rng) != got[d][r]
+        assert differ <= 2, f"{differ} of {rows * draws} draws differ ({temperature}, {top_k}, {top_p})"
 
 
 def test_sampling_uses_the_indexed_generator_and_advances_it():
