@@ -153,7 +153,8 @@ struct Crossing {
 // running mass reaches (inclusive) / exceeds (!inclusive) fraction x (mass of the set).
 __device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, float inv_t,
                                   float zmax, const Kept& kept, bool by_mass, int want_count,
-                                  float fraction, bool inclusive, bool with_mass = true) {
+                                  float fraction, bool inclusive, bool with_mass = true,
+                                  int few_enough = 0) {
     SampleShared* sh = c.sh;
     Crossing r;
     r.key = 0;
@@ -239,6 +240,12 @@ __device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, 
         r.above_count = cnt;
         r.above_mass = ms;
         r.key |= (uint32_t)pick << shift;
+        if (few_enough > 0 && cnt + pick_count <= few_enough) {
+            // the caller wants the candidates themselves, and they are few: every element at
+            // or above the bucket's lowest key (r.key with the lower bits clear) is one
+            r.ties = pick_count;
+            return r;
+        }
         if (level == 7) {
             r.ties = pick_count;
             r.q = pick_count > 0 ? pick_mass / (float)pick_count : 0.f;
@@ -512,8 +519,10 @@ sample_rows_kernel(SampleArgs p) {
         bool listed = false;
         if (use_k) {
             // (the search for the k-th largest counts only: no masses are summed)
+            // (and it stops as soon as the bucket it has come to, with everything above it,
+            // fits the list: the list is sorted anyway)
             const Crossing k = find_crossing(c, row, lo, hi, inv_t, zmax, kept, false, p.top_k, 0.f,
-                                             true, false);
+                                             true, false, SAMPLE_LIST);
             if (k.above_count + k.ties <= SAMPLE_LIST) {
                 listed = true;
                 token = sample_from_short_list(c, row, lo, hi, inv_t, zmax, k.key, p.top_k, p.top_p,
