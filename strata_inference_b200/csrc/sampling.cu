@@ -146,6 +146,8 @@ struct Crossing {
     int ties;          // kept elements with exactly this key
     float q;           // mass of one of them
     float total_mass;  // mass of the whole kept set (from the first pass)
+    bool few;          // the walk stopped early: `key` is the lowest key of a bucket that, with
+                       // everything above it, holds at most the asked-for number of elements
 };
 
 // Walk the radix tree of keys, 4 bits a level, towards the element where, in
@@ -163,6 +165,7 @@ __device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, 
     r.ties = 0;
     r.q = 0.f;
     r.total_mass = 0.f;
+    r.few = false;
     float want_mass = 0.f;
     for (int level = 0; level < 8; ++level) {
         const int shift = 28 - 4 * level;
@@ -244,6 +247,7 @@ __device__ Crossing find_crossing(Cluster& c, const float* row, int lo, int hi, 
             // the caller wants the candidates themselves, and they are few: every element at
             // or above the bucket's lowest key (r.key with the lower bits clear) is one
             r.ties = pick_count;
+            r.few = true;
             return r;
         }
         if (level == 7) {
@@ -320,7 +324,7 @@ __device__ int nth_with_key(Cluster& c, const float* row, int lo, int hi, float 
 // (-1 elsewhere); the caller shares it.
 __device__ int sample_from_short_list(Cluster& c, const float* row, int lo, int hi, float inv_t,
                                       float zmax, uint32_t floor_key, int top_k, float top_p,
-                                      float r, int fallback) {
+                                      float r, int fallback, float whole_mass = -1.f) {
     SampleShared* sh = c.sh;
     for (int i = lo + threadIdx.x; i < hi; i += SAMPLE_THREADS) {
         const float z = row[i] * inv_t;
@@ -355,6 +359,9 @@ __device__ int sample_from_short_list(Cluster& c, const float* row, int lo, int 
                 sh->list_z[j] = expf(sh->sorted_z[j] - zmax);      // (the list's own maximum is zmax)
                 total += sh->list_z[j];
             }
+            // (without top-k the list is the head of the whole vocabulary, whose mass the
+            // caller brings: the list reaches beyond the place where top_p is crossed)
+            if (whole_mass >= 0.f) total = whole_mass;
             int cut = kept;
             float mass = total;           // of the candidates that stay
             if (top_p < 1.0f) {
@@ -535,10 +542,30 @@ sample_rows_kernel(SampleArgs p) {
                 kept.floor_q = expf(key_value(k.key) - zmax);
             }
         }
+        if (!use_k && use_p) {
+            // the place where the mass reaches top_p, or, if the walk gets to a bucket that
+            // fits the list with everything above it first, the head of the vocabulary as a list
+            const Crossing q = find_crossing(c, row, lo, hi, inv_t, zmax, kept, true, 0, p.top_p,
+                                             true, true, SAMPLE_LIST);
+            if (q.few) {
+                listed = true;
+                token = sample_from_short_list(c, row, lo, hi, inv_t, zmax, q.key, SAMPLE_LIST,
+                                               p.top_p, r, best_i, q.total_mass);
+                token = cluster_share_found(c, token);
+                if (token < 0) token = best_i;
+            } else {
+                const float want = p.top_p * q.total_mass;
+                int need = q.ties;
+                if (q.q > 0.f) need = max(1, min(q.ties, (int)ceilf((want - q.above_mass) / q.q)));
+                kept.floor_key = q.key;
+                kept.floor_ties = need;
+                kept.floor_q = q.q;
+            }
+        }
         if (listed) {
             // (done above)
         } else {
-        if (use_p) {
+        if (use_k && use_p) {
             const Crossing q = find_crossing(c, row, lo, hi, inv_t, zmax, kept, true, 0, p.top_p,
                                              true);
             const float want = p.top_p * q.total_mass;

@@ -811,7 +811,7 @@ def test_greedy_takes_the_first_maximum(vocab):
 
 @pytest.mark.parametrize("temperature,top_k,top_p", [
     (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.9), (1.0, 40, 0.95), (2.0, 1, 1.0), (0.5, 3, 0.3),
-    (1.0, 400, 0.9), (1.5, 256, 1.0), (0.9, 257, 0.99)])
+    (1.0, 400, 0.9), (1.5, 256, 1.0), (0.9, 257, 0.99), (0.3, 0, 0.9), (0.4, 0, 0.999), (3.0, 0, 0.5)])
 def test_sampling_matches_the_plain_sampler_draw_by_draw(temperature, top_k, top_p):
     """Same generator, same draws: the kernel picks the token the plain sampler
     picks, except where a draw falls within rounding of a boundary."""
