@@ -252,3 +252,32 @@ def test_eight_prompts_of_128_to_4096_at_9b_sizes():
         assert err <= tol, f"8 sequences, step {k}: {err:.2e}"
     for s in slots:
         eng.end_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_at_real_sizes_one_step_ahead_of_the_host(model, dtype):
+    """Generation through the entry point at real layer sizes and vocabulary, with the
+    reference's default sampling options (temperature 0.8, top-k 40, top-p 0.95, the list
+    path of the sampling kernel) and greedy: the loop that keeps the device a step ahead
+    gives the tokens of the loop that waits for every step; in 32-bit the greedy tokens are
+    the plain implementation's."""
+    from strata_inference_b200 import GenerationConfig, GenerationEngine, SamplingConfig
+    d, reqs, refs = model
+    cfg = [c for c in CONFIGS.values() if c["vocab_size"] == refs[0].shape[1]][0]
+    gen = GenerationEngine.from_dir(d, dtype=dtype, max_tokens=2048)
+    prompts = [reqs[0][:150], reqs[1][:20], reqs[2][:90]]
+    for sampling in (SamplingConfig(temperature=0.8, top_k=40, top_p=0.95, seed=3), SamplingConfig()):
+        waited = gen.generate(prompts, GenerationConfig(max_tokens=10, sampling=sampling, look_ahead=False))
+        ahead = gen.generate(prompts, GenerationConfig(max_tokens=10, sampling=sampling, look_ahead=True))
+        assert [o.token_ids for o in waited] == [o.token_ids for o in ahead]
+        assert all(len(o.token_ids) == 10 or o.stop_reason == "eos" for o in ahead)
+    if dtype == "float32":
+        W = {k: v.float() for k, v in plain_weights(d).items()}
+        for p, o in zip(prompts[1:2], ahead[1:2]):       # the short request: 10 plain steps
+            seq = list(p)
+            for tok in o.token_ids:
+                logits = plain.forward(seq, W, cfg, dtype=torch.float32)[-1]
+                top = torch.topk(logits, 2).values
+                assert int(logits.argmax()) == tok or float(top[0] - top[1]) < 1e-4 * float(top[0].abs())
+                seq.append(tok)
+    assert gen.engine.cache.pages_in_use() == 0
