@@ -226,10 +226,13 @@ class Engine:
     def _prompt_step(self, seqs, tokens, want_rows, from_start: bool = True) -> torch.Tensor:
         from .graph import PromptGraph
         rows = -(-int(tokens.size) // 64) * 64 if from_start else int(tokens.size)
-        key = ("prompts" if from_start else "tokens", rows, len(seqs), len(want_rows))
+        # (steps whose prompts are all short are recorded apart: their attention is another kernel)
+        short = self.rt.short_prompt_tokens
+        longest = short if from_start and max(n for _, _, n in seqs) <= short < rows else None
+        key = ("prompts" if from_start else "tokens", rows, len(seqs), len(want_rows), longest)
         g = self._prompt_graphs.pop(key, None)
         if g is None:
-            g = PromptGraph(self, rows, len(seqs), len(want_rows), from_start)
+            g = PromptGraph(self, rows, len(seqs), len(want_rows), from_start, longest)
             while len(self._prompt_graphs) >= self.max_graphs:
                 self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
         self._prompt_graphs[key] = g       # most recently used last

@@ -157,10 +157,12 @@ class PromptGraph:
     wherever they stand (nothing to fill up), which returns logits where ``DecodeGraph``
     samples."""
 
-    def __init__(self, engine, rows: int, n_seqs: int, n_want: int, from_start: bool = True):
+    def __init__(self, engine, rows: int, n_seqs: int, n_want: int, from_start: bool = True,
+                 longest: Optional[int] = None):
         self.engine = engine
         self.rows, self.B, self.n_want = rows, n_seqs, n_want
         self.from_start = from_start
+        self.longest = longest      # no prompt of a replay is longer (None: no bound but the rows)
         size = StepContext.packed_size(rows, n_seqs + (1 if from_start else 0), n_want)
         self.hosts = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(_STAGES)]
         self.copied = [None] * _STAGES
@@ -173,7 +175,7 @@ class PromptGraph:
     def _forward(self, seqs):
         eng = self.engine
         ctx = StepContext(self.meta, seqs, self.n_want, eng.cache, eng.rt, graph_capture=True,
-                          from_start=self.from_start)
+                          from_start=self.from_start, longest=self.longest)
         return eng.model.logits(eng.model.hidden_states(ctx), ctx.want_rows)
 
     def run(self, seqs, tokens: np.ndarray, want_rows: Sequence[int]) -> torch.Tensor:
@@ -185,6 +187,9 @@ class PromptGraph:
         if len(seqs) != self.B or len(want_rows) != self.n_want or used > self.rows:
             raise ValueError(f"this graph steps {self.B} sequences of {self.rows} rows in all")
         if self.from_start:
+            if self.longest is not None and any(n > self.longest for _, _, n in seqs):
+                raise ValueError(f"this graph steps prompts of at most {self.longest} tokens")
+            # (the rows that are left over, as sequences without a slot, none longer than the bound)
             padded = list(seqs) + [(-1, 0, self.rows - used)]
             tokens = np.concatenate([tokens, np.zeros(self.rows - used, dtype=np.int64)])
         else:

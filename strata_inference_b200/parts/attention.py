@@ -192,8 +192,14 @@ class Attention:
 
         out = torch.empty((R, nh * hd), dtype=qkv.dtype, device=qkv.device)
         width = qkv.shape[1]
+        # (prompts of up to 128 tokens: the mma.sync kernel, whose blocks of 64 rows start in a
+        # fraction of the time that a tcgen05 block needs before its first tile; measured on 2 048
+        # rows of the Gemma2-2B shape: 64 prompts of 32 tokens 22 against 65 us a call, 16 of 128
+        # 28 against 39 us, 8 of 256 36 against 56 us the other way round)
+        short = ctx.max_count <= rt.short_prompt_tokens and native.attention_prefill_supports(
+            nh, self.nkv, hd)
         if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
-                native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
+                not short and native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
             # a launch too small for the device splits its long blocks, given the memory
             # (with the lengths known on the host, not in a recorded step, the launch is a
             # balanced list of work items)

@@ -82,6 +82,8 @@ class Runtime:
         # library product followed by the rotation kernel up to 16 rows (and behind from 17).
         self.fused_rope_max_rows = 16
         self.chain_max_rows = 16     # what the (optional) chain kernel of few-row steps takes
+        # prompts of up to this many tokens are attended to by the mma.sync prompt kernel
+        self.short_prompt_tokens = 128
         # Up to 128 rows against a matrix of so many rows that its 128-row tiles are several
         # waves of blocks go to the tcgen05 weight-streaming product (csrc/linear_rows_tc.cu):
         # there it reads at 0.91 of the copy bandwidth; with fewer tiles the library is as fast.
@@ -340,7 +342,8 @@ class StepContext:
     same number of sequences and at most as many rows in all: its last sequence holds no
     slot (``seq_slot`` -1) and takes the rows that are left over, nothing of it is stored,
     and ``counts`` is not readable either; ``max_count`` is the number of rows, the most
-    that one sequence of a replay can have.
+    that one sequence of a replay can have, or the smaller bound ``longest`` that the caller
+    keeps for every replay.
     """
 
     @staticmethod
@@ -383,7 +386,7 @@ class StepContext:
 
     def __init__(self, meta: torch.Tensor, seqs: Sequence[Tuple[int, int, int]], n_want: int,
                  cache: SequenceCache, runtime: Runtime, graph_capture: bool = False,
-                 from_start: bool = False):
+                 from_start: bool = False, longest: Optional[int] = None):
         """``graph_capture`` with ``from_start``: a captured step of prompts that all start at
         position 0 (replays bring other prompts of at most this step's rows in all, filled up
         with the rows of a sequence that holds no slot: slot -1, nothing of it is stored)."""
@@ -408,7 +411,8 @@ class StepContext:
         self.want_rows = take(n_want)
         # (the most rows of one sequence sizes launches: a captured step of prompts may be
         # replayed with one sequence that takes nearly all rows)
-        self.max_count = R if (graph_capture and from_start) else max(self._counts)
+        # (``longest``: a bound that the caller promises for every replay)
+        self.max_count = (longest or R) if (graph_capture and from_start) else max(self._counts)
         self.graph_capture = graph_capture
         self._counts_vary = graph_capture and from_start
         self.all_from_start = from_start if graph_capture else all(st == 0 for _, st, _ in seqs)

@@ -673,3 +673,29 @@ def test_tokens_are_fed_on_the_device_only_right_after_the_step_that_sampled_the
         eng.decode_step(slots, None)
     for s in slots:
         eng.end_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_many_short_prompts_in_one_step(model_dirs, dtype):
+    """A step of many short prompts (recorded apart from steps with a long prompt: their
+    attention runs on the kernel with the cheaper start), then a step with one long prompt
+    among short ones, against the plain implementation."""
+    name, cfg = "A", CONFIGS["A"]
+    eng = _engine(model_dirs, name, dtype, 4, max_tokens=4096)
+    eng.rt.short_prompt_tokens = 24          # (the tiny model's prompts are short anyway)
+    for rnd, lens in enumerate(([5, 17, 9, 24, 3, 12, 20, 8], [7, 11, 24, 2, 19, 6, 23, 10],
+                                [5, 17, 60, 24, 3, 12, 20, 8], [9, 9, 9, 9, 9, 9, 9, 30])):
+        reqs = random_prompts(cfg, [n + 1 for n in lens], seed=90 + rnd)
+        refs = [plain_logits(t, model_dirs[name, dtype], cfg) for t in reqs]
+        slots = [eng.new_sequence() for _ in reqs]
+        got = eng.step([(s, t[:n]) for s, t, n in zip(slots, reqs, lens)])
+        assert_logits_close(got, torch.stack([r[n - 1] for r, n in zip(refs, lens)]), dtype,
+                            f"step {rnd}: prompts of {lens}")
+        got = eng.step([(s, [t[n]]) for s, t, n in zip(slots, reqs, lens)])
+        assert_logits_close(got, torch.stack([r[n] for r, n in zip(refs, lens)]), dtype,
+                            f"step {rnd}: the token after the prompts")
+        for s in slots:
+            eng.end_sequence(s)
+    bounds = {k[4] for k in eng._prompt_graphs if k[0] == "prompts"}
+    assert bounds == {None, 24}                      # one recording with the bound, one without
+    assert eng.cache.pages_in_use() == 0
