@@ -194,7 +194,7 @@ def time_decode(engine, batch, context, steps, warmup, blocks=BLOCKS):
     engine.kernel_watch.check()            # a kernel that gave up would make the number void
     per_step = sorted(marks[b].elapsed_time(marks[b + 1]) / steps for b in range(blocks))
     lengths = [engine.length(s) for s in slots]
-    graph = engine._graphs[(batch, 0.0, 0, 1.0)]
+    graph = engine.recorded_step(batch)
     launches = graph.launches_per_step
     for s in slots:
         engine.end_sequence(s)

@@ -73,7 +73,8 @@ class Engine:
         self._prompt_graphs: Dict[Tuple, "PromptGraph"] = {}
         # captured steps kept: single-token steps by batch size and sampling options, and
         # as many steps of prompts by rows, sequences and wanted rows
-        self.max_graphs = 8
+        self.max_graphs = 16
+        self.first_span = 512       # the shortest length class of recorded single-token steps
         self.prompt_graph_rows = 1024   # steps of prompts of up to this many rows are recorded
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
         self._latest_step = None    # key of the recorded single-token step that ran last, if one did
@@ -229,10 +230,11 @@ class Engine:
         # (steps whose prompts are all short are recorded apart: their attention is another kernel)
         short = self.rt.short_prompt_tokens
         longest = short if from_start and max(n for _, _, n in seqs) <= short < rows else None
-        key = ("prompts" if from_start else "tokens", rows, len(seqs), len(want_rows), longest)
+        span = None if from_start else self._span([s for s, _, _ in seqs])
+        key = ("prompts" if from_start else "tokens", rows, len(seqs), len(want_rows), longest, span)
         g = self._prompt_graphs.pop(key, None)
         if g is None:
-            g = PromptGraph(self, rows, len(seqs), len(want_rows), from_start, longest)
+            g = PromptGraph(self, rows, len(seqs), len(want_rows), from_start, longest, span)
             while len(self._prompt_graphs) >= self.max_graphs:
                 self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
         self._prompt_graphs[key] = g       # most recently used last
@@ -268,7 +270,7 @@ class Engine:
         same slots, taken on the device (``can_feed_back`` says whether that is possible);
         the host may read them afterwards."""
         from .graph import DecodeGraph
-        key = (len(slots), float(temperature), int(top_k), float(top_p))
+        key = (len(slots), float(temperature), int(top_k), float(top_p), self._span(slots))
         g = self._graphs.pop(key, None)
         if g is None:
             g = DecodeGraph(self, *key)
@@ -289,9 +291,30 @@ class Engine:
     def can_feed_back(self, slots: Sequence[int], temperature: float = 0.0, top_k: int = 0,
                       top_p: float = 1.0) -> bool:
         """Whether ``decode_step(slots, None, ...)`` is possible now."""
-        key = (len(slots), float(temperature), int(top_k), float(top_p))
+        key = (len(slots), float(temperature), int(top_k), float(top_p), self._span(slots))
         g = self._graphs.get(key)
         return g is not None and self._latest_step == key and g.can_feed_back(slots)
+
+    def recorded_step(self, n_seqs: int, temperature: float = 0.0, top_k: int = 0,
+                      top_p: float = 1.0):
+        """The most recently used recorded single-token step for this many sequences and these
+        sampling options (of whatever length class), or None."""
+        want = (n_seqs, float(temperature), int(top_k), float(top_p))
+        for key in reversed(list(self._graphs)):
+            if key[:4] == want:
+                return self._graphs[key]
+        return None
+
+    def _span(self, slots: Sequence[int]) -> int:
+        """The length class of a single-token step: the next power of two (from 512 on) that
+        holds the longest of its sequences after the step.  A recorded step divides the
+        attention's work for that length; sequences that outgrow it move on to the next
+        class's recording."""
+        longest = max(self.cache.length(int(s)) for s in slots) + 1
+        span = self.first_span
+        while span < longest:
+            span *= 2
+        return min(span, self.max_seq_len)
 
     def read_later(self, t: torch.Tensor):
         """Start bringing the integer tensor ``t`` (at most one value per slot) to the host:

@@ -32,9 +32,11 @@ _STAGES = 4      # steps a caller may be ahead of the device
 
 
 class DecodeGraph:
-    def __init__(self, engine, n_seqs: int, temperature: float, top_k: int, top_p: float):
+    def __init__(self, engine, n_seqs: int, temperature: float, top_k: int, top_p: float,
+                 span: Optional[int] = None):
         self.engine = engine
         self.B = B = n_seqs
+        self.span = span      # the attention's work is divided for sequences of up to this length
         self.temperature, self.top_k, self.top_p = temperature, top_k, top_p
         # Pinned staging buffers for the step's integers, used in turn: a caller may issue
         # steps without waiting for them, and a buffer must not be rewritten before its
@@ -55,7 +57,8 @@ class DecodeGraph:
 
     def _forward(self, seqs, capture: bool):
         eng, B = self.engine, self.B
-        ctx = StepContext(self.meta, seqs, B, eng.cache, eng.rt, graph_capture=capture)
+        ctx = StepContext(self.meta, seqs, B, eng.cache, eng.rt, graph_capture=capture,
+                          span=self.span)
         h = eng.model.hidden_states(ctx)
         logits = eng.model.logits(h, ctx.want_rows)
         out = torch.empty(B, dtype=torch.int32, device=eng.device)
@@ -158,9 +161,10 @@ class PromptGraph:
     samples."""
 
     def __init__(self, engine, rows: int, n_seqs: int, n_want: int, from_start: bool = True,
-                 longest: Optional[int] = None):
+                 longest: Optional[int] = None, span: Optional[int] = None):
         self.engine = engine
         self.rows, self.B, self.n_want = rows, n_seqs, n_want
+        self.span = span
         self.from_start = from_start
         self.longest = longest      # no prompt of a replay is longer (None: no bound but the rows)
         size = StepContext.packed_size(rows, n_seqs + (1 if from_start else 0), n_want)
@@ -175,7 +179,7 @@ class PromptGraph:
     def _forward(self, seqs):
         eng = self.engine
         ctx = StepContext(self.meta, seqs, self.n_want, eng.cache, eng.rt, graph_capture=True,
-                          from_start=self.from_start, longest=self.longest)
+                          from_start=self.from_start, longest=self.longest, span=self.span)
         return eng.model.logits(eng.model.hidden_states(ctx), ctx.want_rows)
 
     def run(self, seqs, tokens: np.ndarray, want_rows: Sequence[int]) -> torch.Tensor:

@@ -116,7 +116,7 @@ class Attention:
 
     # ------------------------------------------------------------------
     def _longest(self, ctx, capacity: int) -> int:
-        longest = capacity if ctx.graph_capture else ctx.max_end
+        longest = (min(ctx.span or capacity, capacity)) if ctx.graph_capture else ctx.max_end
         return min(longest, self.window) if self.window > 0 else longest
 
     def _splits(self, ctx, capacity: int) -> int:

@@ -386,7 +386,8 @@ class StepContext:
 
     def __init__(self, meta: torch.Tensor, seqs: Sequence[Tuple[int, int, int]], n_want: int,
                  cache: SequenceCache, runtime: Runtime, graph_capture: bool = False,
-                 from_start: bool = False, longest: Optional[int] = None):
+                 from_start: bool = False, longest: Optional[int] = None,
+                 span: Optional[int] = None):
         """``graph_capture`` with ``from_start``: a captured step of prompts that all start at
         position 0 (replays bring other prompts of at most this step's rows in all, filled up
         with the rows of a sequence that holds no slot: slot -1, nothing of it is stored)."""
@@ -411,6 +412,9 @@ class StepContext:
         self.want_rows = take(n_want)
         # (the most rows of one sequence sizes launches: a captured step of prompts may be
         # replayed with one sequence that takes nearly all rows)
+        # ``span``: how long the sequences of a recorded step's replays get at most, if the
+        # caller says (work is divided for that length; any length stays correct)
+        self.span = span if graph_capture else None
         # (``longest``: a bound that the caller promises for every replay)
         self.max_count = (longest or R) if (graph_capture and from_start) else max(self._counts)
         self.graph_capture = graph_capture

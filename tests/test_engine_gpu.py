@@ -699,3 +699,25 @@ def test_many_short_prompts_in_one_step(model_dirs, dtype):
     bounds = {k[4] for k in eng._prompt_graphs if k[0] == "prompts"}
     assert bounds == {None, 24}                      # one recording with the bound, one without
     assert eng.cache.pages_in_use() == 0
+
+
+def test_single_token_steps_are_recorded_by_length_class(model_dirs):
+    """A recorded single-token step divides the attention's work for a class of lengths
+    (powers of two from ``first_span``, 512 unless set): sequences that outgrow their class go
+    on in the next class's recording, with the plain implementation's logits all along."""
+    name, cfg = "C", CONFIGS["C"]
+    eng = _engine(model_dirs, name, "float32", 16, max_tokens=1024)
+    eng.first_span = 32
+    toks = random_prompts(cfg, [150], seed=33)[0]
+    ref = plain_logits(toks, model_dirs[name, "float32"], cfg)
+    slot = eng.new_sequence()
+    eng.step([(slot, toks[:50])])
+    choices = []
+    for i in range(50, 150):            # crosses 64 and 128 positions
+        out = eng.decode_step([slot], [toks[i]])
+        choices.append(int(eng.read_back(out)[0]))
+        assert_logits_close(eng.last_logits, ref[i:i + 1], "float32", f"position {i}")
+    assert choices == [int(ref[i].argmax()) for i in range(50, 150)]
+    assert sorted(k[4] for k in eng._graphs) == [64, 128, 256]
+    assert all(g.graph is not None for g in eng._graphs.values())
+    eng.end_sequence(slot)

@@ -633,7 +633,7 @@ def test_toy_mixer_with_state_in_captured_steps_with_changing_slots(tmp_path):
         _close(eng.last_logits, ref, torch.float32, f"captured toy step {k}")
         for i in live:
             pos[i] += 1
-    assert eng._graphs[(3, 0.0, 0, 1.0)].graph is not None    # the steps were replays
+    assert eng.recorded_step(3).graph is not None    # the steps were replays
 
 
 # ---------------------------------------------------------------- a toy embedding with positions
