@@ -275,6 +275,7 @@ struct TcArgs {
     __nv_bfloat16* out;      // [rows, n_heads * head_dim]
     const int* seq_row0;
     const int* seq_len;
+    const int* seq_q0;       // per sequence: rows before this position are keys only (null: none)
     int* error_flag;
     float* part;             // partial results of split blocks (see SPLIT below), or null
     int* tickets;            // 8 per block of query rows, zero between launches
@@ -367,8 +368,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
         unit = ((size_t)b * p.n_kv + kvh) * gridDim.x + blockIdx.x;
     }
     const int n = p.seq_len[b];
+    const int q0 = p.seq_q0 ? p.seq_q0[b] : 0;
     const int p0 = first0 + rank * MP;
-    if (first0 >= n) return;                               // (both blocks of a pair)
+    if (first0 >= n || first0 + NB * MP <= q0) return;     // (both blocks of a pair)
     const int row0 = p.seq_row0[b];
     const int k_hi = min(n, first0 + NB * MP);
     const int k_lo = p.window > 0 ? max(0, first0 - p.window + 1) : 0;
@@ -682,7 +684,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
         }
         if (ok) {
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
-            const bool store = pos < n;
+            const bool store = pos < n && pos >= q0;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD +
                                  (HD / 2) * half;
 #pragma unroll 1
@@ -860,13 +862,13 @@ float plan_for(const std::vector<PlanBlock>& blocks, int n_kv, int split_from, i
     return longest;
 }
 
-bool plan_items_now(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int window, int sms,
-                    TcItems* out, int* n_units);
+bool plan_items_now(const int* lens, const int* q0s, int n_seqs, int n_kv, int G, int head_dim,
+                    int window, int sms, TcItems* out, int* n_units);
 
 // Fills `out` for prompts of `lens` (host memory); false if a list does not fit or pay.
 // (Every layer of a step asks for the same few plans: the last ones are kept.)
-bool plan_items(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int window, int sms,
-                TcItems* out, int* n_units) {
+bool plan_items(const int* lens, const int* q0s, int n_seqs, int n_kv, int G, int head_dim,
+                int window, int sms, TcItems* out, int* n_units) {
     struct Kept {
         std::vector<int> key;
         TcItems items;
@@ -877,6 +879,7 @@ bool plan_items(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int 
     static thread_local int next = 0;
     if (!lens || n_seqs <= 0) return false;
     std::vector<int> key(lens, lens + n_seqs);
+    for (int b = 0; b < n_seqs; ++b) key.push_back(q0s ? q0s[b] : 0);
     const int tail[6] = {n_kv, G, head_dim, window, sms, tc_pairs_allowed() ? 1 : 0};
     key.insert(key.end(), tail, tail + 6);
     for (Kept& k : kept)
@@ -891,7 +894,7 @@ bool plan_items(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int 
     next = (next + 1) % 4;
     k.key = key;
     k.units = 0;
-    k.ok = plan_items_now(lens, n_seqs, n_kv, G, head_dim, window, sms, &k.items, &k.units);
+    k.ok = plan_items_now(lens, q0s, n_seqs, n_kv, G, head_dim, window, sms, &k.items, &k.units);
     if (k.ok) {
         *out = k.items;
         if (n_units) *n_units = k.units;
@@ -899,8 +902,8 @@ bool plan_items(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int 
     return k.ok;
 }
 
-bool plan_items_now(const int* lens, int n_seqs, int n_kv, int G, int head_dim, int window, int sms,
-                    TcItems* out, int* n_units) {
+bool plan_items_now(const int* lens, const int* q0s, int n_seqs, int n_kv, int G, int head_dim,
+                    int window, int sms, TcItems* out, int* n_units) {
     static const bool allowed = [] {
         const char* v = getenv("SIB_PREFILL_BALANCE");
         return !(v && v[0] == '0');
@@ -913,7 +916,8 @@ bool plan_items_now(const int* lens, int n_seqs, int n_kv, int G, int head_dim, 
     for (int b = 0; b < n_seqs; ++b) {
         const int n = lens[b];
         if (n < 0) return false;
-        for (int q = 0; q * span < n; ++q) {
+        // (blocks of rows that are keys only have no work)
+        for (int q = (q0s ? std::max(0, q0s[b]) : 0) / span; q * span < n; ++q) {
             if (q >= 4096 || (long long)(blocks.size() + 1) * n_kv > MAX_ITEMS) return false;
             const int first0 = q * span, k_hi = std::min(n, first0 + span);
             const int k_lo = window > 0 ? std::max(0, first0 - window + 1) : 0;
@@ -960,16 +964,16 @@ int device_sms() {
 // What a launch for prompts of these lengths (host memory) needs to run as a balanced list
 // of work items: bytes of scratch memory and ticket counters (int, zero between launches)
 // for the blocks it splits.  Returns the number of items, 0 if such a launch is a grid.
-SIB_EXPORT int sib_attention_prefill_tc_plan(const int* host_lens, int n_seqs, int n_heads, int n_kv,
-                                             int head_dim, int window, long long* scratch_bytes,
-                                             int* n_tickets) {
+SIB_EXPORT int sib_attention_prefill_tc_plan(const int* host_lens, const int* host_q0, int n_seqs,
+                                             int n_heads, int n_kv, int head_dim, int window,
+                                             long long* scratch_bytes, int* n_tickets) {
     if (scratch_bytes) *scratch_bytes = 0;
     if (n_tickets) *n_tickets = 0;
     if (n_kv <= 0 || n_heads % n_kv) return 0;
     TcItems items;
     int units = 0;
-    if (!plan_items(host_lens, n_seqs, n_kv, n_heads / n_kv, head_dim, window, device_sms(), &items,
-                    &units))
+    if (!plan_items(host_lens, host_q0, n_seqs, n_kv, n_heads / n_kv, head_dim, window, device_sms(),
+                    &items, &units))
         return 0;
     const int nb = (head_dim >= 128 && tc_pairs_allowed()) ? 2 : 1;
     if (scratch_bytes)
@@ -979,7 +983,10 @@ SIB_EXPORT int sib_attention_prefill_tc_plan(const int* host_lens, int n_seqs, i
 }
 
 // Attention of `n_seqs` packed prompts that all start at position 0; `total_rows`
-// is the number of rows of the packed buffer.
+// is the number of rows of the packed buffer.  `seq_q0` (device; `host_q0` the same on the
+// host, for the planner; both null: none): the rows of a sequence before this position
+// bring keys and values only, their output rows are not written (a step that continues
+// sequences puts what they hold there, see sib_gather_kv_rows).
 // Whether a launch of this shape would split its long blocks of query rows (see SPLIT at the
 // top): it does when its blocks would fill at most half of the device.  Returns
 // the number of key tiles from which a block is split (0: no split) and what the launch then
@@ -1017,7 +1024,8 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
                                         int max_len, int n_heads, int n_kv, int head_dim,
                                         float scale, float softcap, int window, void* scratch,
                                         long long scratch_bytes, int* tickets, int n_tickets,
-                                        const int* host_lens, void* stream) {
+                                        const int* host_lens, const int* seq_q0, const int* host_q0,
+                                        void* stream) {
     if (n_seqs == 0 || max_len == 0) return 0;
     SIB_REQUIRE(sib_attention_prefill_tc_supports(n_heads, n_kv, head_dim, width),
                 "attention_prefill_tc: heads=%d kv_heads=%d head_dim=%d is not a shape this kernel "
@@ -1062,7 +1070,8 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
     items.n = 0;
     if (host_lens) {
         int units = 0;
-        if (plan_items(host_lens, n_seqs, n_kv, G, head_dim, window, device_sms(), &items, &units)) {
+        if (plan_items(host_lens, host_q0, n_seqs, n_kv, G, head_dim, window, device_sms(), &items,
+                       &units)) {
             const int nb = (head_dim >= 128 && tc_pairs_allowed()) ? 2 : 1;
             const long long bytes = (long long)units * nb * 2 * (long long)BM * (head_dim + 2) * sizeof(float);
             if (units > 0 && (scratch == nullptr || tickets == nullptr || scratch_bytes < bytes ||
@@ -1073,7 +1082,7 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
         }
     }
     if (items.n > 0) split_tiles = 0;
-    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, error_flag, (float*)scratch, tickets,
+    TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, seq_q0, error_flag, (float*)scratch, tickets,
              split_tiles, n_heads, n_kv, window, scale, softcap};
     cudaStream_t s = (cudaStream_t)stream;
 #define BY_G(HD, PAIR)                                                         \

@@ -217,3 +217,73 @@ SIB_EXPORT int sib_rope_store(void* qkv, int dtype, const int* row_pos, const in
                                                  (cudaStream_t)stream, p));
     return sib_check_launch("rope_store");
 }
+
+// ---------------------------------------------------------------------------
+// The way back: keys and values of positions that a sequence already holds, copied from
+// the pages into rows of a packed q|k|v buffer (row = position), so that a step that
+// continues sequences with many tokens can run the prompt attention over "what was there
+// + what came" (parts/attention.py).  Of sequence b the positions [from[b], upto[b]) go
+// to rows row0[b] + position; the q columns of those rows are set to zero.
+// ---------------------------------------------------------------------------
+struct GatherArgs {
+    __nv_bfloat16* packed;     // [rows, (n_heads + 2 n_kv) * head_dim]
+    const __nv_bfloat16* k_pool;
+    const __nv_bfloat16* v_pool;
+    const int* page_table;     // [slots, max_pages]
+    const int* seq_slot;       // [seqs]
+    const int* seq_from;       // [seqs] first position to copy
+    const int* seq_upto;       // [seqs] one past the last
+    const int* seq_row0;       // [seqs] packed row of the sequence's position 0
+    int n_heads, n_kv, head_dim;
+    int max_pages, page_tokens, ring_tokens;
+};
+
+__global__ void __launch_bounds__(128) gather_kv_rows_kernel(GatherArgs p) {
+    pdl_trigger();
+    const int b = blockIdx.y;
+    const int pos = p.seq_from[b] + blockIdx.x;
+    pdl_wait();
+    if (pos >= p.seq_upto[b]) return;
+    const int hd = p.head_dim;
+    const int width = (p.n_heads + 2 * p.n_kv) * hd;
+    const int cell = p.ring_tokens > 0 ? pos % p.ring_tokens : pos;
+    const int page = p.page_table[(size_t)p.seq_slot[b] * p.max_pages + cell / p.page_tokens];
+    __nv_bfloat16* row = p.packed + (size_t)(p.seq_row0[b] + pos) * width;
+    const int per_head = hd / 8;                 // 16-byte pieces of a head
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int u = threadIdx.x; u < p.n_heads * per_head; u += blockDim.x)
+        reinterpret_cast<uint4*>(row)[u] = zero;
+    for (int u = threadIdx.x; u < 2 * p.n_kv * per_head; u += blockDim.x) {
+        const int which = u / (p.n_kv * per_head);          // 0: keys, 1: values
+        const int kvh = (u / per_head) % p.n_kv, piece = u % per_head;
+        const __nv_bfloat16* pool = which ? p.v_pool : p.k_pool;
+        const __nv_bfloat16* src = pool + (((size_t)page * p.n_kv + kvh) * p.page_tokens +
+                                           cell % p.page_tokens) * hd + 8 * piece;
+        __nv_bfloat16* dst = row + (size_t)(p.n_heads + which * p.n_kv + kvh) * hd + 8 * piece;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    }
+}
+
+// `most`: the most positions any sequence has to copy (the grid's width).
+SIB_EXPORT int sib_gather_kv_rows(void* packed, const void* k_pool, const void* v_pool,
+                                  const int* page_table, const int* seq_slot, const int* seq_from,
+                                  const int* seq_upto, const int* seq_row0, int n_seqs, int most,
+                                  int n_heads, int n_kv, int head_dim, int max_pages,
+                                  int page_tokens, int ring_tokens, void* stream) {
+    if (n_seqs == 0 || most <= 0) return 0;
+    SIB_REQUIRE(n_seqs > 0 && n_seqs < 65536 && n_heads > 0 && n_kv > 0 && head_dim > 0 &&
+                    head_dim % 8 == 0,
+                "gather_kv_rows: seqs=%d heads=%d kv=%d head_dim=%d (a multiple of 8)", n_seqs, n_heads,
+                n_kv, head_dim);
+    SIB_REQUIRE(packed && k_pool && v_pool && page_table && seq_slot && seq_from && seq_upto && seq_row0 &&
+                    page_tokens > 0 && max_pages > 0 && ring_tokens >= 0,
+                "gather_kv_rows: incomplete description");
+    SIB_REQUIRE(((uintptr_t)packed % 16) == 0 && ((uintptr_t)k_pool % 16) == 0 &&
+                    ((uintptr_t)v_pool % 16) == 0,
+                "gather_kv_rows: buffers must be 16-byte aligned");
+    GatherArgs p{(__nv_bfloat16*)packed, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                 page_table, seq_slot, seq_from, seq_upto, seq_row0, n_heads, n_kv, head_dim,
+                 max_pages, page_tokens, ring_tokens};
+    sib_launch_chained(gather_kv_rows_kernel, dim3(most, n_seqs), dim3(128), 0, (cudaStream_t)stream, p);
+    return sib_check_launch("gather_kv_rows");
+}

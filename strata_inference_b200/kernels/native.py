@@ -524,33 +524,40 @@ def attention_prefill_tc_split(n_seqs: int, max_len: int, n_heads: int, n_kv: in
 
 
 def attention_prefill_tc_plan(lens: Sequence[int], n_heads: int, n_kv: int, head_dim: int,
-                              window: int):
+                              window: int, first_query: Optional[Sequence[int]] = None):
     """(work items, bytes of scratch memory, ticket counters) of a launch for prompts of these
-    lengths that runs as a balanced list of work items; (0, 0, 0) if it would run as a grid."""
+    lengths that runs as a balanced list of work items; (0, 0, 0) if it would run as a grid.
+    ``first_query``: per sequence, the position from which rows are queries."""
     from ctypes import byref
     nbytes, n_tickets = c_longlong(0), c_int(0)
     arr = (c_int * len(lens))(*[int(n) for n in lens])
-    n_items = library().sib_attention_prefill_tc_plan(arr, c_int(len(lens)), c_int(n_heads),
+    q0 = None if first_query is None else (c_int * len(lens))(*[int(n) for n in first_query])
+    n_items = library().sib_attention_prefill_tc_plan(arr, q0, c_int(len(lens)), c_int(n_heads),
                                                       c_int(n_kv), c_int(head_dim), c_int(window),
                                                       byref(nbytes), byref(n_tickets))
     return int(n_items), int(nbytes.value), int(n_tickets.value)
 
 
 @_timed(lambda qkv, out, seq_row0, seq_len, n_seqs, max_len, n_heads, n_kv, head_dim, scale,
-        softcap, window, scratch=None, tickets=None, host_lens=None: _prompt_work(
+        softcap, window, scratch=None, tickets=None, host_lens=None, seq_q0=None,
+        host_q0=None: _prompt_work(
             "attention_prefill_tc (tcgen05)", qkv, seq_len, n_heads, head_dim, window))
 def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                          max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
                          softcap: float, window: int, scratch: Optional[torch.Tensor] = None,
                          tickets: Optional[torch.Tensor] = None,
-                         host_lens: Optional[Sequence[int]] = None) -> torch.Tensor:
+                         host_lens: Optional[Sequence[int]] = None,
+                         seq_q0: Optional[torch.Tensor] = None,
+                         host_q0: Optional[Sequence[int]] = None) -> torch.Tensor:
     """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu).  With ``scratch``
     and ``tickets`` (int32, zero before the first call; every call leaves them zero) of the
     sizes ``attention_prefill_tc_split`` gives, a launch that cannot fill the device runs its
     long blocks of query rows as two halves.  With ``host_lens`` (the prompts' lengths, as
     ``seq_len`` holds them on the device) and memory of the sizes ``attention_prefill_tc_plan``
     gives, the launch is a list of work items ordered by their work, with the blocks split
-    that make the busiest SM's share smallest."""
+    that make the busiest SM's share smallest.  ``seq_q0`` (int32 on the device, ``host_q0``
+    the same on the host): per sequence the position from which rows are queries; the rows
+    before it bring keys and values only and their output rows are not written."""
     _want(qkv, torch.bfloat16, "qkv")
     _want(out, torch.bfloat16, "out")
     if out.shape[0] != qkv.shape[0] or out.shape[1] != n_heads * head_dim:
@@ -564,8 +571,34 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
         c_longlong(scratch.numel() * scratch.element_size() if scratch is not None else 0),
         _ptr(tickets), c_int(tickets.numel() if tickets is not None else 0),
         None if host_lens is None else (c_int * len(host_lens))(*[int(n) for n in host_lens]),
+        _ptr(seq_q0),
+        None if host_q0 is None else (c_int * len(host_q0))(*[int(n) for n in host_q0]),
         _stream()))
     return out
+
+
+@_timed(lambda packed, k_pool, *a, **kw: ("gather_kv_rows", 0, 0))
+def gather_kv_rows(packed: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   page_table: torch.Tensor, seq_slot: torch.Tensor, seq_from: torch.Tensor,
+                   seq_upto: torch.Tensor, seq_row0: torch.Tensor, most: int, page_tokens: int,
+                   ring_tokens: int, n_heads: int, n_kv: int, head_dim: int) -> torch.Tensor:
+    """Keys and values of the positions [seq_from[b], seq_upto[b]) that sequence b holds in
+    the paged cache, into rows seq_row0[b] + position of the packed q|k|v buffer (q columns
+    of those rows: zero).  ``most``: the most positions of any sequence."""
+    _want(packed, torch.bfloat16, "packed")
+    _want(k_pool, torch.bfloat16, "k_pool")
+    _want(v_pool, torch.bfloat16, "v_pool")
+    for t, name in ((page_table, "page_table"), (seq_slot, "seq_slot"), (seq_from, "seq_from"),
+                    (seq_upto, "seq_upto"), (seq_row0, "seq_row0")):
+        _want(t, torch.int32, name)
+    if packed.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("gather_kv_rows: the packed rows do not fit the head counts")
+    _check(library().sib_gather_kv_rows(
+        _ptr(packed), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(seq_slot), _ptr(seq_from),
+        _ptr(seq_upto), _ptr(seq_row0), c_int(seq_slot.numel()), c_int(most), c_int(n_heads),
+        c_int(n_kv), c_int(head_dim), c_int(page_table.shape[1]), c_int(page_tokens),
+        c_int(ring_tokens), _stream()))
+    return packed
 
 
 def attention_prefill_tc_error(clear: bool = True) -> int:

@@ -84,6 +84,9 @@ class Runtime:
         self.chain_max_rows = 16     # what the (optional) chain kernel of few-row steps takes
         # prompts of up to this many tokens are attended to by the mma.sync prompt kernel
         self.short_prompt_tokens = 128
+        # a step that continues a sequence with at least this many tokens attends through the
+        # prompt kernel over a packed copy of what the sequence holds (parts/attention.py)
+        self.piece_attention_rows = 32
         # Up to 128 rows against a matrix of so many rows that its 128-row tiles are several
         # waves of blocks go to the tcgen05 weight-streaming product (csrc/linear_rows_tc.cu):
         # there it reads at 0.91 of the copy bandwidth; with fewer tiles the library is as fast.
@@ -425,6 +428,7 @@ class StepContext:
         self._max_end = max(st + n for _, st, n in seqs)
         self.cache = cache
         self.runtime = runtime
+        self.memo: Dict = {}       # what parts work out once a step (kept by their own keys)
 
     def _host(self, name: str, value):
         if self.graph_capture:

@@ -371,6 +371,78 @@ def test_attention_prefill_tc_kernel_as_a_balanced_list_of_work(nh, nkv, hd, win
             _close(out[r0:r0 + T].view(T, nh, hd), ref, dtype, f"balanced prefill, sequence of {T}, call {call}")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,lens,q0s", [
+    (8, 4, 256, 0, [1500], [1300]), (4, 2, 128, 200, [900, 333], [700, 332]),
+    (2, 2, 64, 0, [700, 64, 300], [650, 0, 129]), (4, 2, 256, 96, [200, 51], [168, 50])])
+def test_attention_prefill_tc_kernel_with_rows_that_are_keys_only(nh, nkv, hd, window, lens, q0s):
+    """The rows of a sequence before its first query position bring keys and values only:
+    the later rows' results are the plain implementation's over the whole sequence, the
+    earlier rows of the output are not written; as a balanced list and as a grid.  The q
+    columns of the earlier rows hold NaN, which must not reach any result."""
+    n = _native()
+    g = torch.Generator().manual_seed(19)
+    dtype = torch.bfloat16
+    scale = 3.0 / math.sqrt(hd)
+    qs, refs = [], []
+    for T, q0 in zip(lens, q0s):
+        q = torch.randn(T, nh, hd, generator=g).to(dtype)
+        k = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(T, nkv, hd, generator=g).to(dtype)
+        refs.append(plain.attention(q.double(), k.double(), v.double(), scale, 30.0, window))
+        q = q.clone()
+        q[:q0] = float("nan")
+        qs.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    packed = torch.cat(qs, dim=0).contiguous().to(DEV)
+    row0 = [0]
+    for T in lens[:-1]:
+        row0.append(row0[-1] + T)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    n_items, need, n_tickets = n.attention_prefill_tc_plan(lens, nh, nkv, hd, window, q0s)
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
+    tickets = torch.zeros(max(n_tickets, 1), dtype=torch.int32, device=DEV)
+    for host in (lens, None):
+        out = torch.full((sum(lens), nh * hd), float("nan"), dtype=dtype, device=DEV)
+        n.attention_prefill_tc(packed, out, i32(row0), i32(lens), len(lens), max(lens), nh, nkv, hd,
+                               scale, 30.0, window, scratch, tickets, host, i32(q0s),
+                               q0s if host else None)
+        assert n.attention_prefill_tc_error() == 0
+        for r0, T, q0, ref in zip(row0, lens, q0s, refs):
+            _close(out[r0 + q0:r0 + T].view(T - q0, nh, hd), ref[q0:], dtype,
+                   f"rows from {q0} of a sequence of {T}")
+            assert torch.isnan(out[r0:r0 + q0].float()).all(), "rows that are keys only were written"
+
+
+def test_gather_kv_rows_brings_pages_back_into_packed_rows():
+    n = _native()
+    g = torch.Generator().manual_seed(20)
+    nh, nkv, hd, page, ring = 3, 2, 16, 4, 12
+    n_pages, slots, max_pages = 40, 3, 10
+    k_pool = torch.randn(n_pages, nkv, page, hd, generator=g).to(torch.bfloat16).to(DEV)
+    v_pool = torch.randn(n_pages, nkv, page, hd, generator=g).to(torch.bfloat16).to(DEV)
+    table = torch.randperm(n_pages, generator=g)[:slots * max_pages].view(slots, max_pages).to(torch.int32).to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    seq_slot, first, upto, row0 = [2, 0], [3, 20], [17, 29], [0, 17]
+    width = (nh + 2 * nkv) * hd
+    for ring_tokens in (0, ring):
+        packed = torch.full((17 + 29, width), 7.0, dtype=torch.bfloat16, device=DEV)
+        n.gather_kv_rows(packed, k_pool, v_pool, table, i32(seq_slot), i32(first), i32(upto), i32(row0),
+                         14, page, ring_tokens, nh, nkv, hd)
+        got = packed.cpu()
+        for b in range(2):
+            for pos in range(0 if b == 0 else 0, upto[b]):
+                row = got[row0[b] + pos]
+                if pos < first[b]:
+                    assert (row == 7.0).all(), "a position that was not asked for was written"
+                    continue
+                cell = pos % ring_tokens if ring_tokens else pos
+                pg = int(table[seq_slot[b], cell // page])
+                assert (row[:nh * hd] == 0).all()
+                want_k = k_pool[pg, :, cell % page].reshape(-1).cpu()
+                want_v = v_pool[pg, :, cell % page].reshape(-1).cpu()
+                assert torch.equal(row[nh * hd:(nh + nkv) * hd], want_k)
+                assert torch.equal(row[(nh + nkv) * hd:], want_v)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
 @pytest.mark.parametrize("hd,rot", [(48, 32), (64, 64), (16, 16)])

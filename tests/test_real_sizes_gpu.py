@@ -281,3 +281,32 @@ def test_generation_at_real_sizes_one_step_ahead_of_the_host(model, dtype):
                 assert int(logits.argmax()) == tok or float(top[0] - top[1]) < 1e-4 * float(top[0].abs())
                 seq.append(tok)
     assert gen.engine.cache.pages_in_use() == 0
+
+
+def test_a_prompt_that_comes_in_pieces_at_real_sizes(model):
+    """A request continued in pieces of 64 and 37 tokens (the windowed layer's ring wraps),
+    alone and beside a second request that goes on token by token: the pieces attend
+    through the prompt kernel over a packed copy of what the sequence holds."""
+    from strata_inference_b200 import Engine
+    from strata_inference_b200.kernels import native
+    d, reqs, refs = model
+    tol = REL_TOL["bfloat16"]
+    eng = Engine.from_dir(d, dtype="bfloat16", max_tokens=2048, max_continuation=64)
+    s = eng.new_sequence()
+    outs, at = [], 0
+    with native.KernelProfile() as prof:
+        for piece in (40, 64, 64):
+            outs.append(eng.step([(s, reqs[0][at:at + piece])], want=[list(range(piece))]))
+            at += piece
+    assert any(r["name"] == "gather_kv_rows" for r in prof.rows())
+    err = _rel(torch.cat(outs), refs[0][:at])
+    assert err <= tol, f"pieces of one request: {err:.2e}"
+    # a second request beside it: its prompt, then single tokens while the first goes on in pieces
+    s2 = eng.new_sequence()
+    eng.step([(s2, reqs[2][:50])])
+    got = eng.step([(s, reqs[0][at:]), (s2, [reqs[2][50]])], want=[[len(reqs[0]) - at - 1], [0]])
+    ref = torch.stack([refs[0][-1], refs[2][50]])
+    assert _rel(got, ref) <= tol, f"a piece beside a single token: {_rel(got, ref):.2e}"
+    eng.end_sequence(s)
+    eng.end_sequence(s2)
+    assert eng.cache.pages_in_use() == 0
