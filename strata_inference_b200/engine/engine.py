@@ -71,9 +71,12 @@ class Engine:
         self.kernel_watch = native.KernelWatch()
         self._graphs: Dict[Tuple, "DecodeGraph"] = {}
         self._prompt_graphs: Dict[Tuple, "PromptGraph"] = {}
-        # captured steps kept: single-token steps by batch size and sampling options, and
-        # as many steps of prompts by rows, sequences and wanted rows
-        self.max_graphs = 16
+        # recorded steps kept, least recently used first out: single-token steps with sampling
+        # (by number of sequences, sampling options and length class: recording one costs what
+        # 15 replays cost, and each keeps a [sequences, vocabulary] logits buffer), and steps
+        # that return logits (prompts by rows, sequences and wanted rows; tokens likewise)
+        self.max_graphs = 48
+        self.max_prompt_graphs = 16
         self.first_span = 512       # the shortest length class of recorded single-token steps
         self.prompt_graph_rows = 1024   # steps of prompts of up to this many rows are recorded
         self.last_logits: Optional[torch.Tensor] = None   # of the latest sampled step
@@ -235,7 +238,7 @@ class Engine:
         g = self._prompt_graphs.pop(key, None)
         if g is None:
             g = PromptGraph(self, rows, len(seqs), len(want_rows), from_start, longest, span)
-            while len(self._prompt_graphs) >= self.max_graphs:
+            while len(self._prompt_graphs) >= self.max_prompt_graphs:
                 self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
         self._prompt_graphs[key] = g       # most recently used last
         # (the graph's buffer is overwritten by its next replay: the caller gets a copy)

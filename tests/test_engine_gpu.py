@@ -586,7 +586,7 @@ def test_recorded_prompt_steps_can_be_switched_off_and_are_few(model_dirs):
     eng.end_sequence(slot)
     assert not eng._prompt_graphs
     eng.prompt_graph_rows = 1024
-    eng.max_graphs = 2
+    eng.max_prompt_graphs = 2
     for n_seqs in (1, 2, 3, 1):      # a recording per number of sequences; the oldest goes
         slots = [eng.new_sequence() for _ in range(n_seqs)]
         got = eng.step([(s, toks) for s in slots])
