@@ -721,3 +721,74 @@ def test_single_token_steps_are_recorded_by_length_class(model_dirs):
     assert sorted(k[4] for k in eng._graphs) == [64, 128, 256]
     assert all(g.graph is not None for g in eng._graphs.values())
     eng.end_sequence(slot)
+
+
+@pytest.mark.parametrize("name,page,seed", [("A", 4, 1), ("C", 16, 2), ("B", 8, 3), ("C", 64, 4)])
+def test_a_random_schedule_of_steps(model_dirs, name, page, seed):
+    """Sequences come and go in a random order of prompt steps, pieces, single-token steps
+    through ``step`` and through ``decode_step`` (recorded or not, fed from the host or on
+    the device), with other sequences beside them or alone: every logit row that comes back
+    is the plain implementation's for that sequence at that position."""
+    import random
+    rnd = random.Random(seed)
+    cfg = CONFIGS[name]
+    top = cfg["max_position_embeddings"]
+    eng = _engine(model_dirs, name, "float32", page, max_tokens=8 * ((top + 63) // 64) * 64)
+    eng.first_span = 32
+    room = eng.cache.max_step_tokens()
+    live = {}          # slot -> [tokens, reference logits, position]
+    checked = 0
+    for op in range(70):
+        kind = rnd.choice(["new", "new", "piece", "tokens", "tokens", "decode", "decode", "end"])
+        if kind == "new" and len(live) < 6:
+            fresh = []
+            for _ in range(rnd.randint(1, 3)):
+                if len(live) + len(fresh) >= 6:
+                    break
+                toks = random_prompts(cfg, [rnd.randint(top // 2, top - 1)], seed=1000 * seed + op + len(fresh))[0]
+                fresh.append((eng.new_sequence(), toks, rnd.randint(1, min(len(toks) - 1, 70))))
+            got = eng.step([(s, t[:n]) for s, t, n in fresh])
+            for row, (s, t, n) in enumerate(fresh):
+                ref = plain_logits(t, model_dirs[name, "float32"], cfg)
+                live[s] = [t, ref, n]
+                assert_logits_close(got[row:row + 1], ref[n - 1:n], "float32", f"op {op}: prompt of {n}")
+                checked += 1
+        elif kind == "piece" and live:
+            s = rnd.choice(sorted(live))
+            t, ref, pos = live[s]
+            n = min(rnd.randint(2, 40), len(t) - pos, eng.cache.max_step_tokens(pos))
+            if n >= 1:
+                got = eng.step([(s, t[pos:pos + n])], want=[[0, n - 1]])
+                assert_logits_close(got, torch.stack([ref[pos], ref[pos + n - 1]]), "float32",
+                                    f"op {op}: piece of {n} at {pos}")
+                live[s][2] = pos + n
+                checked += 2
+        elif kind in ("tokens", "decode") and live:
+            some = [s for s in sorted(live) if live[s][2] < len(live[s][0])]
+            some = rnd.sample(some, rnd.randint(1, len(some))) if some else []
+            for _ in range(rnd.randint(1, 4)):
+                some = [s for s in some if live[s][2] < len(live[s][0])]
+                if not some:
+                    break
+                fed = [live[s][0][live[s][2]] for s in some]
+                if kind == "tokens":
+                    got = eng.step([(s, [f]) for s, f in zip(some, fed)])
+                else:
+                    eng.decode_step(some, fed, use_graph=rnd.random() < 0.8)
+                    got = eng.last_logits
+                ref = torch.stack([live[s][1][live[s][2]] for s in some])
+                assert_logits_close(got, ref, "float32", f"op {op}: {kind} for {some}")
+                for s in some:
+                    live[s][2] += 1
+                checked += len(some)
+        elif kind == "end" and live:
+            s = rnd.choice(sorted(live))
+            eng.end_sequence(s)
+            del live[s]
+        for s in [s for s in live if live[s][2] >= len(live[s][0])]:
+            eng.end_sequence(s)
+            del live[s]
+    for s in list(live):
+        eng.end_sequence(s)
+    assert checked > 60 and eng.cache.pages_in_use() == 0
+    eng.read_back(torch.zeros(1, dtype=torch.int32, device="cuda:0"))      # no bounded wait ran out
