@@ -310,3 +310,72 @@ def test_a_prompt_that_comes_in_pieces_at_real_sizes(model):
     eng.end_sequence(s)
     eng.end_sequence(s2)
     assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype,seed", [("bfloat16", 1), ("bfloat16", 2), ("float32", 3)])
+def test_a_random_schedule_at_real_sizes(model, dtype, seed):
+    """The three requests start, go on in pieces, token by token through ``step`` and through
+    recorded steps, end and start again in a random order, alone or beside each other: every
+    row of logits that comes back is the plain implementation's.  (At these sizes the steps
+    run the tcgen05 prompt attention as a list and over gathered pieces, the mma.sync prompt
+    attention for short prompts, the decode attention with its splits, the weight-streaming
+    products and the library's.)"""
+    import random
+    from strata_inference_b200 import Engine
+    d, reqs, refs = model
+    tol = REL_TOL[dtype]
+    rnd = random.Random(seed)
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=2048, max_continuation=64)
+    eng.first_span = 64
+    live, worst, checked = {}, 0.0, 0          # request -> [slot, position]
+
+    def check(got, rows, what):
+        nonlocal worst, checked
+        ref = torch.stack([refs[i][p] for i, p in rows])
+        err = _rel(got, ref)
+        worst = max(worst, err)
+        checked += len(rows)
+        assert err <= tol, f"{what}: {err:.2e}"
+
+    for op in range(90):
+        kind = rnd.choice(["new", "piece", "tokens", "tokens", "decode", "decode", "end"])
+        idle = [i for i in range(3) if i not in live]
+        if kind == "new" and idle:
+            some = rnd.sample(idle, rnd.randint(1, len(idle)))
+            cut = {i: rnd.randint(1, len(reqs[i]) - 2) for i in some}
+            for i in some:
+                live[i] = [eng.new_sequence(), cut[i]]
+            got = eng.step([(live[i][0], reqs[i][:cut[i]]) for i in some])
+            check(got, [(i, cut[i] - 1) for i in some], f"op {op}: prompts {cut}")
+        elif kind == "piece" and live:
+            i = rnd.choice(sorted(live))
+            s, pos = live[i]
+            n = min(rnd.randint(2, 64), len(reqs[i]) - pos, eng.cache.max_step_tokens(pos))
+            if n >= 1:
+                got = eng.step([(s, reqs[i][pos:pos + n])], want=[[0, n - 1]])
+                check(got, [(i, pos), (i, pos + n - 1)], f"op {op}: piece of {n} at {pos}")
+                live[i][1] = pos + n
+        elif kind in ("tokens", "decode") and live:
+            some = rnd.sample(sorted(live), rnd.randint(1, len(live)))
+            for _ in range(rnd.randint(1, 5)):
+                some = [i for i in some if live[i][1] < len(reqs[i])]
+                if not some:
+                    break
+                fed = [reqs[i][live[i][1]] for i in some]
+                if kind == "tokens":
+                    got = eng.step([(live[i][0], [f]) for i, f in zip(some, fed)])
+                else:
+                    eng.decode_step([live[i][0] for i in some], fed, use_graph=rnd.random() < 0.8)
+                    got = eng.last_logits
+                check(got, [(i, live[i][1]) for i in some], f"op {op}: {kind} for {some}")
+                for i in some:
+                    live[i][1] += 1
+        elif kind == "end" and live:
+            i = rnd.choice(sorted(live))
+            eng.end_sequence(live.pop(i)[0])
+        for i in [i for i in live if live[i][1] >= len(reqs[i])]:
+            eng.end_sequence(live.pop(i)[0])
+    for i in list(live):
+        eng.end_sequence(live.pop(i)[0])
+    assert checked > 25 and eng.cache.pages_in_use() == 0
+    eng.read_back(torch.zeros(1, dtype=torch.int32, device="cuda:0"))
