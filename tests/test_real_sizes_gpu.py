@@ -6,6 +6,8 @@ The tiny configurations never reach the code paths that these sizes select
 (head size 256, the 16-byte vector paths, the cluster split of the products,
 the tensor-memory product for many rows of logits)."""
 
+import os
+
 import pytest
 import torch
 
@@ -298,7 +300,8 @@ def test_a_prompt_that_comes_in_pieces_at_real_sizes(model):
         for piece in (40, 64, 64):
             outs.append(eng.step([(s, reqs[0][at:at + piece])], want=[list(range(piece))]))
             at += piece
-    assert any(r["name"] == "gather_kv_rows" for r in prof.rows())
+    if os.environ.get("SIB_PREFILL_TCGEN05") != "0":       # (the switch also takes this path away)
+        assert any(r["name"] == "gather_kv_rows" for r in prof.rows())
     err = _rel(torch.cat(outs), refs[0][:at])
     assert err <= tol, f"pieces of one request: {err:.2e}"
     # a second request beside it: its prompt, then single tokens while the first goes on in pieces
