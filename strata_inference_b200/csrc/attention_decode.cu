@@ -82,13 +82,15 @@ constexpr int MAX_SPLITS = 128;
 // the chain of waits of a step of one row: batch 1 runs 1.5 % faster with it; with more rows
 // the registers that the tile holds across the wait cost more than the wait: batch 2 ran 3 %
 // and batch 8 2 % slower with it).
-template <int HD, int G, bool EARLY>
-__global__ void __launch_bounds__(128) attention_decode_kernel(AttnDecodeArgs p) {
+// WIDE: blocks of 8 warps (a single row's step: half as many partial results to join as with
+// blocks of 4); the narrower kernel keeps its registers and shared memory as they were.
+template <int HD, int G, bool EARLY, bool WIDE = false>
+__global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(AttnDecodeArgs p) {
     constexpr int KB = HD / 32;          // 32-wide blocks of the head dimension
     constexpr int LPK = HD / 8;          // lanes that cover one value row
     constexpr int KPP = 32 / LPK;        // keys per pass of the weighted sum
     constexpr int PW = HD + 2;           // a partial: max, sum, HD accumulators
-    __shared__ float sm_all[4][2][16][8];
+    __shared__ float sm_all[WIDE ? 8 : 4][2][16][8];
     extern __shared__ __align__(16) float part_dyn[];          // [warps][G][PW]
     float(*part_sm)[G][PW] = reinterpret_cast<float(*)[G][PW]>(part_dyn);
     __shared__ float w_sm[G][MAX_SPLITS];
@@ -358,7 +360,19 @@ SIB_EXPORT int sib_attention_decode_supports(int n_heads, int n_kv, int head_dim
 // How many warps of this kernel the current device holds at a time for the shape (blocks of
 // 4 warps that fit on an SM, by the kernel's registers and shared memory, times the SMs):
 // what a caller sizes its split of the keys by.  0 if the shape is not one this kernel takes.
+static int resident_warps(int n_heads, int n_kv, int head_dim, int warps);
+
 SIB_EXPORT int sib_attention_decode_resident_warps(int n_heads, int n_kv, int head_dim) {
+    return resident_warps(n_heads, n_kv, head_dim, 4);
+}
+
+// The same for blocks of `warps` warps (8: the wide kernel, which has room for fewer blocks).
+SIB_EXPORT int sib_attention_decode_resident_warps_of(int n_heads, int n_kv, int head_dim, int warps) {
+    if (warps != 1 && warps != 2 && warps != 4 && warps != 8) return 0;
+    return resident_warps(n_heads, n_kv, head_dim, warps);
+}
+
+static int resident_warps(int n_heads, int n_kv, int head_dim, int warps) {
     if (!sib_attention_decode_supports(n_heads, n_kv, head_dim, 16)) return 0;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -368,8 +382,13 @@ SIB_EXPORT int sib_attention_decode_resident_warps(int n_heads, int n_kv, int he
     int per_sm = 0;
     cudaError_t e = cudaErrorInvalidValue;
 #define ASK(HD, GG)                                                                         \
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, GG, false>, 128, \
-                                                      (size_t)4 * GG * (HD + 2) * sizeof(float))
+    e = warps == 8                                                                          \
+            ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(                                \
+                  &per_sm, attention_decode_kernel<HD, GG, false, true>, 256,               \
+                  (size_t)8 * GG * (HD + 2) * sizeof(float))                                \
+            : cudaOccupancyMaxActiveBlocksPerMultiprocessor(                                \
+                  &per_sm, attention_decode_kernel<HD, GG, false>, 32 * warps,              \
+                  (size_t)warps * GG * (HD + 2) * sizeof(float))
 #define BY_G(HD)                    \
     do {                            \
         if (G == 1) ASK(HD, 1);     \
@@ -383,7 +402,7 @@ SIB_EXPORT int sib_attention_decode_resident_warps(int n_heads, int n_kv, int he
 #undef BY_G
 #undef ASK
     if (e != cudaSuccess || per_sm <= 0) return 0;
-    return per_sm * 4 * sms;
+    return per_sm * warps * sms;
 }
 
 static int attention_decode(
@@ -399,8 +418,8 @@ static int attention_decode(
                 "in multiples of 16)", n_heads, n_kv, head_dim, page_tokens);
     SIB_REQUIRE(rows > 0 && splits >= 1 && splits <= MAX_SPLITS,
                 "attention_decode: rows=%d splits=%d (1 to %d)", rows, splits, MAX_SPLITS);
-    SIB_REQUIRE(warps == 1 || warps == 2 || warps == 4,
-                "attention_decode: %d warps a block; 1, 2 or 4", warps);
+    SIB_REQUIRE(warps == 1 || warps == 2 || warps == 4 || warps == 8,
+                "attention_decode: %d warps a block; 1, 2, 4 or 8", warps);
     SIB_REQUIRE(splits == 1 || (partial != nullptr && tickets != nullptr &&
                                 ((uintptr_t)partial % 16) == 0),
                 "attention_decode: %d splits need memory for their partial results and the "
@@ -423,7 +442,13 @@ static int attention_decode(
     const bool early_keys = fresh > 0 && rows == 1;
 #define GO(HD, GG)                                                                                 \
     do {                                                                                           \
-        if (early_keys)                                                                            \
+        if (warps == 8 && early_keys)                                                              \
+            sib_launch_chained(attention_decode_kernel<HD, GG, true, true>, dim3((unsigned)blocks), \
+                               dim3(32 * warps), (size_t)warps * GG * (HD + 2) * sizeof(float), s, p); \
+        else if (warps == 8)                                                                       \
+            sib_launch_chained(attention_decode_kernel<HD, GG, false, true>, dim3((unsigned)blocks), \
+                               dim3(32 * warps), (size_t)warps * GG * (HD + 2) * sizeof(float), s, p); \
+        else if (early_keys)                                                                       \
             sib_launch_chained(attention_decode_kernel<HD, GG, true>, dim3((unsigned)blocks),      \
                                dim3(32 * warps), (size_t)warps * GG * (HD + 2) * sizeof(float), s, p); \
         else                                                                                       \

@@ -433,11 +433,11 @@ def attention_decode_supports(n_heads: int, n_kv: int, head_dim: int, page_token
                                                         c_int(head_dim), c_int(page_tokens)))
 
 
-def attention_decode_resident_warps(n_heads: int, n_kv: int, head_dim: int) -> int:
+def attention_decode_resident_warps(n_heads: int, n_kv: int, head_dim: int, warps: int = 4) -> int:
     """Warps of the decode attention kernel that the current device holds at a time for this
-    shape (0: not a shape the kernel takes)."""
-    return int(library().sib_attention_decode_resident_warps(c_int(n_heads), c_int(n_kv),
-                                                             c_int(head_dim)))
+    shape, in blocks of ``warps`` warps (0: not a shape the kernel takes)."""
+    return int(library().sib_attention_decode_resident_warps_of(c_int(n_heads), c_int(n_kv),
+                                                                c_int(head_dim), c_int(warps)))
 
 
 @_timed(lambda q, q_stride, k_pool, v_pool, page_table, page_tokens, ring_tokens, row_pos, row_seq,

@@ -110,6 +110,7 @@ class Attention:
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
         self._resident_warps: Optional[int] = None
         self._target_warps = _WARPS_PER_SM * rt.sm_count
+        self._block_warps = tuple(int(w) for w in os.environ.get("SIB_DECODE_WARPS", "8,4,2").split(","))
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.window))
@@ -130,12 +131,22 @@ class Attention:
         ``runs`` blocks of ``warps`` warps.  All of them should be resident at
         once (a second, partly filled wave of blocks costs more than it brings)
         and be about as many warps as that allows; a warp takes no fewer than 32
-        keys."""
+        keys.  Blocks of 8 warps (of which the device holds fewer warps in all) halve the
+        partial results that the last block of a (row, kv head) joins: they are taken where
+        that join weighs most, with few rows and therefore many runs each (measured at the
+        Gemma2-2B shape, context 8 192: batch 1 1.83 -> 1.74 ms, batch 2 1.95 -> 1.84, batch 4
+        2.06 -> 2.04; batch 6 and 8 are better off with blocks of 4)."""
         if self._resident_warps is None:     # what the device holds of this kernel at a time
-            self._resident_warps = native.attention_decode_resident_warps(self.nh, self.nkv, self.hd)
+            self._resident_warps = {w: native.attention_decode_resident_warps(self.nh, self.nkv, self.hd, w)
+                                    for w in (8, 4)}
         units = max(1, ctx.n_rows * self.nkv)
-        most = max(1, min(self._resident_warps // units, -(-self._longest(ctx, capacity) // 32)))
-        for warps in (4, 2):     # wider blocks leave fewer partial results to join
+        keys = -(-self._longest(ctx, capacity) // 32)
+        most = max(1, min(self._resident_warps[4] // units, keys))
+        if 8 in self._block_warps and self._resident_warps[8]:
+            wide = min(self._resident_warps[8] // units, keys) // 8
+            if wide >= 8 and 8 * wide >= 0.6 * most:
+                return min(wide, 128), 8
+        for warps in (w for w in self._block_warps if w < 8):   # wider blocks: fewer results to join
             runs = min(most // warps, 128)
             if runs >= 1 and runs * warps >= 0.9 * most:
                 return runs, warps
