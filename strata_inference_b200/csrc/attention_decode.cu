@@ -292,6 +292,20 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
     if (ticket_sm != p.splits - 1) return;
     __threadfence();
     const float* unit_partial = p.partial + ((size_t)r * p.n_heads + kvh * G) * p.splits * PW;
+    // With a thread per pair of output columns and at most 32 runs, every accumulator that a
+    // thread needs is asked for now, before the maxima and the sums (which do not depend on
+    // them): one round trip instead of one per 8 runs after two more.
+    constexpr int AHEAD = 32;
+    const bool ahead = WIDE && G * HD / 2 <= (int)blockDim.x && p.splits <= AHEAD;
+    float2 early_v[WIDE ? AHEAD : 1];
+    if (WIDE && ahead && (int)threadIdx.x < G * HD / 2) {
+        const int h = threadIdx.x / (HD / 2), d = 2 * (threadIdx.x % (HD / 2));
+        const float* pp = unit_partial + (size_t)h * p.splits * PW + 2 + d;
+#pragma unroll
+        for (int b = 0; b < AHEAD; ++b)
+            early_v[b] = b < p.splits ? __ldcg(reinterpret_cast<const float2*>(pp + (size_t)b * PW))
+                                      : make_float2(0.f, 0.f);
+    }
     for (int i = threadIdx.x; i < G * p.splits; i += blockDim.x)
         w_sm[i / p.splits][i % p.splits] = __ldcg(unit_partial + (size_t)i * PW);       // the maxima
     __syncthreads();
@@ -317,6 +331,23 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
         ml_sm[h][1] = sum;
     }
     __syncthreads();
+    if (WIDE && ahead) {
+        if ((int)threadIdx.x < G * HD / 2) {
+            const int h = threadIdx.x / (HD / 2), d = 2 * (threadIdx.x % (HD / 2));
+            float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int b = 0; b < AHEAD; ++b) {        // in run order; runs beyond the last weigh 0
+                const float f = b < p.splits ? w_sm[h][b] : 0.f;
+                a.x += f * early_v[b].x;
+                a.y += f * early_v[b].y;
+            }
+            const float inv = 1.0f / ml_sm[h][1];
+            *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
+                __floats2bfloat162_rn(a.x * inv, a.y * inv);
+        }
+        if (threadIdx.x == 0) p.tickets[r * p.n_kv + kvh] = 0;
+        return;
+    }
     // the weighted sum of the runs' accumulators, 8 loads in flight per thread
     for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
         const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
@@ -382,6 +413,10 @@ static int resident_warps(int n_heads, int n_kv, int head_dim, int warps) {
     int per_sm = 0;
     cudaError_t e = cudaErrorInvalidValue;
 #define ASK(HD, GG)                                                                         \
+    if (warps == 8 && (size_t)8 * GG * (HD + 2) * sizeof(float) > 48 * 1024)                \
+        cudaFuncSetAttribute(attention_decode_kernel<HD, GG, false, true>,                  \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                             (int)((size_t)8 * GG * (HD + 2) * sizeof(float)));             \
     e = warps == 8                                                                          \
             ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(                                \
                   &per_sm, attention_decode_kernel<HD, GG, false, true>, 256,               \
@@ -391,10 +426,10 @@ static int resident_warps(int n_heads, int n_kv, int head_dim, int warps) {
                   (size_t)warps * GG * (HD + 2) * sizeof(float))
 #define BY_G(HD)                    \
     do {                            \
-        if (G == 1) ASK(HD, 1);     \
-        else if (G == 2) ASK(HD, 2); \
-        else if (G == 4) ASK(HD, 4); \
-        else ASK(HD, 8);            \
+        if (G == 1) { ASK(HD, 1); }      \
+        else if (G == 2) { ASK(HD, 2); } \
+        else if (G == 4) { ASK(HD, 4); } \
+        else { ASK(HD, 8); }             \
     } while (0)
     if (head_dim == 64) BY_G(64);
     else if (head_dim == 128) BY_G(128);
@@ -442,6 +477,15 @@ static int attention_decode(
     const bool early_keys = fresh > 0 && rows == 1;
 #define GO(HD, GG)                                                                                 \
     do {                                                                                           \
+        if (warps == 8 && (size_t)warps * GG * (HD + 2) * sizeof(float) > 48 * 1024) {             \
+            /* (8 warps' partial results of 8 heads of 256 do not fit the default limit) */       \
+            cudaFuncSetAttribute(attention_decode_kernel<HD, GG, true, true>,                      \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
+                                 (int)((size_t)warps * GG * (HD + 2) * sizeof(float)));            \
+            cudaFuncSetAttribute(attention_decode_kernel<HD, GG, false, true>,                     \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
+                                 (int)((size_t)warps * GG * (HD + 2) * sizeof(float)));            \
+        }                                                                                          \
         if (warps == 8 && early_keys)                                                              \
             sib_launch_chained(attention_decode_kernel<HD, GG, true, true>, dim3((unsigned)blocks), \
                                dim3(32 * warps), (size_t)warps * GG * (HD + 2) * sizeof(float), s, p); \

@@ -170,7 +170,11 @@ def test_attention_rows_over_cache_and_fresh(dtype, nh, nkv, hd, window, cap, sp
 @pytest.mark.parametrize("nh,nkv,hd,window,cap,splits,warps", [
     (4, 2, 64, 0, 0.0, 1, 4), (8, 4, 256, 40, 50.0, 5, 4), (8, 1, 128, 0, 30.0, 3, 2),
     (2, 2, 128, 21, 0.0, 16, 1), (8, 4, 256, 0, 0.0, 2, 1), (4, 1, 256, 100, 50.0, 1, 2),
-    (8, 4, 256, 0, 50.0, 1, 1), (16, 2, 64, 0, 0.0, 7, 4)])
+    (8, 4, 256, 0, 50.0, 1, 1), (16, 2, 64, 0, 0.0, 7, 4),
+    # blocks of 8 warps: a thread per pair of output columns (accumulators asked for ahead of
+    # the maxima) and fewer threads than that; more runs than are asked for ahead; one run
+    (8, 4, 256, 0, 50.0, 4, 8), (8, 4, 256, 40, 50.0, 2, 8), (16, 2, 64, 0, 0.0, 3, 8),
+    (4, 2, 128, 0, 30.0, 40, 8), (2, 2, 128, 21, 0.0, 1, 8), (8, 1, 256, 0, 0.0, 2, 8)])
 def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits, warps):
     """The bfloat16 decode kernel: rows at tile and page edges, with and
     without a ring, several rows of different sequences in one launch."""
