@@ -428,7 +428,7 @@ def run_sweep(args):
               f"{moved / (ms * 1e-3) / 1e9 / peaks['hbm_gbs']:.2f} of the copy bandwidth", flush=True)
     print(f"prompt steps, one prompt (peak {peaks['bf16_tflops']:.0f} TFLOP/s)")
     for T in (64, 128, 256, 512, 1024, 2048, 4096, 8192):
-        if T >= engine.max_seq_len:
+        if T > engine.max_seq_len:
             continue
         ms = time_prefill(engine, T, reps=3)
         frac = prefill_flops(cfg, T) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
