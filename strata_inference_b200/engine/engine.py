@@ -1,7 +1,9 @@
 """The engine: model + cache + ONE step function.
 
 ``step(entries, want)`` runs exactly the tokens it is given, for sequences
-that hold cache slots, as one packed batch (no padding rows exist), and
+that hold cache slots, as one packed batch (rows of different sequences follow
+one another; a recorded short step is filled up with rows of a sequence that
+holds no slot, which no other row sees and which are not stored), and
 returns 32-bit logits at the wanted rows.  A sequence's first step carries
 its whole prompt; later steps carry its next token(s).  Everything above
 (generation, replay, benchmarks) goes through this function or through its
