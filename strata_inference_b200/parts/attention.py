@@ -46,6 +46,38 @@ _WARPS_PER_SM = 16
 _USE_TCGEN05_PREFILL = os.environ.get("SIB_PREFILL_TCGEN05", "1") != "0"
 
 
+def decode_shape(units: int, longest: int, window: int, resident4: int, resident8: int,
+                 block_warps=(8, 4, 2)):
+    """(runs, warps) of the decode kernel for ``units`` (row, kv head) pairs whose rows see up
+    to ``longest`` keys, on a device that holds ``resident4`` warps of the kernel in blocks of
+    4 (or fewer) warps and ``resident8`` in blocks of 8 (``Attention._decode_shape`` says why)."""
+    # (a full window does not begin at a tile's first key: it reaches into one tile more)
+    tiles = -(-longest // 16) + (1 if 0 < window <= longest else 0)
+
+    def fewest(resident: int) -> int:
+        """Warps for a (row, kv head): as few tiles each as ``resident`` warps allow."""
+        room = max(1, resident // units)
+        each = -(-tiles // room)
+        return max(1, min(room, -(-tiles // each)))
+
+    def trimmed(runs: int, warps: int):
+        """Without the blocks that whole blocks of ``warps`` warps leave no tile for."""
+        each = -(-tiles // (runs * warps))
+        return -(-(-(-tiles // each)) // warps), warps
+
+    most = fewest(resident4)
+    if 8 in block_warps and resident8 // units >= 8:
+        wide = min(-(-fewest(resident8) // 8), resident8 // units // 8, 128)
+        if wide >= 8 and 8 * wide >= 0.6 * most:
+            return trimmed(wide, 8)
+    room = max(1, resident4 // units)
+    for warps in (w for w in block_warps if w < 8):   # wider blocks: fewer results to join
+        runs = min(-(-most // warps), room // warps, 128)
+        if runs >= 1 and runs * warps >= 0.9 * most:
+            return trimmed(runs, warps)
+    return trimmed(min(most, 128), 1)
+
+
 class Attention:
     chain_safe = True      # deferred results are read by this runtime's and native's launchers only
 
@@ -129,9 +161,14 @@ class Attention:
     def _decode_shape(self, ctx, capacity: int):
         """(runs, warps) for the decode kernel: each (row, kv head) is read by
         ``runs`` blocks of ``warps`` warps.  All of them should be resident at
-        once (a second, partly filled wave of blocks costs more than it brings)
-        and be about as many warps as that allows; a warp takes no fewer than 32
-        keys.  Blocks of 8 warps (of which the device holds fewer warps in all) halve the
+        once (a second, partly filled wave of blocks costs more than it brings).  A warp
+        walks its tiles of 16 keys one after the other, a round trip to memory each, so a
+        (row, kv head) gets as many warps as give each the fewest tiles that residency
+        allows, and no more than that needs: more warps only mean more partial results to
+        join.  (Before, a warp took no fewer than 32 keys and all the warps that fit: with the
+        rule above batch 1 went from 1.64 to 1.57 ms at context 1 024 and from 1.72 to 1.68 ms at
+        8 192, batch 16 from 2.07 to 1.98 ms at context 1 024; no size measured lost, on the 9B
+        and 27B shapes neither.)  Blocks of 8 warps (of which the device holds fewer warps in all) halve the
         partial results that the last block of a (row, kv head) joins: they are taken where
         that join weighs most, with few rows and therefore many runs each (measured at the
         Gemma2-2B shape, context 8 192: batch 1 1.83 -> 1.74 ms, batch 2 1.95 -> 1.84, batch 4
@@ -139,18 +176,8 @@ class Attention:
         if self._resident_warps is None:     # what the device holds of this kernel at a time
             self._resident_warps = {w: native.attention_decode_resident_warps(self.nh, self.nkv, self.hd, w)
                                     for w in (8, 4)}
-        units = max(1, ctx.n_rows * self.nkv)
-        keys = -(-self._longest(ctx, capacity) // 32)
-        most = max(1, min(self._resident_warps[4] // units, keys))
-        if 8 in self._block_warps and self._resident_warps[8]:
-            wide = min(self._resident_warps[8] // units, keys) // 8
-            if wide >= 8 and 8 * wide >= 0.6 * most:
-                return min(wide, 128), 8
-        for warps in (w for w in self._block_warps if w < 8):   # wider blocks: fewer results to join
-            runs = min(most // warps, 128)
-            if runs >= 1 and runs * warps >= 0.9 * most:
-                return runs, warps
-        return min(most, 128), 1
+        return decode_shape(max(1, ctx.n_rows * self.nkv), self._longest(ctx, capacity), self.window,
+                            self._resident_warps[4], self._resident_warps[8], self._block_warps)
 
     def _pieces_pay(self, ctx) -> bool:
         """Whether copying what the step's sequences hold (read, write, read again by the
