@@ -77,6 +77,65 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&o)[8]) {
 // The most splits of a (row, kv head) a launch takes.
 constexpr int MAX_SPLITS = 128;
 
+// The join of the runs of a (row, kv head) by the block that drew the last ticket, without a
+// barrier: a thread takes NITEM pairs of output columns (pair threadIdx.x, then threadIdx.x +
+// blockDim.x; all lanes of a warp work on one head, since HD / 2 is a multiple of 32) and a
+// lane the maximum and the sum of run `lane` (and lane + 32 with NRUN 64).  Every
+// accumulator that a thread needs and its lane's runs' maxima and sums are asked for at
+// once, one round trip; the runs' weights are made with the warp's shuffles.  For at most
+// NRUN runs and G * HD / 2 <= NITEM * blockDim.x.
+template <int HD, int G, int NITEM, int NRUN>
+__device__ __forceinline__ void join_runs_by_warp(const float* unit_partial, int splits,
+                                                  __nv_bfloat16* out_row, int lane) {
+    constexpr int PW = HD + 2;
+    constexpr int LR = (NRUN + 31) / 32;     // runs a lane answers for
+    float2 v[NITEM][NRUN], ml[NITEM][LR];
+#pragma unroll
+    for (int k = 0; k < NITEM; ++k) {
+        const int item = threadIdx.x + k * blockDim.x;
+        const bool live = item < G * HD / 2;                  // (the same for a whole warp)
+        const int h = live ? item / (HD / 2) : 0, d = 2 * (item % (HD / 2));
+        const float* ph = unit_partial + (size_t)h * splits * PW;
+#pragma unroll
+        for (int b = 0; b < NRUN; ++b)
+            v[k][b] = live && b < splits
+                          ? __ldcg(reinterpret_cast<const float2*>(ph + (size_t)b * PW + 2 + d))
+                          : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < LR; ++j)
+            ml[k][j] = live && lane + 32 * j < splits
+                           ? __ldcg(reinterpret_cast<const float2*>(ph + (size_t)(lane + 32 * j) * PW))
+                           : make_float2(-INFINITY, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < NITEM; ++k) {
+        const int item = threadIdx.x + k * blockDim.x;
+        if (item >= G * HD / 2) continue;
+        const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
+        float mx = ml[k][0].x;
+#pragma unroll
+        for (int j = 1; j < LR; ++j) mx = fmaxf(mx, ml[k][j].x);
+        mx = warp_max(mx);
+        float f[LR], part = 0.f;
+#pragma unroll
+        for (int j = 0; j < LR; ++j) {
+            f[j] = ml[k][j].x == -INFINITY ? 0.f : expf(ml[k][j].x - mx);   // a run without keys
+            part += f[j] * ml[k][j].y;
+        }
+        const float sum = warp_sum(part);
+        float2 a = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int b = 0; b < NRUN; ++b) {         // in run order; runs beyond the last weigh 0
+            const float fb = __shfl_sync(0xffffffffu, f[b / 32], b % 32);
+            a.x += fb * v[k][b].x;
+            a.y += fb * v[k][b].y;
+        }
+        const float inv = 1.0f / sum;
+        *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
+            __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    }
+}
+
 // HD: head size (64, 128 or 256).  G: query heads per kv head (1, 2, 4 or 8).  EARLY: the first
 // tile of keys may be fetched before the kernel ahead of this one has finished (it shortens
 // the chain of waits of a step of one row: batch 1 runs 1.5 % faster with it; with more rows
@@ -292,19 +351,28 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
     if (ticket_sm != p.splits - 1) return;
     __threadfence();
     const float* unit_partial = p.partial + ((size_t)r * p.n_heads + kvh * G) * p.splits * PW;
-    // With a thread per pair of output columns and at most 32 runs, every accumulator that a
-    // thread needs is asked for now, before the maxima and the sums (which do not depend on
-    // them): one round trip instead of one per 8 runs after two more.
-    constexpr int AHEAD = 32;
-    const bool ahead = WIDE && G * HD / 2 <= (int)blockDim.x && p.splits <= AHEAD;
-    float2 early_v[WIDE ? AHEAD : 1];
-    if (WIDE && ahead && (int)threadIdx.x < G * HD / 2) {
-        const int h = threadIdx.x / (HD / 2), d = 2 * (threadIdx.x % (HD / 2));
-        const float* pp = unit_partial + (size_t)h * p.splits * PW + 2 + d;
-#pragma unroll
-        for (int b = 0; b < AHEAD; ++b)
-            early_v[b] = b < p.splits ? __ldcg(reinterpret_cast<const float2*>(pp + (size_t)b * PW))
-                                      : make_float2(0.f, 0.f);
+    // Few enough runs and columns for a warp to join its columns by itself (before: maxima, a
+    // barrier, one thread's loop over the runs, a barrier, the sums' loads, a barrier, a loop,
+    // a barrier, then the accumulators).
+    {
+        constexpr int ITEMS = G * HD / 2;
+        bool joined = true;
+        if (WIDE && ITEMS <= 256 && p.splits <= 32)
+            join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane);
+        else if (WIDE && ITEMS <= 256 && p.splits <= 64)
+            join_runs_by_warp<HD, G, 1, 64>(unit_partial, p.splits, out_row, lane);
+        else if (WIDE && ITEMS <= 512 && p.splits <= 32)
+            join_runs_by_warp<HD, G, 2, 32>(unit_partial, p.splits, out_row, lane);
+        else if (!WIDE && ITEMS <= (int)blockDim.x && p.splits <= 32)
+            join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane);
+        else if (!WIDE && ITEMS <= 2 * (int)blockDim.x && p.splits <= 16)
+            join_runs_by_warp<HD, G, 2, 16>(unit_partial, p.splits, out_row, lane);
+        else
+            joined = false;
+        if (joined) {
+            if (threadIdx.x == 0) p.tickets[r * p.n_kv + kvh] = 0;
+            return;
+        }
     }
     for (int i = threadIdx.x; i < G * p.splits; i += blockDim.x)
         w_sm[i / p.splits][i % p.splits] = __ldcg(unit_partial + (size_t)i * PW);       // the maxima
@@ -331,23 +399,6 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
         ml_sm[h][1] = sum;
     }
     __syncthreads();
-    if (WIDE && ahead) {
-        if ((int)threadIdx.x < G * HD / 2) {
-            const int h = threadIdx.x / (HD / 2), d = 2 * (threadIdx.x % (HD / 2));
-            float2 a = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int b = 0; b < AHEAD; ++b) {        // in run order; runs beyond the last weigh 0
-                const float f = b < p.splits ? w_sm[h][b] : 0.f;
-                a.x += f * early_v[b].x;
-                a.y += f * early_v[b].y;
-            }
-            const float inv = 1.0f / ml_sm[h][1];
-            *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
-                __floats2bfloat162_rn(a.x * inv, a.y * inv);
-        }
-        if (threadIdx.x == 0) p.tickets[r * p.n_kv + kvh] = 0;
-        return;
-    }
     // the weighted sum of the runs' accumulators, 8 loads in flight per thread
     for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
         const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
@@ -413,7 +464,7 @@ static int resident_warps(int n_heads, int n_kv, int head_dim, int warps) {
     int per_sm = 0;
     cudaError_t e = cudaErrorInvalidValue;
 #define ASK(HD, GG)                                                                         \
-    if (warps == 8 && (size_t)8 * GG * (HD + 2) * sizeof(float) > 48 * 1024)                \
+    if (warps == 8 && (size_t)8 * GG * (HD + 2) * sizeof(float) > 32 * 1024)                \
         cudaFuncSetAttribute(attention_decode_kernel<HD, GG, false, true>,                  \
                              cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
                              (int)((size_t)8 * GG * (HD + 2) * sizeof(float)));             \
@@ -477,8 +528,8 @@ static int attention_decode(
     const bool early_keys = fresh > 0 && rows == 1;
 #define GO(HD, GG)                                                                                 \
     do {                                                                                           \
-        if (warps == 8 && (size_t)warps * GG * (HD + 2) * sizeof(float) > 48 * 1024) {             \
-            /* (8 warps' partial results of 8 heads of 256 do not fit the default limit) */       \
+        if (warps == 8 && (size_t)warps * GG * (HD + 2) * sizeof(float) > 32 * 1024) {             \
+            /* (with the kernel's own arrays these do not fit the default 48 KB) */                \
             cudaFuncSetAttribute(attention_decode_kernel<HD, GG, true, true>,                      \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
                                  (int)((size_t)warps * GG * (HD + 2) * sizeof(float)));            \

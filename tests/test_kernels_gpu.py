@@ -174,7 +174,11 @@ def test_attention_rows_over_cache_and_fresh(dtype, nh, nkv, hd, window, cap, sp
     # blocks of 8 warps: a thread per pair of output columns (accumulators asked for ahead of
     # the maxima) and fewer threads than that; more runs than are asked for ahead; one run
     (8, 4, 256, 0, 50.0, 4, 8), (8, 4, 256, 40, 50.0, 2, 8), (16, 2, 64, 0, 0.0, 3, 8),
-    (4, 2, 128, 0, 30.0, 40, 8), (2, 2, 128, 21, 0.0, 1, 8), (8, 1, 256, 0, 0.0, 2, 8)])
+    (4, 2, 128, 0, 30.0, 40, 8), (2, 2, 128, 21, 0.0, 1, 8), (8, 1, 256, 0, 0.0, 2, 8),
+    # the ways the runs are joined: by a warp for its own columns (one or two pairs of columns
+    # a thread; up to 16, 32 or 64 runs) and by the whole block (more runs or more columns)
+    (2, 2, 256, 0, 0.0, 20, 4), (8, 4, 256, 0, 50.0, 20, 4), (2, 2, 256, 30, 0.0, 40, 4),
+    (8, 2, 256, 0, 0.0, 5, 8), (16, 2, 128, 25, 30.0, 3, 8), (8, 4, 256, 0, 0.0, 70, 8)])
 def test_attention_decode_kernel(nh, nkv, hd, window, cap, splits, warps):
     """The bfloat16 decode kernel: rows at tile and page edges, with and
     without a ring, several rows of different sequences in one launch."""
