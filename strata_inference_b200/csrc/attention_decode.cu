@@ -305,39 +305,31 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
         }
     }
     __syncthreads();
-    if (threadIdx.x < G) {
-        const int h = threadIdx.x;
+    __nv_bfloat16* out_row = p.out + (size_t)r * p.n_heads * HD + (size_t)kvh * G * HD;
+    float* my_partial = p.partial + (((size_t)r * p.n_heads + kvh * G) * p.splits + split) * PW;
+    // (every thread makes the warps' weights for its head itself: no thread's loop and no
+    // second barrier between the warps' results and their sum)
+    for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
+        const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
         float mx = -INFINITY;
         for (int w = 0; w < nw; ++w) mx = fmaxf(mx, part_sm[w][h][0]);
         float sum = 0.f;
-        for (int w = 0; w < nw; ++w) {
+        float2 a = make_float2(0.f, 0.f);
+        for (int w = 0; w < nw; ++w) {                      // in warp order
             const float mw = part_sm[w][h][0];
             const float f = mw == -INFINITY ? 0.f : expf(mw - mx);   // a warp without keys
-            w_sm[h][w] = f;
             sum += f * part_sm[w][h][1];
-        }
-        ml_sm[h][0] = mx;
-        ml_sm[h][1] = sum;
-    }
-    __syncthreads();
-    __nv_bfloat16* out_row = p.out + (size_t)r * p.n_heads * HD + (size_t)kvh * G * HD;
-    float* my_partial = p.partial + (((size_t)r * p.n_heads + kvh * G) * p.splits + split) * PW;
-    for (int item = threadIdx.x; item < G * HD / 2; item += blockDim.x) {
-        const int h = item / (HD / 2), d = 2 * (item % (HD / 2));
-        float2 a = make_float2(0.f, 0.f);
-        for (int w = 0; w < nw; ++w) {
-            const float f = w_sm[h][w];
             const float2 v = *reinterpret_cast<const float2*>(&part_sm[w][h][2 + d]);
             a.x += f * v.x;
             a.y += f * v.y;
         }
         if (p.splits == 1) {
-            const float inv = 1.0f / ml_sm[h][1];
+            const float inv = 1.0f / sum;
             *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
                 __floats2bfloat162_rn(a.x * inv, a.y * inv);
         } else {
             float* pp = my_partial + (size_t)h * p.splits * PW;
-            if (d == 0) *reinterpret_cast<float2*>(pp) = make_float2(ml_sm[h][0], ml_sm[h][1]);
+            if (d == 0) *reinterpret_cast<float2*>(pp) = make_float2(mx, sum);
             *reinterpret_cast<float2*>(pp + 2 + d) = a;
         }
     }

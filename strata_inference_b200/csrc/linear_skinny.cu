@@ -82,7 +82,10 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     extern __shared__ float red[];
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = ksplit > 1 ? (int)cluster.block_rank() : 0;
-    if (ksplit > 1) cluster.sync();   // every block of the cluster is running: its memory can be written
+    // Every block of the cluster must be running before its memory is written.  The blocks
+    // say so here and look for the others' word only when they have their sums: the meeting
+    // costs the loads below nothing.
+    if (ksplit > 1) asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (16 * MT);
@@ -170,6 +173,7 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     __syncthreads();
     float4* peers = reinterpret_cast<float4*>(red) + (size_t)8 * (MT * NT * 32);
     if (ksplit > 1) {
+        asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // (all are running)
         // the blocks of a cluster took alternating runs of k of the same weight rows:
         // each adds its 8 warps and hands the sum to the first block
         if (rank > 0) {
