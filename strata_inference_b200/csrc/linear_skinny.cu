@@ -25,6 +25,10 @@
 // Reference: src/model/layer.rs:22-43 (x . W^T, weights [out, in]).
 #include <cooperative_groups.h>
 
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -73,10 +77,9 @@ __device__ __forceinline__ float gelu_tanh_f(float g) {
 
 // NT: activation tiles of 8 rows; MT: weight tiles of 16 rows per block.
 template <int NT, int MT, typename OutT, int EPI>
-__global__ void __launch_bounds__(256)
-skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
-                     OutT* __restrict__ y, int R, int N, int K, int x_stride, int y_stride,
-                     float cap, int ksplit, RopeTail rope) {
+__device__ __forceinline__ void skinny_linear_body(
+    const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x, OutT* __restrict__ y,
+    int R, int N, int K, int x_stride, int y_stride, float cap, int ksplit, const RopeTail& rope) {
     // [8 warps][MT][NT][32 lanes][4], then [ksplit - 1][MT][NT][32][4] for the other
     // blocks of the cluster (used in the cluster's first block only)
     extern __shared__ float red[];
@@ -271,15 +274,59 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
 }
 
 template <int NT, int MT, typename OutT, int EPI>
+__global__ void __launch_bounds__(256)
+skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                     OutT* __restrict__ y, int R, int N, int K, int x_stride, int y_stride,
+                     float cap, int ksplit, RopeTail rope) {
+    skinny_linear_body<NT, MT, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, ksplit, rope);
+}
+
+// The same with 48 registers instead of 52 to 56, so that an SM holds five blocks, not four
+// (one tile of rows only).
+template <typename OutT, int EPI>
+__global__ void __launch_bounds__(256, 5)
+skinny_linear_dense_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                           OutT* __restrict__ y, int R, int N, int K, int x_stride, int y_stride,
+                           float cap, int ksplit, RopeTail rope) {
+    skinny_linear_body<1, 1, OutT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, ksplit, rope);
+}
+
+template <int NT, int MT, typename OutT, int EPI>
 static int launch_skinny(const void* W, const void* x, void* y, int R, int N, int K, int x_stride,
                          int y_stride, float cap, const RopeTail& rope, cudaStream_t s) {
     const int blocks = (N + 16 * MT - 1) / (16 * MT);
     // few weight rows: several blocks (a cluster) share a tile of rows and split k, so
     // that enough loads are in flight to fill the memory system
+    static int sms = 0;          // (of the first device asked: the split is a matter of speed only)
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    static const int fill = getenv("SIB_SKINNY_FILL") ? atoi(getenv("SIB_SKINNY_FILL")) : 3;
     int ksplit = 1;
-    while (ksplit < 8 && blocks * ksplit < 3 * 148 && K >= 2 * ksplit * 8 * 64) ksplit *= 2;
+    while (ksplit < 8 && blocks * ksplit < fill * sms && K >= 2 * ksplit * 8 * 64) ksplit *= 2;
     const size_t smem = (size_t)(8 + ksplit - 1) * MT * NT * 32 * 4 * sizeof(float);
-    auto kernel = skinny_linear_kernel<NT, MT, OutT, EPI>;
+    // Five blocks an SM instead of four (48 registers, which costs a warp some of the loads
+    // it keeps in flight) where that is what lets every block be resident at once: a grid
+    // that nearly fills or overflows four blocks an SM and fits five.  Clusters need their
+    // blocks' places free at the same time, so a nearly full device places the last ones late.
+    // (Measured on single-token steps at context 8 192, batch 8 / batch 1: the Gemma2-2B shape's
+    // output and down products, 576 blocks each, -2.8 % / -5.7 % of the step's time, with q|k|v's
+    // 512 blocks -2.8 % / -6.3 %; its gate/up product, 1 152 blocks, +0.4 % / +1.1 %; the 9B shape's
+    // output product, 448 blocks, +0.9 % / +1.8 %; every product of the 27B shape +3.2 % / +5.6 %,
+    // its down product with 18 432 of k a block most of it: so only blocks with a short run of k.)
+    static const int dense_k = getenv("SIB_SKINNY_DENSE_K") ? atoi(getenv("SIB_SKINNY_DENSE_K")) : 2560;
+    const long long grid_blocks = (long long)blocks * ksplit;
+    bool dense = NT == 1 && MT == 1 && 20 * grid_blocks > 17 * 4 * sms && grid_blocks <= 5 * sms &&
+                 K / ksplit <= dense_k;
+    if (const char* only = getenv("SIB_SKINNY_DENSE_SHAPES")) {      // (for measurements)
+        char want[64];
+        snprintf(want, sizeof want, "%dx%d", N, K);
+        dense = NT == 1 && MT == 1 && (strstr(only, want) != nullptr || strstr(only, "all") != nullptr);
+    }
+    auto kernel = dense ? skinny_linear_dense_kernel<OutT, EPI> : skinny_linear_kernel<NT, MT, OutT, EPI>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
