@@ -359,6 +359,12 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
             join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane);
         else if (!WIDE && ITEMS <= 2 * (int)blockDim.x && p.splits <= 16)
             join_runs_by_warp<HD, G, 2, 16>(unit_partial, p.splits, out_row, lane);
+        else if (!WIDE && HD == 256 && ITEMS <= 2 * (int)blockDim.x && p.splits <= 32) {
+            // (only where the loop over the keys needs as many registers anyway: at smaller
+            // head sizes this would cost a resident block)
+            if constexpr (HD == 256)
+                join_runs_by_warp<HD, G, 2, 32>(unit_partial, p.splits, out_row, lane);
+        }
         else
             joined = false;
         if (joined) {
