@@ -3,7 +3,7 @@
 // (scale, soft cap, causal and window mask, softmax in 32-bit, weighted sum of
 // v); this file only changes how the work is laid out:
 //
-// * one block of 1, 2 or 4 warps per (row, kv head, split), each warp an equal
+// * one block of 1, 2, 4 or 8 warps per (row, kv head, split), each warp an equal
 //   share of the split's keys: the G = n_heads / n_kv query heads that share a kv
 //   head are done together, so each key and value is read once;
 // * keys are walked in tiles of 16 positions, aligned so that a tile lies in
@@ -20,6 +20,9 @@
 //   ticket of its (row, kv head); the block that draws the last ticket joins all
 //   the splits and writes the output, so no second kernel is needed.  The ticket
 //   counters are zero between launches: the last block puts its counter back.
+//   Neither join has a loop of one thread or a barrier of its own where the sizes
+//   allow it: every thread makes the warps' weights for its columns itself, and the
+//   last block's warps join their own columns (join_runs_by_warp).
 //
 // Plain counterpart: tests/plain_gemma2.py attention().
 // Reference: src/backend/cuda/kernels.rs:2851-3180 (grouped_attn_decode: one block
