@@ -332,7 +332,8 @@ def run_ours(args):
             torch.cuda.empty_cache()
 
     line = {
-        "metric": METRIC.replace("2B", args.shape.upper()), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
+        "metric": METRIC.replace("2B", args.shape.upper()).replace("batch 8", f"batch {args.batch}")
+                  .replace("context 8192", f"context {args.context}"), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "timed_blocks": BLOCKS, "spread_ms": [round(spread[0], 4), round(spread[1], 4)],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
