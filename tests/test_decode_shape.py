@@ -3,8 +3,6 @@ once, as few tiles of keys per warp as that allows, and no more warps than that 
 
 import itertools
 
-import pytest
-
 from strata_inference_b200.parts.attention import decode_shape
 
 RES4, RES8 = 1776, 1184        # warps a device of 148 SMs holds: 3 blocks of 4, 1 block of 8 an SM
@@ -14,24 +12,25 @@ def _tiles(longest, window):
     return -(-longest // 16) + (1 if 0 < window <= longest else 0)
 
 
-@pytest.mark.parametrize("units,longest,window", list(itertools.product(
-    (1, 4, 8, 16, 32, 64, 100, 256, 1024), (1, 16, 17, 500, 512, 1024, 4096, 8192), (0, 512, 4096))))
-def test_all_blocks_resident_and_no_warp_idle(units, longest, window):
-    seen = min(longest, window) if window else longest
-    runs, warps = decode_shape(units, seen, window, RES4, RES8)
-    assert runs >= 1 and warps in (1, 2, 4, 8) and runs <= 128
-    resident = RES8 if warps == 8 else RES4
-    # one wave: unless a single warp per (row, kv head) is already more than the device holds
-    assert runs * warps * units <= resident or runs * warps == 1
-    tiles = _tiles(seen, window)
-    each = -(-tiles // (runs * warps))
-    # no warp is left without a tile (a whole block at most, where blocks are wide)
-    assert (runs * warps - 1) * each < tiles + each * (warps - 1)
-    # and a warp walks at most about twice the fewest tiles that residency allows (wider
-    # blocks, which mean fewer partial results, may cost a tile or two), unless the number
-    # of runs is at the kernel's limit
-    best = -(-tiles // max(1, RES4 // units))
-    assert each <= 2 * best + 1 or runs == 128
+def test_all_blocks_resident_and_no_warp_idle():
+    for units, longest, window in itertools.product(
+            (1, 4, 8, 16, 32, 64, 100, 256, 1024), (1, 16, 17, 500, 512, 1024, 4096, 8192), (0, 512, 4096)):
+        where = f"units={units} longest={longest} window={window}"
+        seen = min(longest, window) if window else longest
+        runs, warps = decode_shape(units, seen, window, RES4, RES8)
+        assert runs >= 1 and warps in (1, 2, 4, 8) and runs <= 128, where
+        resident = RES8 if warps == 8 else RES4
+        # one wave: unless a single warp per (row, kv head) is already more than the device holds
+        assert runs * warps * units <= resident or runs * warps == 1, where
+        tiles = _tiles(seen, window)
+        each = -(-tiles // (runs * warps))
+        # no warp is left without a tile (a whole block at most, where blocks are wide)
+        assert (runs * warps - 1) * each < tiles + each * (warps - 1), where
+        # and a warp walks at most about twice the fewest tiles that residency allows (wider
+        # blocks, which mean fewer partial results, may cost a tile or two), unless the number
+        # of runs is at the kernel's limit
+        best = -(-tiles // max(1, RES4 // units))
+        assert each <= 2 * best + 1 or runs == 128, where
 
 
 def test_few_rows_take_wide_blocks_and_one_tile_a_warp():
